@@ -1,0 +1,142 @@
+"""GPU parity: dequant (bit-exact) and the dequant-fused matvec (rel 1e-3) against the oracle and
+against outputs of the reference's own compiled C, all through the C ABI."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from conftest import rel_err_ok
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+DIGESTS = json.load(open(os.path.join(HERE, "golden", "reference_digests.json")))
+VEC = np.load(os.path.join(HERE, "golden", "ref_vectors.npz"))
+
+
+def host_dequant(lib, enc, packed):
+    from skainet_b200 import _lib as L
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    nb = packed.size // L.BLOCK_BYTES[enc]
+    out = np.empty(nb * L.BLOCK_ELEMS[enc], dtype=np.float32)
+    L.check(lib.skainet_cuda_dequant(L.ENC[enc], packed.ctypes.data_as(L.u8p), nb, out.ctypes.data_as(L.f32p)))
+    return out
+
+
+@pytest.mark.parametrize("enc", ["Q8_0", "Q4_K", "Q5_K", "Q6_K"])
+def test_dequant_reproduces_reference_golden_digest(gpu, cuda_lib, oracle, enc):
+    blocks = oracle.golden_weight_blocks(enc, 4, 3, 0x5EED0001)
+    got = host_dequant(cuda_lib, enc, oracle.golden_row_major(blocks))
+    assert oracle.golden_digest(got) == DIGESTS[f"decode/{enc}"]
+
+
+@pytest.mark.parametrize("enc", ["Q8_0", "Q4_K", "Q5_K", "Q6_K"])
+def test_dequant_bit_exact_on_random_bytes(gpu, cuda_lib, oracle, enc):
+    # every byte random, f16 fields sane (the reference's own fixture builder), 64 blocks
+    blocks = oracle.golden_weight_blocks(enc, 8, 8, 1234)
+    packed = oracle.golden_row_major(blocks)
+    np.testing.assert_array_equal(host_dequant(cuda_lib, enc, packed).view(np.uint32), oracle.dequant(enc, packed).view(np.uint32))
+
+
+@pytest.mark.parametrize("enc", ["Q8_0", "Q4_K", "Q5_K", "Q6_K"])
+@pytest.mark.parametrize("order", [0, 1])
+def test_upload_split_export_is_the_identity_and_resident_dequant_is_bit_exact(gpu, oracle, enc, order):
+    rows, bpr = 5, 3
+    blocks = oracle.golden_weight_blocks(enc, rows, bpr, 77)
+    rm = oracle.golden_row_major(blocks)
+    given = rm if order == 0 else oracle.golden_block_major(blocks)
+    w = gpu.Weight.upload(given, enc, rows, bpr * oracle.BLOCK_ELEMS[enc], order)
+    np.testing.assert_array_equal(w.export(), rm)
+    np.testing.assert_array_equal(w.dequant().reshape(-1).view(np.uint32), oracle.dequant(enc, rm).view(np.uint32))
+    w.free()
+
+
+@pytest.mark.parametrize("tag", ["Q4_K_1024x37", "Q4_K_2816x16", "Q8_0_512x45", "Q8_0_96x7"])
+def test_host_twins_match_reference_c_outputs(gpu, oracle, tag):
+    from skainet_b200.provider import CudaKernelProvider
+    enc = tag[:4]; k, n = (int(t) for t in tag[5:].split("x"))
+    p = CudaKernelProvider()
+    assert p.isAvailable()
+    w, x = VEC[tag + "_w"], VEC[tag + "_x"]
+    for row_major in (True, False):
+        kern = (p.matmulQ4KRowMajor() if row_major else p.matmulQ4K()) if enc == "Q4_K" else \
+               (p.matmulQ8_0RowMajor() if row_major else p.matmulQ8_0())
+        wb = w if row_major else oracle.to_feed_order(w, enc, n, k)
+        # offsets exercised like the SPI allows: activation, weight and output all start mid-array
+        xin = np.concatenate([np.full(5, 9.0, np.float32), x])
+        wbuf = np.concatenate([np.full(16, 0xEE, np.uint8), wb])
+        out = np.full(n + 3, -7.0, np.float32)
+        x_before, w_before = xin.copy(), wbuf.copy()
+        kern.matmul(xin, 5, wbuf, 16, k, n, out, 3)
+        assert (out[:3] == -7.0).all()
+        np.testing.assert_array_equal(xin, x_before); np.testing.assert_array_equal(wbuf, w_before)
+        rel_err_ok(out[3:], VEC[tag + ("_y_rm" if row_major else "_y_feed")])
+
+
+@pytest.mark.parametrize("enc,n,k", [("Q4_K", 64, 256), ("Q4_K", 129, 4096), ("Q4_K", 33, 11008), ("Q4_K", 1, 512),
+                                     ("Q8_0", 64, 32), ("Q8_0", 130, 4096), ("Q8_0", 9, 11008), ("Q8_0", 1, 64)])
+@pytest.mark.parametrize("m", [1, 3, 8, 13])
+def test_resident_matvec_matches_oracle(gpu, oracle, enc, n, k, m):
+    rng = np.random.default_rng(n * 131 + k + m)
+    wf = (0.02 * rng.standard_normal((n, k))).astype(np.float32)
+    packed = oracle.quantize_q4k(wf) if enc == "Q4_K" else oracle.quantize_q8_0(wf)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = gpu.Weight.upload(packed, enc, n, k)
+    ref = oracle.matmul(enc, x, packed, k, n, "rm", use_ref=oracle.ref() is not None)
+    rel_err_ok(gpu.matmul_host(w, x), ref)
+    # F32 mode = the exact-float arithmetic of the scalar Kotlin kernels
+    exact = x.astype(np.float64) @ oracle.dequant(enc, packed).reshape(n, k).astype(np.float64).T
+    rel_err_ok(gpu.matmul_host(w, x, act_mode=1), exact, 1e-4)
+    w.free()
+
+
+def test_q4k_saturated_codes_and_adversarial_activation(gpu, oracle):
+    # all nibbles 15, all scales/mins 63, activation alternating +-max: integer partial sums at their extremes
+    n, k = 8, 1024
+    blk = np.zeros(144, np.uint8)
+    blk[0:2] = np.array([0.01], np.float16).view(np.uint8); blk[2:4] = np.array([0.02], np.float16).view(np.uint8)
+    blk[4:16] = oracle.pack_k4_scales(np.full((1, 8), 63), np.full((1, 8), 63))[0]
+    blk[16:] = 0xFF
+    packed = np.tile(blk, n * (k // 256))
+    for x in (np.full(k, 3.0, np.float32), np.where(np.arange(k) % 2 == 0, 5.0, -5.0).astype(np.float32)):
+        w = gpu.Weight.upload(packed, "Q4_K", n, k)
+        rel_err_ok(gpu.matmul_host(w, x), oracle.matmul("Q4_K", x, packed, k, n, "rm"))
+        w.free()
+
+
+def test_zero_activation_blocks(gpu, oracle):
+    rng = np.random.default_rng(9)
+    n, k = 16, 1024
+    packed = oracle.quantize_q4k((0.02 * rng.standard_normal((n, k))).astype(np.float32))
+    x = rng.standard_normal(k).astype(np.float32); x[256:512] = 0.0
+    w = gpu.Weight.upload(packed, "Q4_K", n, k)
+    rel_err_ok(gpu.matmul_host(w, x), oracle.matmul("Q4_K", x, packed, k, n, "rm"))
+    assert not gpu.matmul_host(w, np.zeros(k, np.float32)).any()
+    w.free()
+
+
+def test_linearity_at_full_size_q4k(gpu):
+    """Size-independent property at the BASELINE shape (11008 x 4096, F32 mode is linear in x):
+    W(a + b) == W a + W b within fp32 rounding, on a device-generated weight."""
+    w = gpu.Weight.synth("Q4_K", 11008, 4096, seed=3, std=0.02)
+    rng = np.random.default_rng(10)
+    a = rng.standard_normal(4096).astype(np.float32); b = rng.standard_normal(4096).astype(np.float32)
+    ya, yb, yab = (gpu.matmul_host(w, v, act_mode=1) for v in (a, b, a + b))
+    rel_err_ok(yab, ya.astype(np.float64) + yb, 1e-4)
+    # and the native (int8-activation) mode stays within its documented distance of the exact product
+    yn = gpu.matmul_host(w, a)
+    rel_rms = np.sqrt(np.mean((yn - ya) ** 2) / np.mean(ya ** 2))
+    assert rel_rms < 0.03
+    w.free()
+
+
+def test_synth_weights_are_valid_and_match_oracle_on_exported_bytes(gpu, oracle):
+    for enc, n, k in (("Q4_K", 40, 2048), ("Q8_0", 24, 1024)):
+        w = gpu.Weight.synth(enc, n, k, seed=5, std=0.02)
+        packed = w.export()
+        deq = oracle.dequant(enc, packed)
+        assert np.isfinite(deq).all() and 0.015 < deq.std() < 0.025 and abs(deq.mean()) < 2e-3
+        np.testing.assert_array_equal(w.dequant().reshape(-1).view(np.uint32), deq.view(np.uint32))
+        x = np.random.default_rng(6).standard_normal(k).astype(np.float32)
+        rel_err_ok(gpu.matmul_host(w, x), oracle.matmul(enc, x, packed, k, n, "rm"))
+        w.free()

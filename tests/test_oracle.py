@@ -1,0 +1,146 @@
+"""CPU: the oracle pinned to the reference's own golden digests and compiled kernels."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from conftest import rel_err_ok
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+DIGESTS = json.load(open(os.path.join(HERE, "golden", "reference_digests.json")))
+VEC = np.load(os.path.join(HERE, "golden", "ref_vectors.npz"))
+
+
+@pytest.mark.parametrize("enc", ["Q8_0", "Q4_K", "Q5_K", "Q6_K"])
+def test_decode_digest_matches_reference_golden(oracle, enc):
+    # PackedDecodeGoldenTest.kt:27-60: 4 rows x 3 blocks, seed 0x5EED_0001, row-major bytes
+    blocks = oracle.golden_weight_blocks(enc, 4, 3, 0x5EED0001)
+    got = oracle.golden_digest(oracle.dequant(enc, oracle.golden_row_major(blocks)))
+    assert got == DIGESTS[f"decode/{enc}"]
+
+
+@pytest.mark.parametrize("enc", ["Q8_0", "Q4_K"])
+def test_scalar_matmul_digest_matches_reference_golden(oracle, enc):
+    # ScalarKernelGoldenTest.kt:16-42: OUT=4, BLOCKS=3, BATCH=3, seed 0x5EED_0002, feed-order bytes
+    k = 3 * oracle.BLOCK_ELEMS[enc]
+    w = oracle.golden_block_major(oracle.golden_weight_blocks(enc, 4, 3, 0x5EED0002))
+    x = oracle.golden_floats(3 * k, 0x5EED0002 + 100)
+    out = np.concatenate([oracle.scalar_matmul(enc, x[r * k:(r + 1) * k], w, k, 4) for r in range(3)])
+    assert oracle.golden_digest(out) == DIGESTS[f"scalar-matmul/{enc}"]
+    # the dispatch bridge golden is the first activation row of the same computation
+    assert oracle.golden_digest(out[:4]) == DIGESTS[f"dispatch-bridge/{enc}"]
+
+
+def test_q4k_analytic_block(oracle):
+    # Q4KCanonicalLayoutTest.kt:171-200 style known-answer block: d=0.125, dMin=0.0625, distinct scales/mins
+    sc = np.array([[1, 2, 3, 4, 17, 34, 51, 63]]); mn = np.array([[8, 7, 6, 5, 20, 40, 60, 33]])
+    blk = np.zeros(144, dtype=np.uint8)
+    blk[0:2] = np.array([0.125], dtype=np.float16).view(np.uint8)
+    blk[2:4] = np.array([0.0625], dtype=np.float16).view(np.uint8)
+    blk[4:16] = oracle.pack_k4_scales(sc, mn)[0]
+    codes = (np.arange(256) * 7 + 3) % 16
+    qg = codes.reshape(4, 2, 32)
+    blk[16:] = (qg[:, 0, :] | (qg[:, 1, :] << 4)).reshape(-1)
+    want = (0.125 * np.repeat(sc[0], 32)) * codes - 0.0625 * np.repeat(mn[0], 32)
+    np.testing.assert_array_equal(oracle.dequant("Q4_K", blk), want.astype(np.float32))
+
+
+def test_q4k_nibble_order(oracle):
+    # Q4KDequantizationTest.kt:115-129: byte i of group g holds element 64g+i (low) and 64g+32+i (high)
+    blk = np.zeros(144, dtype=np.uint8)
+    blk[0:2] = np.array([1.0], dtype=np.float16).view(np.uint8)
+    blk[4:8] = 1; blk[12:16] = 1          # all eight scales = 1, mins = 0
+    blk[16 + 32 * 2 + 5] = 0xA3
+    out = oracle.dequant("Q4_K", blk)
+    assert out[64 * 2 + 5] == 3.0 and out[64 * 2 + 32 + 5] == 10.0 and out.sum() == 13.0
+
+
+def test_q8_0_quantizer_rule(oracle):
+    # Q8_0QuantizerTest.kt:25-35: d = amax/127 stored as RNE fp16, codes round(x/d) clamped
+    rng = np.random.default_rng(3)
+    v = rng.standard_normal(64).astype(np.float32)
+    packed = oracle.quantize_q8_0(v).reshape(2, 34)
+    for b in range(2):
+        d = np.float32(np.abs(v[32 * b:32 * b + 32]).max() / np.float32(127))
+        assert packed[b, :2].view(np.float16)[0] == np.float16(d)
+        assert np.abs(packed[b, 2:].view(np.int8)).max() == 127
+    back = oracle.dequant("Q8_0", packed.reshape(-1))
+    assert np.abs(back - v).max() <= np.abs(v).max() / 127 * 0.51 + 1e-3
+    assert oracle.quantize_q8_0(np.zeros(32, np.float32)).sum() == 0
+
+
+def test_q4k_packer_round_trip(oracle):
+    rng = np.random.default_rng(4)
+    w = (0.02 * rng.standard_normal((8, 512))).astype(np.float32)
+    back = oracle.dequant("Q4_K", oracle.quantize_q4k(w)).reshape(8, 512)
+    assert np.sqrt(np.mean((back - w) ** 2)) < 0.1 * 0.02
+
+
+@pytest.mark.parametrize("tag", ["Q4_K_1024x37", "Q4_K_2816x16", "Q8_0_512x45", "Q8_0_96x7"])
+def test_port_matvec_matches_reference_c(oracle, tag):
+    enc = tag[:4]; k, n = (int(t) for t in tag[5:].split("x"))
+    w, x = VEC[tag + "_w"], VEC[tag + "_x"]
+    y_rm = oracle.matmul(enc, x, w, k, n, "rm")
+    y_feed = oracle.matmul(enc, x, oracle.to_feed_order(w, enc, n, k), k, n, "feed")
+    np.testing.assert_array_equal(y_rm, y_feed)             # layout parity (RowMajorMatmulParityTest.kt:16-24)
+    rel_err_ok(y_rm, VEC[tag + "_y_rm"], 2e-5)              # -ffast-math reassociation only
+    rel_err_ok(y_rm, VEC[tag + "_y_feed"], 2e-5)
+
+
+def test_compiled_reference_matches_committed_vectors(oracle):
+    if oracle.ref() is None:
+        pytest.skip("oracle/_ref not built here")
+    tag = "Q4_K_1024x37"
+    y = oracle.matmul("Q4_K", VEC[tag + "_x"], VEC[tag + "_w"], 1024, 37, "rm", use_ref=True)
+    np.testing.assert_array_equal(y, VEC[tag + "_y_rm"])
+
+
+def test_q4k_native_differs_from_exact_float_by_activation_quantization(oracle):
+    # NativeQ4KMatmulKernelParityTest.kt:75-103: aggregate RMS-relative <= 0.03 against the exact-float kernel
+    tag = "Q4_K_1024x37"
+    w, x = VEC[tag + "_w"], VEC[tag + "_x"]
+    exact = oracle.dequant("Q4_K", w).reshape(37, 1024).astype(np.float64) @ x.astype(np.float64)
+    native = oracle.matmul("Q4_K", x, w, 1024, 37, "rm")
+    rel_rms = np.sqrt(np.mean((native - exact) ** 2) / np.mean(exact ** 2))
+    assert 1e-4 < rel_rms < 0.03
+
+
+def test_port_row_kernels_match_reference_c(oracle):
+    rel_err_ok(oracle.rms_norm(VEC["rms_x"], VEC["rms_g"], 1e-5), VEC["rms_y"], 1e-5)
+    rel_err_ok(oracle.sdpa(VEC["sdpa_dec_q"], VEC["sdpa_dec_k"], VEC["sdpa_dec_v"], 0.125, causal=True), VEC["sdpa_dec_o"], 1e-5)
+    rel_err_ok(oracle.sdpa(VEC["sdpa_win_q"], VEC["sdpa_win_k"], VEC["sdpa_win_v"], 0.2, causal=True, window=4),
+               VEC["sdpa_win_o"], 1e-5)
+    rel_err_ok(oracle.silu(VEC["silu_x"]), VEC["silu_y"], 1e-5)
+
+
+def test_sdpa_fully_masked_row_is_uniform_and_finite(oracle):
+    # NativeFusedKernelsTest.kt:198-205
+    rng = np.random.default_rng(5)
+    q = rng.standard_normal((1, 2, 1, 32)).astype(np.float32)
+    k = rng.standard_normal((1, 2, 6, 32)).astype(np.float32); v = rng.standard_normal((1, 2, 6, 32)).astype(np.float32)
+    out = oracle.sdpa(q, k, v, 1.0, causal=False, lengths=np.array([0], dtype=np.int32))
+    np.testing.assert_allclose(out[0, :, 0, :], v[0].mean(axis=1), rtol=1e-5, atol=1e-6)
+
+
+def test_q8_activation_quantizer(oracle):
+    x = np.linspace(-3, 5, 512).astype(np.float32)
+    q8, d = oracle.q8_quantize(x)
+    assert q8.dtype == np.int8 and np.abs(q8).max() == 127
+    np.testing.assert_allclose(d, [3.0 / 127 if False else np.abs(x[:256]).max() / 127, 5.0 / 127], rtol=1e-6)
+    q8z, dz = oracle.q8_quantize(np.zeros(256, np.float32))
+    assert dz[0] == 0.0 and not q8z.any()
+
+
+def test_rope_conventions(oracle):
+    x = np.arange(8, dtype=np.float32).reshape(1, 8) + 1
+    np.testing.assert_array_equal(oracle.rope(x, 1, 8, 0), x)            # position 0 is the identity
+    y0 = oracle.rope(x, 1, 8, 3, 1e4, 0); y1 = oracle.rope(x, 1, 8, 3, 1e4, 1)
+    c, s = np.cos(3.0), np.sin(3.0)
+    np.testing.assert_allclose(y0[0, :2], [1 * c - 2 * s, 1 * s + 2 * c], rtol=1e-6)     # pair (0,1)
+    np.testing.assert_allclose([y1[0, 0], y1[0, 4]], [1 * c - 5 * s, 1 * s + 5 * c], rtol=1e-6)  # pair (0,4)
+    np.testing.assert_allclose(np.linalg.norm(y0), np.linalg.norm(x), rtol=1e-6)
+
+
+def test_argmax_lowest_index_on_ties(oracle):
+    assert oracle.argmax(np.array([1, 5, 5, 2], dtype=np.float32)) == 1
