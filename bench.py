@@ -216,7 +216,7 @@ def run_ours(args) -> None:
     barrier()
     ms = e0.elapsed_time(e1)
     # keep the GPU busy long enough for the clock sampler to see it under load
-    if rank == 0:
+    if rank == 0 and not args.skip_cpu:
         t_end = time.time() + 1.0
         with torch.cuda.stream(stream):
             while time.time() < t_end:
@@ -235,8 +235,8 @@ def run_ours(args) -> None:
                 device.matmul(weights[si][ci], xs[si].data_ptr(), 1, ys[si].data_ptr(), L.ACT_NATIVE, sp)
                 L.check(lib.skainet_cuda_memcpy_d2h(hy[si].data_ptr(), ys[si].data_ptr(), hy[si].numel() * 4, sp))  # syncs
 
-    e2e_steps = max(1, min(args.steps, 5))
-    for _ in range(2):
+    e2e_steps = 0 if args.skip_e2e else max(1, min(args.steps, 5))
+    for _ in range(0 if args.skip_e2e else 2):
         e2e_sweep()
     barrier()
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -258,7 +258,7 @@ def run_ours(args) -> None:
         nmat = copies * len(shapes)
         per_launch_us = ms * 1e3 / (args.steps * nmat)
         achieved = (bytes_per_step / nmat) / (per_launch_us * 1e-6) / 1e9
-        cpu = cpu_matvec_rate(args.workload, 10.0) if world == 1 else None
+        cpu = cpu_matvec_rate(args.workload, 10.0) if (world == 1 and not args.skip_cpu) else None
         line = {
             "metric": f"{args.workload}_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
@@ -268,7 +268,7 @@ def run_ours(args) -> None:
                          "traffic": None, "peak_kind": peak_kind, "kernel": "q4k_matvec_kernel<1>" if enc == "Q4_K" else "q8_0_matvec_kernel<1>",
                          "avg_launch_us": per_launch_us,
                          "note": "avg launch = timed region / matvec launches (activation quantizer and launch gaps included)"},
-            "e2e": {"value": bytes_per_step * world * e2e_steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+            "e2e": {"value": (bytes_per_step * world * e2e_steps / (e2e_ms * 1e-3) / 1e9) if e2e_steps else None, "unit": "GB/s",
                     "h2d_bytes_per_step": int(sum(4 * c for _, c in shapes) * copies),
                     "d2h_bytes_per_step": int(sum(4 * r for r, _ in shapes) * copies),
                     "note": "weights resident; each matvec copies its activation in and its output out"},
@@ -288,6 +288,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="q4k_matvec", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-cpu", action="store_true", help="omit the cpu_baseline leg (profiling runs)")
+    ap.add_argument("--skip-e2e", action="store_true", help="omit the end-to-end leg (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

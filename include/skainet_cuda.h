@@ -79,6 +79,11 @@ SKAINET_CUDA_API int32_t skainet_cuda_set_device(int32_t device);
 /* Device facts a host needs for sizing: [0]=SM count, [1]=L2 bytes, [2]=total HBM bytes, [3]=cc major*10+minor. */
 SKAINET_CUDA_API int32_t skainet_cuda_device_info(int64_t* out4);
 
+/* Synchronises the device and reports SKAINET_CUDA_ERR_TIMEOUT if any kernel since the last call gave
+ * up a bounded wait (its outputs are then invalid); clears the condition. The reference has no
+ * counterpart: its kernels cannot time out. */
+SKAINET_CUDA_API int32_t skainet_cuda_device_status(void);
+
 /* ---- 1. drop-in twins (HOST pointers) -------------------------------------------------------- */
 
 /* Availability probe, out[i] = 2*in[i] computed on the GPU.
@@ -175,6 +180,15 @@ SKAINET_CUDA_API int32_t skainet_cuda_weight_dequant(skainet_weight_t w, float* 
  * which issues m matvec calls. act_mode: SKAINET_ACT_*. */
 SKAINET_CUDA_API int32_t skainet_cuda_matmul_dev(skainet_weight_t w, const float* x_dev, int32_t m, float* y_dev,
     int32_t act_mode, skainet_stream_t stream);
+
+/* One decode-step linear in a single launch: y[rows] = (resid +) W . quantize(norm(x)) for one
+ * activation row. gamma_dev != NULL applies RMSNorm (x / sqrt(mean(x^2)+eps) * gamma, the arithmetic
+ * of skainet_f32_rms_norm, skainet_kernels.h:574-576) before the reference's activation
+ * quantization; resid_dev != NULL adds the result to a residual (y may alias resid). This is the
+ * CUDA handler for the graph-level fused ops `fused_rms_norm` + matmul (+ add) that
+ * skainet-compile/skainet-compile-opt/src/commonMain/kotlin/sk/ainet/compile/opt/passes/LLMFusionPass.kt:12-22 emits. */
+SKAINET_CUDA_API int32_t skainet_cuda_matvec_fused_dev(skainet_weight_t w, const float* x_dev, const float* gamma_dev,
+    float eps, const float* resid_dev, float* y_dev, skainet_stream_t stream);
 
 /* Row kernels on the device (contracts as the twins above). */
 SKAINET_CUDA_API int32_t skainet_cuda_rms_norm_dev(const float* in, const float* gamma, float* out,

@@ -37,6 +37,7 @@ SIGNATURES = {
     "skainet_cuda_device_count": [],
     "skainet_cuda_set_device": [i32],
     "skainet_cuda_device_info": [i64p],
+    "skainet_cuda_device_status": [],
     "skainet_cuda_smoke_double": [f32p, f32p, i32],
     "skainet_cuda_q4k_matmul": _MATVEC,
     "skainet_cuda_q4k_matmul_rm": _MATVEC,
@@ -62,6 +63,7 @@ SIGNATURES = {
     "skainet_cuda_weight_free": [i64],
     "skainet_cuda_weight_dequant": [i64, vp, vp],
     "skainet_cuda_matmul_dev": [i64, vp, i32, vp, i32, vp],
+    "skainet_cuda_matvec_fused_dev": [i64, vp, vp, f32, vp, vp, vp],
     "skainet_cuda_rms_norm_dev": [vp, vp, vp, i32, i32, f32, vp],
     "skainet_cuda_unary_dev": [i32, vp, vp, i64, vp],
     "skainet_cuda_binary_dev": [i32, vp, i32, vp, i32, vp, i64, i32, vp],

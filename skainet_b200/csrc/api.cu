@@ -2,6 +2,7 @@
 // the resident-weight registry, per-stream scratch, and the host-pointer twins of the reference's
 // native entry points, which are thin wrappers over the resident API (upload, run, read back).
 #include "common.cuh"
+#include "matvec_fused.cuh"
 
 #include <cstdarg>
 #include <cstdio>
@@ -67,6 +68,20 @@ int32_t ensure_device() {
 int sm_count() {
     const int c = t_device < 64 ? g_sm_count[t_device] : 0;
     return c > 0 ? c : 148;
+}
+
+// One int per device, set by kernels whose bounded waits give up.
+static int* g_timeout_flag[64] = {nullptr};
+int* device_timeout_flag() {
+    if (t_device >= 64) return nullptr;
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_timeout_flag[t_device]) {
+        int* p = nullptr;
+        if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        cudaMemset(p, 0, sizeof(int));
+        g_timeout_flag[t_device] = p;
+    }
+    return g_timeout_flag[t_device];
 }
 
 // ---- weight registry ---------------------------------------------------------------------------------------
@@ -189,6 +204,20 @@ int32_t skainet_cuda_device_info(int64_t* out4) {
     cudaDeviceProp p;
     SK_CUDA(cudaGetDeviceProperties(&p, t_device));
     out4[0] = p.multiProcessorCount; out4[1] = p.l2CacheSize; out4[2] = (int64_t) p.totalGlobalMem; out4[3] = p.major * 10 + p.minor;
+    return SKAINET_CUDA_OK;
+}
+
+int32_t skainet_cuda_device_status(void) {
+    SK_TRY(ensure_device());
+    int* flag = device_timeout_flag();
+    if (!flag) return SKAINET_CUDA_OK;
+    int v = 0;
+    SK_CUDA(cudaMemcpy(&v, flag, sizeof(int), cudaMemcpyDeviceToHost));
+    if (v != 0) {
+        cudaMemset(flag, 0, sizeof(int));
+        set_error("a kernel's bounded wait on an asynchronous copy ran out; its outputs are not valid");
+        return SKAINET_CUDA_ERR_TIMEOUT;
+    }
     return SKAINET_CUDA_OK;
 }
 
@@ -361,7 +390,49 @@ int32_t skainet_cuda_matmul_dev(skainet_weight_t h, const float* x_dev, int32_t 
     const size_t need = act_scratch_bytes(w->enc, act_mode, m, w->cols);
     if (need) SK_TRY(scratch_get(s, SCRATCH_ACT, need, &scratch));
     SK_TRY(launch_act_quant(w->enc, act_mode, x_dev, m, w->cols, scratch, s));
+    if (m == 1 && act_mode == SKAINET_ACT_NATIVE && matvec_env_mode() == 0) {
+        MatvecIn in;
+        if (w->enc == SKAINET_ENC_Q8_0) in.split = act_split_layout(scratch, 1, w->cols); else in.q8 = act_q8k_layout(scratch, 1, w->cols);
+        const int32_t st = launch_matvec_fused(*w, in, PREP_QUANTIZED, y_dev, nullptr, s);
+        if (st != 1) return st;
+    }
     return launch_matvec(*w, x_dev, scratch, m, y_dev, act_mode, s);
+}
+
+int32_t skainet_cuda_matvec_fused_dev(skainet_weight_t h, const float* x_dev, const float* gamma_dev, float eps,
+                                      const float* resid_dev, float* y_dev, skainet_stream_t stream) {
+    Weight* w = weight_from_handle(h);
+    if (!w) return SKAINET_CUDA_ERR_HANDLE;
+    if (w->rows == 0) return SKAINET_CUDA_OK;
+    SK_REQUIRE(x_dev != nullptr && y_dev != nullptr, "matvec_fused: null activation or output");
+    SK_REQUIRE((((uintptr_t) x_dev | (uintptr_t) gamma_dev) & 15) == 0, "matvec_fused: x and gamma must be 16-byte aligned");
+    SK_REQUIRE(w->cols > 0, "matvec_fused: empty input dimension");
+    SK_TRY(ensure_device());
+    cudaStream_t s = as_stream(stream);
+    MatvecIn in; in.x = x_dev; in.gamma = gamma_dev; in.eps = eps;
+    const int32_t st = launch_matvec_fused(*w, in, gamma_dev ? PREP_NORM_F32 : PREP_F32, y_dev, resid_dev, s);
+    if (st != 1) return st;
+    // shapes the fused kernel does not take: the same result from the general kernels
+    const float* xin = x_dev;
+    if (gamma_dev) {
+        void* tmp = nullptr;
+        SK_TRY(scratch_get(s, SCRATCH_FUSED, sizeof(float) * (size_t) w->cols, &tmp));
+        SK_TRY(launch_rms_norm(x_dev, gamma_dev, (float*) tmp, 1, w->cols, eps, s));
+        xin = (const float*) tmp;
+    }
+    float* yout = y_dev;
+    if (resid_dev) {
+        void* tmp = nullptr;
+        SK_TRY(scratch_get(s, SCRATCH_FUSED2, sizeof(float) * (size_t) w->rows, &tmp));
+        yout = (float*) tmp;
+    }
+    void* scratch = nullptr;
+    const size_t need = act_scratch_bytes(w->enc, SKAINET_ACT_NATIVE, 1, w->cols);
+    if (need) SK_TRY(scratch_get(s, SCRATCH_ACT, need, &scratch));
+    SK_TRY(launch_act_quant(w->enc, SKAINET_ACT_NATIVE, xin, 1, w->cols, scratch, s));
+    SK_TRY(launch_matvec(*w, xin, scratch, 1, yout, SKAINET_ACT_NATIVE, s));
+    if (resid_dev) SK_TRY(launch_binary(0, resid_dev, 0, yout, 0, y_dev, w->rows, 1, s));
+    return SKAINET_CUDA_OK;
 }
 
 int32_t skainet_cuda_rms_norm_dev(const float* in, const float* gamma, float* out, int32_t rows, int32_t cols, float eps,

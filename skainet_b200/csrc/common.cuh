@@ -76,9 +76,10 @@ Weight* weight_from_handle(skainet_weight_t h);   // nullptr (+ error set) when 
 // Grown on demand outside stream capture; never shrinks.
 int32_t scratch_get(cudaStream_t stream, int slot, size_t nbytes, void** out);
 enum { SCRATCH_ACT = 0, SCRATCH_ATTN = 1, SCRATCH_TWIN_A = 2, SCRATCH_TWIN_B = 3, SCRATCH_TWIN_C = 4,
-       SCRATCH_TWIN_D = 5, SCRATCH_TWIN_E = 6, SCRATCH_TWIN_F = 7, SCRATCH_SLOTS = 8 };
+       SCRATCH_TWIN_D = 5, SCRATCH_TWIN_E = 6, SCRATCH_TWIN_F = 7, SCRATCH_FUSED = 8, SCRATCH_FUSED2 = 9, SCRATCH_SLOTS = 10 };
 
 int sm_count();
+int* device_timeout_flag();   // device int set by a kernel whose bounded wait ran out (nullptr if unavailable)
 
 // ---- launchers implemented in the kernel files ------------------------------------------------------
 // repack.cu
@@ -89,10 +90,13 @@ int32_t launch_dequant_canonical(int enc, const uint8_t* canon_dev, int64_t nblo
 int32_t launch_synth(Weight& w, uint64_t seed, float std, int mode, cudaStream_t s);
 int32_t launch_embed(const Weight& w, const int32_t* ids, int n, float* out, cudaStream_t s);
 // matvec.cu
+int matvec_env_mode();
 size_t act_scratch_bytes(int enc, int act_mode, int m, int cols);
 int32_t launch_act_quant(int enc, int act_mode, const float* x, int m, int cols, void* scratch, cudaStream_t s);
 int32_t launch_matvec(const Weight& w, const float* x, const void* act_scratch, int m, float* y, int act_mode,
                       cudaStream_t s);
+// matvec_stream.cu: rows m0..m0+mm of the quantized activation; returns 1 when the shape is not taken
+int32_t launch_matvec_stream(const Weight& w, const void* act_scratch, int m_total, int m0, int mm, float* y, cudaStream_t s);
 // rowops.cu
 int32_t launch_rms_norm(const float* in, const float* gamma, float* out, int rows, int cols, float eps, cudaStream_t s);
 int32_t launch_unary(int op, const float* in, float* out, int64_t n, cudaStream_t s);

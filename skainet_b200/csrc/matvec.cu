@@ -11,6 +11,10 @@
 //         ScalarQ4_KMatmulKernel.kt:66-75 and ScalarQ8_0MatmulKernel.kt:56-59.
 #include "common.cuh"
 #include "actquant.cuh"
+#include "tma.cuh"
+
+#include <cstdlib>
+#include <cstring>
 
 namespace sk {
 
@@ -43,12 +47,16 @@ ActSplit act_split_layout(void* scratch, int m, int cols) {
 // ---- activation quantizers ----------------------------------------------------------------------------
 // One warp per 256-element block of one activation row.
 __global__ void act_quant_q8k_kernel(const float* x, int64_t nblocks, ActQ8K a) {
+    skd::pdl_launch_dependents();
+    skd::pdl_wait();
     const int64_t warp = (blockIdx.x * (int64_t) blockDim.x + threadIdx.x) >> 5;
     if (warp >= nblocks) return;
     skd::quant_q8k_block(x + warp * 256, a.q + warp * 256, a.d + warp, a.bsums + warp * 8, threadIdx.x & 31);
 }
 // One warp per 8 blocks of 32 (lane group of 4 per block).
 __global__ void act_quant_split_kernel(const float* x, int64_t nblocks32, ActSplit a) {
+    skd::pdl_launch_dependents();
+    skd::pdl_wait();
     const int64_t t = blockIdx.x * (int64_t) blockDim.x + threadIdx.x;
     const int64_t blk = t >> 2;
     const bool live = blk < nblocks32;
@@ -59,10 +67,10 @@ int32_t launch_act_quant(int enc, int act_mode, const float* x, int m, int cols,
     if (act_mode == SKAINET_ACT_F32 || m == 0 || cols == 0) return SKAINET_CUDA_OK;
     if (enc == SKAINET_ENC_Q8_0) {
         const int64_t nb = (int64_t) m * (cols / 32);
-        act_quant_split_kernel<<<(unsigned) ((nb * 4 + 255) / 256), 256, 0, s>>>(x, nb, act_split_layout(scratch, m, cols));
+        SK_CUDA(launch_pdl(act_quant_split_kernel, dim3((unsigned) ((nb * 4 + 255) / 256)), dim3(256), 0, s, x, nb, act_split_layout(scratch, m, cols)));
     } else {
         const int64_t nb = (int64_t) m * (cols / 256);
-        act_quant_q8k_kernel<<<(unsigned) ((nb * 32 + 255) / 256), 256, 0, s>>>(x, nb, act_q8k_layout(scratch, m, cols));
+        SK_CUDA(launch_pdl(act_quant_q8k_kernel, dim3((unsigned) ((nb * 32 + 255) / 256)), dim3(256), 0, s, x, nb, act_q8k_layout(scratch, m, cols)));
     }
     SK_CUDA(cudaGetLastError());
     return SKAINET_CUDA_OK;
@@ -251,6 +259,18 @@ q8_0_matvec_f32_kernel(const int8_t* __restrict__ codes, const __half* __restric
     if (lane == 0) y[(int64_t) m * rows + row] = acc;
 }
 
+// SKAINET_MATVEC=direct|stream selects the earlier kernel generations (kept for A/B measurements):
+// 0 = default (persistent for single rows), 1 = direct loads, 2 = one-tile streaming kernels.
+int matvec_env_mode() {
+    static const int mode = []() {
+        const char* e = getenv("SKAINET_MATVEC");
+        if (e && strcmp(e, "direct") == 0) return 1;
+        if (e && strcmp(e, "stream") == 0) return 2;
+        return 0;
+    }();
+    return mode;
+}
+
 // ---- dispatch -------------------------------------------------------------------------------------------
 template <int M>
 static void launch_q4k_m(const Weight& w, ActQ8K act, float* y, cudaStream_t s) {
@@ -285,10 +305,17 @@ int32_t launch_matvec(const Weight& w, const float* x, const void* act_scratch, 
         SK_CUDA(cudaGetLastError());
         return SKAINET_CUDA_OK;
     }
+    // SKAINET_MATVEC=direct|stream selects the earlier kernel generations (kept for A/B measurements).
+    static const bool force_direct = matvec_env_mode() == 1;
     for (int m0 = 0; m0 < m;) {
         const int left = m - m0;
         const int mm = left >= 8 ? 8 : (left >= 4 ? 4 : (left >= 2 ? 2 : 1));
         float* yo = y + (int64_t) m0 * w.rows;
+        if (!force_direct) {
+            const int32_t st = launch_matvec_stream(w, act_scratch, m, m0, mm, yo, s);
+            if (st == SKAINET_CUDA_OK) { m0 += mm; continue; }
+            if (st != 1) return st;
+        }
         if (w.enc == SKAINET_ENC_Q4_K) {
             ActQ8K a = act_q8k_layout(const_cast<void*>(act_scratch), m, w.cols);
             a.q += (int64_t) m0 * w.cols; a.d += (int64_t) m0 * (w.cols / 256); a.bsums += (int64_t) m0 * (w.cols / 32);

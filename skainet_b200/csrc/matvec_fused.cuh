@@ -1,0 +1,26 @@
+// Interface of the fused single-row matvec (matvec_fused.cu).
+#pragma once
+#include "common.cuh"
+#include "actquant.cuh"
+
+namespace sk {
+
+// How the activation reaches the kernel.
+enum { PREP_QUANTIZED = 0,   // already quantized in global memory (q8 for K-quants, split for Q8_0)
+       PREP_F32 = 1,         // fp32 row, quantized inside the kernel
+       PREP_NORM_F32 = 2 };  // fp32 row, RMS-normalised with gamma and eps, then quantized
+enum { EPI_STORE = 0, EPI_ADD = 1 };   // y = W x   |   y = resid + W x
+
+struct MatvecIn {
+    const float* x = nullptr;       // PREP_F32 / PREP_NORM_F32
+    const float* gamma = nullptr;   // PREP_NORM_F32
+    float eps = 0.0f;
+    ActQ8K q8 = {nullptr, nullptr, nullptr};       // PREP_QUANTIZED, K-quant weights
+    ActSplit split = {nullptr, nullptr, nullptr};  // PREP_QUANTIZED, Q8_0 weights
+};
+
+// y[rows] (= resid +) W . prep(x). Returns SKAINET_CUDA_OK, an error status, or 1 when the shape is
+// outside what the kernel takes (the caller then uses the general kernels).
+int32_t launch_matvec_fused(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s);
+
+}  // namespace sk

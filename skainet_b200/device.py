@@ -125,6 +125,11 @@ def matmul(w: Weight, x_ptr: int, m: int, y_ptr: int, act_mode: int = L.ACT_NATI
     L.check(L.lib().skainet_cuda_matmul_dev(w.handle, x_ptr, m, y_ptr, act_mode, stream))
 
 
+def matvec_fused(w: Weight, x_ptr: int, gamma_ptr: int, eps: float, resid_ptr: int, y_ptr: int, stream: int = 0) -> None:
+    """y = (resid +) W . quantize(rmsnorm(x) if gamma else x), one launch."""
+    L.check(L.lib().skainet_cuda_matvec_fused_dev(w.handle, x_ptr, gamma_ptr or None, eps, resid_ptr or None, y_ptr, stream))
+
+
 def matmul_host(w: Weight, x: np.ndarray, act_mode: int = L.ACT_NATIVE) -> np.ndarray:
     """Convenience: x [m, cols] (host) -> y [m, rows] (host) through device buffers."""
     x2 = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, w.cols)

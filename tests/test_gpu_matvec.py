@@ -140,3 +140,31 @@ def test_synth_weights_are_valid_and_match_oracle_on_exported_bytes(gpu, oracle)
         x = np.random.default_rng(6).standard_normal(k).astype(np.float32)
         rel_err_ok(gpu.matmul_host(w, x), oracle.matmul(enc, x, packed, k, n, "rm"))
         w.free()
+
+
+@pytest.mark.parametrize("enc,n,k", [("Q4_K", 4096, 4096), ("Q4_K", 333, 11008), ("Q4_K", 37, 28672), ("Q4_K", 5, 256),
+                                     ("Q8_0", 1000, 4096), ("Q8_0", 77, 2304), ("Q8_0", 9, 256)])
+def test_fused_norm_quant_matvec_residual(gpu, oracle, enc, n, k):
+    """One launch = RMSNorm + activation quantization + matvec + residual add, against the same chain
+    built from the reference kernels (f32_fused.c rms norm -> q4k/q8_0 matmul -> add)."""
+    rng = np.random.default_rng(n + k)
+    wf = (0.02 * rng.standard_normal((n, k))).astype(np.float32)
+    packed = oracle.quantize_q4k(wf) if enc == "Q4_K" else oracle.quantize_q8_0(wf)
+    x = (3 * rng.standard_normal(k)).astype(np.float32); gamma = (1 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+    resid = rng.standard_normal(n).astype(np.float32)
+    w = gpu.Weight.upload(packed, enc, n, k)
+    dx, dg, dr, dy = (gpu.DeviceBuffer.from_host(a) for a in (x, gamma, resid, np.zeros(n, np.float32)))
+    use_ref = oracle.ref() is not None
+    xn = oracle.rms_norm(x, gamma, 1e-5, use_ref=use_ref)
+    # norm + residual
+    gpu.matvec_fused(w, dx.ptr, dg.ptr, 1e-5, dr.ptr, dy.ptr)
+    rel_err_ok(dy.download(np.float32, n) - resid, oracle.matmul(enc, xn, packed, k, n, "rm", use_ref=use_ref), 2e-3)
+    # plain (no norm, no residual) and in-place residual
+    gpu.matvec_fused(w, dx.ptr, 0, 0.0, 0, dy.ptr)
+    plain = oracle.matmul(enc, x, packed, k, n, "rm", use_ref=use_ref)
+    rel_err_ok(dy.download(np.float32, n), plain)
+    gpu.matvec_fused(w, dx.ptr, 0, 0.0, dr.ptr, dr.ptr)
+    rel_err_ok(dr.download(np.float32, n) - resid, plain, 2e-3)
+    from skainet_b200 import _lib
+    assert _lib.lib().skainet_cuda_device_status() == 0
+    w.free()
