@@ -73,6 +73,24 @@ SIGNATURES = {
     "skainet_cuda_embed_dev": [i64, vp, i32, vp, vp],
     "skainet_cuda_attn_decode_dev": [vp, vp, vp, vp, i32, i32, i32, i32, i64, vp, i32, f32, i32, vp],
     "skainet_cuda_f32_to_f16_dev": [vp, vp, i64, vp],
+    # include/skainet_cuda_llama.h
+    "skainet_cuda_llama_create": [vp, i64p],
+    "skainet_cuda_llama_free": [i64],
+    "skainet_cuda_llama_set_weight": [i64, i32, i32, i64],
+    "skainet_cuda_llama_set_norm": [i64, i32, i32, f32p],
+    "skainet_cuda_llama_synth": [i64, C.c_uint64, f32],
+    "skainet_cuda_llama_get_weight": [i64, i32, i32, i64p],
+    "skainet_cuda_llama_finalize": [i64],
+    "skainet_cuda_llama_tp_unique_id": [C.POINTER(C.c_uint8)],
+    "skainet_cuda_llama_tp_init": [i64, C.POINTER(C.c_uint8)],
+    "skainet_cuda_llama_reset": [i64],
+    "skainet_cuda_llama_prefill": [i64, i32, i32p, i32, i32p],
+    "skainet_cuda_llama_fake_prefill": [i64, i32, i32, C.c_uint64],
+    "skainet_cuda_llama_decode": [i64, i32, i32p, i32p],
+    "skainet_cuda_llama_generate": [i64, i32, i32p, i32, i32p],
+    "skainet_cuda_llama_logits": [i64, i32, f32p],
+    "skainet_cuda_llama_step_cost": [i64, i32, i64p],
+    "skainet_cuda_llama_stream": [i64, C.POINTER(vp)],
 }
 _RESTYPE = {"skainet_cuda_last_error": C.c_char_p, "skainet_cuda_version": C.c_char_p}
 

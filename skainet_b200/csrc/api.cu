@@ -108,7 +108,7 @@ static int32_t validate_geometry(int enc, int rows, int cols, const char* who) {
 }
 
 // Allocates the planes of a [rows, cols] weight (one allocation, 256-byte aligned planes).
-static int32_t weight_alloc(int enc, int rows, int cols, Weight** out) {
+int32_t weight_alloc(int enc, int rows, int cols, Weight** out) {
     SK_TRY(ensure_device());
     Weight* w = new Weight();
     w->enc = enc; w->rows = rows; w->cols = cols; w->bpr = cols / block_elems(enc);
@@ -136,7 +136,9 @@ static int32_t weight_alloc(int enc, int rows, int cols, Weight** out) {
     return SKAINET_CUDA_OK;
 }
 
-static void weight_release(Weight* w) {
+skainet_weight_t weight_to_handle(Weight* w) { return (skainet_weight_t) reinterpret_cast<intptr_t>(w); }
+
+void weight_release(Weight* w) {
     { std::lock_guard<std::mutex> lk(g_mu); g_weights.erase(w); }
     if (w->base) cudaFree(w->base);
     w->magic = 0;
@@ -323,7 +325,7 @@ int32_t skainet_cuda_weight_synth(int32_t enc, int32_t rows, int32_t cols, uint6
     SK_REQUIRE(mode == 0 || mode == 1, "weight_synth: mode %d", mode);
     Weight* w = nullptr;
     SK_TRY(weight_alloc(enc, rows, cols, &w));
-    int32_t st = launch_synth(*w, seed, std, mode, nullptr);
+    int32_t st = launch_synth(*w, seed, std, mode, 0, 0, cols, nullptr);
     if (st == SKAINET_CUDA_OK) {
         cudaError_t e = cudaStreamSynchronize(nullptr);
         if (e != cudaSuccess) st = cuda_fail(e, "weight_synth", __FILE__, __LINE__);

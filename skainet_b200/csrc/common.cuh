@@ -87,7 +87,15 @@ int32_t launch_split_planes(const uint8_t* canon_dev, Weight& w, int order, cuda
 int32_t launch_join_planes(const Weight& w, uint8_t* canon_dev, cudaStream_t s);
 int32_t launch_dequant_weight(const Weight& w, float* out, cudaStream_t s);
 int32_t launch_dequant_canonical(int enc, const uint8_t* canon_dev, int64_t nblocks, float* out, cudaStream_t s);
-int32_t launch_synth(Weight& w, uint64_t seed, float std, int mode, cudaStream_t s);
+int32_t launch_synth(Weight& w, uint64_t seed, float std, int mode, int64_t row0, int64_t col0, int64_t full_cols, cudaStream_t s);
+// api.cu: weight records for other translation units
+int32_t weight_alloc(int enc, int rows, int cols, Weight** out);
+void weight_release(Weight* w);
+skainet_weight_t weight_to_handle(Weight* w);
+// attention.cu: causal attention of a block of new queries over an f16 cache (prefill)
+int32_t launch_sdpa_cache(const float* q, const __half* k, const __half* v, float* out, int batch, int heads,
+                          int kv_heads, int seq_q, int seq_kv, int64_t cache_stride, int d, float scale, int window,
+                          const int32_t* q_abs_base, cudaStream_t s);
 int32_t launch_embed(const Weight& w, const int32_t* ids, int n, float* out, cudaStream_t s);
 // matvec.cu
 int matvec_env_mode();

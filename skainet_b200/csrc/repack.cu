@@ -205,7 +205,10 @@ __device__ __forceinline__ float normal_at(uint64_t seed, uint64_t idx) {
 }
 
 // One warp per Q4_K super-block; lane L owns elements 8L..8L+7 (sub-block L/4).
-__global__ void synth_q4k_kernel(uint8_t* qs, uint8_t* hdr, int64_t nblocks, uint64_t seed, float std, int mode) {
+// The value of element (r, c) of the FULL tensor depends only on (seed, r * full_cols + c), so a shard
+// generated with its (row0, col0) offsets holds exactly the corresponding slice of the full tensor.
+__global__ void synth_q4k_kernel(uint8_t* qs, uint8_t* hdr, int64_t nblocks, uint64_t seed, float std, int mode,
+                                 int bpr, int64_t row0, int64_t col0, int64_t full_cols) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = (blockIdx.x * (int64_t) blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t) gridDim.x * blockDim.x) >> 5;
@@ -229,7 +232,7 @@ __global__ void synth_q4k_kernel(uint8_t* qs, uint8_t* hdr, int64_t nblocks, uin
         float lo = 0.0f, hi = 0.0f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            v[i] = std * normal_at(seed, (uint64_t) blk * 256 + lane * 8 + i);
+            v[i] = std * normal_at(seed, (uint64_t) ((row0 + blk / bpr) * full_cols + col0 + (blk % bpr) * 256 + lane * 8 + i));
             lo = fminf(lo, v[i]); hi = fmaxf(hi, v[i]);
         }
         lo = fminf(lo, __shfl_xor_sync(~0u, lo, 1)); lo = fminf(lo, __shfl_xor_sync(~0u, lo, 2));
@@ -284,7 +287,8 @@ __global__ void synth_q4k_kernel(uint8_t* qs, uint8_t* hdr, int64_t nblocks, uin
 }
 
 // One lane per element, one warp per Q8_0 block (rule of Q8_0Quantizer.kt:28-53).
-__global__ void synth_q8_0_kernel(int8_t* codes, __half* scales, int64_t nblocks, uint64_t seed, float std, int mode) {
+__global__ void synth_q8_0_kernel(int8_t* codes, __half* scales, int64_t nblocks, uint64_t seed, float std, int mode,
+                                  int bpr, int64_t row0, int64_t col0, int64_t full_cols) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = (blockIdx.x * (int64_t) blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t) gridDim.x * blockDim.x) >> 5;
@@ -295,7 +299,7 @@ __global__ void synth_q8_0_kernel(int8_t* codes, __half* scales, int64_t nblocks
             if (lane == 0) scales[blk] = __float2half_rn(0.0001f + 0.0003f * (float) ((r >> 8) & 0xFF) / 255.0f);
             continue;
         }
-        const float v = std * normal_at(seed, (uint64_t) blk * 32 + lane);
+        const float v = std * normal_at(seed, (uint64_t) ((row0 + blk / bpr) * full_cols + col0 + (blk % bpr) * 32 + lane));
         const float amax = skd::warp_max(fabsf(v));
         const float d = amax / 127.0f;
         const float id = d != 0.0f ? 1.0f / d : 0.0f;
@@ -306,12 +310,13 @@ __global__ void synth_q8_0_kernel(int8_t* codes, __half* scales, int64_t nblocks
     }
 }
 
-int32_t launch_synth(Weight& w, uint64_t seed, float std, int mode, cudaStream_t s) {
+int32_t launch_synth(Weight& w, uint64_t seed, float std, int mode, int64_t row0, int64_t col0, int64_t full_cols, cudaStream_t s) {
     const int64_t nblocks = (int64_t) w.rows * w.bpr;
     if (nblocks == 0) return SKAINET_CUDA_OK;
     const int grid = (int) std::min<int64_t>((nblocks + 7) / 8, 148 * 16);
-    if (w.enc == SKAINET_ENC_Q4_K) synth_q4k_kernel<<<grid, 256, 0, s>>>(w.qs, w.hdr, nblocks, seed, std, mode);
-    else if (w.enc == SKAINET_ENC_Q8_0) synth_q8_0_kernel<<<grid, 256, 0, s>>>((int8_t*) w.qs, (__half*) w.hdr, nblocks, seed, std, mode);
+    if (full_cols <= 0) full_cols = w.cols;
+    if (w.enc == SKAINET_ENC_Q4_K) synth_q4k_kernel<<<grid, 256, 0, s>>>(w.qs, w.hdr, nblocks, seed, std, mode, w.bpr, row0, col0, full_cols);
+    else if (w.enc == SKAINET_ENC_Q8_0) synth_q8_0_kernel<<<grid, 256, 0, s>>>((int8_t*) w.qs, (__half*) w.hdr, nblocks, seed, std, mode, w.bpr, row0, col0, full_cols);
     else { set_error("weight_synth: encoding %d not supported", w.enc); return SKAINET_CUDA_ERR_INVALID; }
     SK_CUDA(cudaGetLastError());
     return SKAINET_CUDA_OK;
