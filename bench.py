@@ -3,19 +3,28 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
 
-Prints ONE JSON line (rank 0). Workloads:
+Prints ONE JSON line (rank 0). Workloads (all inputs synthetic and seeded):
 
-  q4k_matvec (default) — BASELINE config 2 at M=1: Q4_K dequant-fused matvec over W[11008,4096] and
-      W[4096,11008] (seeded N(0,0.02) weights packed on the device), fp32 activations ~N(0,1).
-      A step is one sweep over 2 x COPIES distinct weights (> 2x L2, so HBM serves every byte).
-      metric = algorithmic HBM GB/s (weight bytes + activation + output per matvec).
+  decode_70b (default) — BASELINE config 5: Llama-style 80 layers, d 8192, FFN 28672, 64 q / 8 kv
+      heads, vocab 128256, all Q4_K, random-init N(0,0.02) packed on the device; greedy decode at
+      batch 1 behind a 4096-token context, tensor-parallel over the N GPUs (strong scaling: the same
+      model and batch at every N). metric = decode tokens/s. A step is one decode step (one token per
+      sequence). The context's K/V are seeded noise, not a real prefill: the reference has no batched
+      GEMM and 4096 prompt rows through matvecs is out of reach for both sides.
+  decode_7b — BASELINE config 4: 32 layers, d 4096, FFN 11008, 32 heads, vocab 32000; Q4_K linears,
+      Q8_0 embedding/output; batch 1 behind a 512-token context.
+  q4k_matvec — BASELINE config 2 at M=1: W[11008,4096] and W[4096,11008]; metric = algorithmic HBM
+      GB/s over a sweep of distinct weights larger than 2x L2.
   q8_0_matvec — BASELINE config 1: Q8_0 W[4096,4096], same protocol.
 
-`value` is timed with the inputs resident in HBM, the sweep captured in one CUDA graph; `e2e` is the
-same sweep driven through the C ABI with HOST activations and outputs (pinned), host<->device copies
-inside the timed region, weights resident (uploaded once at load, as a SKaiNET provider does).
-`--impl reference` times the reference's own C kernels (oracle/_ref, else the port) on the host.
-PyTorch is used here for streams, events, pinned memory and the process group only.
+`value` is timed on the device with everything resident in HBM (decode: one CUDA-graph replay per
+step, tokens fed back on the device). `e2e` is the same metric through the C ABI with HOST buffers
+(decode: one `skainet_cuda_llama_decode` call per step, token ids host -> device and back, host
+synchronisation every step; matvec: activation in, output out per call, weights resident).
+`roofline` is the dequant-fused matvec kernel measured live over the workload's own weights.
+`--impl reference` times the reference's own C kernels (oracle/_ref; the port if absent) on the host:
+for decode a CPU composer built from those kernels, measured on a bounded number of layers and scaled.
+PyTorch is used here for events, pinned memory and the process group only.
 """
 from __future__ import annotations
 
@@ -32,11 +41,13 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-WORKLOADS = {
+MATVEC_WORKLOADS = {
     # name: (encoding, [(rows=out, cols=in), ...], block bytes, block elems)
     "q4k_matvec": ("Q4_K", [(11008, 4096), (4096, 11008)], 144, 256),
     "q8_0_matvec": ("Q8_0", [(4096, 4096)], 34, 32),
 }
+DECODE_WORKLOADS = {"decode_70b": ("70b", 4096), "decode_7b": ("7b", 512)}
+BLOCK = {"Q4_K": (144, 256), "Q8_0": (34, 32)}
 
 
 def algorithmic_bytes(enc_bytes: int, enc_elems: int, rows: int, cols: int, m: int = 1) -> int:
@@ -76,207 +87,376 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
         self.proc.terminate()
-        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        ok = [r for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        sm = [float(r[0]) for r in ok]
+        mx = [float(r[1]) for r in ok if r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i].lower().startswith("active")})
+        reasons = sorted({names[i] for r in ok for i in range(4) if r[2 + i].lower().startswith("active")})
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
                 "samples": len(sm)}
 
 
 def dist_env():
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    return rank, world, local
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+
+
+def model_config(name: str, **kw):
+    from skainet_b200.llama import LlamaConfig
+    return LlamaConfig.llama70b(**kw) if name == "70b" else LlamaConfig.llama7b(**kw)
 
 
 # ---------------------------------------------------------------------------------------------------
-# reference arm / CPU baseline: the reference's own C kernels on the host cores
+# CPU side: the reference's own C kernels on the host cores
 # ---------------------------------------------------------------------------------------------------
-def cpu_matvec_rate(workload: str, seconds: float, rng_seed: int = 5) -> dict:
-    """Times the reference's compiled C matvec (oracle/_ref; the port if it is absent) on this host for
-    about `seconds`, on the workload's shapes with one weight per shape. Returns GB/s of algorithmic bytes."""
+def random_blocks(rng, enc: str, rows: int, cols: int) -> np.ndarray:
+    """Random valid packed blocks (random codes/scales, sane f16 fields), the reference's microbench fixture style."""
+    bb, be = BLOCK[enc]
+    packed = rng.integers(0, 256, size=rows * (cols // be) * bb, dtype=np.uint8)
+    blk = packed.reshape(-1, bb)
+    blk[:, 0:2] = np.array([0.002], np.float16).view(np.uint8)
+    if enc == "Q4_K":
+        blk[:, 2:4] = np.array([0.002], np.float16).view(np.uint8)
+    return packed
+
+
+def cpu_matvec_rate(workload: str, seconds: float) -> dict:
     from oracle import ref as R
-    enc, shapes, bb, be = WORKLOADS[workload]
+    enc, shapes, bb, be = MATVEC_WORKLOADS[workload]
     use_ref = R.ref() is not None
-    rng = np.random.default_rng(rng_seed)
-    items = []
-    for rows, cols in shapes:
-        packed = rng.integers(0, 256, size=rows * (cols // be) * bb, dtype=np.uint8)
-        blk = packed.reshape(-1, bb)
-        blk[:, 0:2] = np.array([0.01], np.float16).view(np.uint8)       # sane f16 scale fields
-        if enc == "Q4_K":
-            blk[:, 2:4] = np.array([0.01], np.float16).view(np.uint8)
-        items.append((rows, cols, packed, rng.standard_normal(cols).astype(np.float32)))
-    for rows, cols, packed, x in items:                                     # warm-up (spins the row pool up)
-        R.matmul(enc, x, packed, cols, rows, "rm", use_ref=use_ref)
+    rng = np.random.default_rng(5)
+    items = [(r, c, random_blocks(rng, enc, r, c), rng.standard_normal(c).astype(np.float32)) for r, c in shapes]
+    for r, c, packed, x in items:
+        R.matmul(enc, x, packed, c, r, "rm", use_ref=use_ref)
     t0 = time.perf_counter(); done = 0; calls = 0
     while time.perf_counter() - t0 < seconds:
-        for rows, cols, packed, x in items:
-            R.matmul(enc, x, packed, cols, rows, "rm", use_ref=use_ref)
-            done += algorithmic_bytes(bb, be, rows, cols); calls += 1
+        for r, c, packed, x in items:
+            R.matmul(enc, x, packed, c, r, "rm", use_ref=use_ref)
+            done += algorithmic_bytes(bb, be, r, c); calls += 1
     dt = time.perf_counter() - t0
+    fn = "skainet_%s_matmul_rm" % ("q4k" if enc == "Q4_K" else "q8_0")
     return {"value": done / dt / 1e9, "unit": "GB/s", "cores": 4 if use_ref else 1, "kind": "reference" if use_ref else "port",
-            "sample": f"{calls} matvec calls over the workload's {len(items)} shapes in {dt:.1f} s, "
-                      f"{'skainet_%s_matmul_rm (reference C, its 4-thread row pool)' % ('q4k' if enc == 'Q4_K' else 'q8_0') if use_ref else 'oracle port, scalar'}"
-                      f" of {os.cpu_count()} host cores", "calls": calls, "seconds": dt}
+            "sample": f"{calls} calls of {fn if use_ref else 'the oracle port'} over the workload's {len(items)} shapes in {dt:.1f} s "
+                      f"({'its 4-thread row pool' if use_ref else 'scalar'}; host has {os.cpu_count()} cores)", "seconds": dt}
+
+
+def cpu_decode_rate(model: str, ctx: int, budget_s: float) -> dict:
+    """tokens/s of a decoder composed from the reference's C kernels: one layer (random valid packed
+    weights of the model's shapes, context of `ctx` cached keys) and the output head are timed, the layer
+    time is multiplied by the layer count. Activation quantization, RMSNorm, SDPA, SiLU, mul, add as the
+    reference computes them; 4 threads (the library's own cap)."""
+    from oracle import ref as R
+    cfg = model_config(model)
+    use_ref = R.ref() is not None
+    rng = np.random.default_rng(7)
+    D, H, HK, d, F = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads, cfg.d_model, cfg.ffn_dim
+    le, te = cfg.linear_enc, cfg.table_enc
+    W = {"q": (H * D, d), "k": (HK * D, d), "v": (HK * D, d), "o": (d, H * D), "gate": (F, d), "up": (F, d), "down": (d, F)}
+    packed = {k: random_blocks(rng, le, r, c) for k, (r, c) in W.items()}
+    vocab_sample = min(cfg.vocab, 16000)          # the head is timed on a slice of its rows and scaled
+    head = random_blocks(rng, te, vocab_sample, d)
+    K = rng.standard_normal((1, HK, ctx + 1, D)).astype(np.float16).astype(np.float32)
+    V = rng.standard_normal((1, HK, ctx + 1, D)).astype(np.float16).astype(np.float32)
+    x = rng.standard_normal(d).astype(np.float32)
+    ones = np.ones(d, np.float32)
+
+    def mm(name, v):
+        r, c = W[name]
+        return R.matmul(le, v, packed[name], c, r, "rm", use_ref=use_ref)
+
+    def layer(x):
+        xn = R.rms_norm(x, ones, cfg.rms_eps, use_ref=use_ref)
+        q = R.rope(mm("q", xn).reshape(H, D), H, D, ctx); k = R.rope(mm("k", xn).reshape(HK, D), HK, D, ctx); v = mm("v", xn)
+        K[0, :, ctx] = R.round_f16(k); V[0, :, ctx] = R.round_f16(v.reshape(HK, D))
+        a = R.sdpa(q.reshape(1, H, 1, D), K, V, 1.0 / np.sqrt(D), causal=True, use_ref=use_ref).reshape(-1)
+        x = x + mm("o", a)
+        xn = R.rms_norm(x, ones, cfg.rms_eps, use_ref=use_ref)
+        return x + mm("down", R.swiglu(mm("gate", xn), mm("up", xn)))
+
+    layer(x)                                        # warm-up
+    t0 = time.perf_counter(); n_layer = 0
+    while n_layer < 1 or time.perf_counter() - t0 < budget_s * 0.8:
+        x = layer(x); x /= max(1.0, float(np.abs(x).max())); n_layer += 1
+    t_layer = (time.perf_counter() - t0) / n_layer
+    t0 = time.perf_counter(); n_head = 0
+    while n_head < 1 or time.perf_counter() - t0 < budget_s * 0.2:
+        R.matmul(te, R.rms_norm(x, ones, cfg.rms_eps, use_ref=use_ref), head, d, vocab_sample, "rm", use_ref=use_ref); n_head += 1
+    t_head = (time.perf_counter() - t0) / n_head * (cfg.vocab / vocab_sample)
+    t_tok = t_layer * cfg.n_layers + t_head
+    return {"value": 1.0 / t_tok, "unit": "tokens/s", "cores": 4 if use_ref else 1, "kind": "reference" if use_ref else "port",
+            "sample": f"{n_layer} decoder layer(s) and {n_head} output-head pass(es) on {vocab_sample} of {cfg.vocab} rows, composed from "
+                      f"{'the reference C kernels (4-thread row pool)' if use_ref else 'the oracle port (scalar)'}; per-layer {t_layer * 1e3:.1f} ms x "
+                      f"{cfg.n_layers} layers + head {t_head * 1e3:.1f} ms, extrapolated; host has {os.cpu_count()} cores",
+            "seconds": t_tok}
 
 
 def run_reference(args) -> None:
-    rank, world, _ = dist_env()
+    rank, _, _ = dist_env()
     if rank != 0:
         return
-    enc, shapes, bb, be = WORKLOADS[args.workload]
-    per_step = max(1.0, min(20.0, 60.0 / max(1, args.steps + args.warmup)))
-    cpu_matvec_rate(args.workload, 0.5)
-    times, vals = [], []
+    budget = max(2.0, min(20.0, 90.0 / max(1, args.steps + args.warmup)))
+    vals, times = [], []
     for i in range(args.warmup + args.steps):
-        r = cpu_matvec_rate(args.workload, per_step)
+        if args.workload in MATVEC_WORKLOADS:
+            r = cpu_matvec_rate(args.workload, budget); unit = "GB/s"; metric = f"{args.workload}_hbm_gbs"
+        else:
+            model, ctx = DECODE_WORKLOADS[args.workload]
+            r = cpu_decode_rate(model, ctx, budget); unit = "tokens/s"; metric = "decode_tokens_per_s"
         if i >= args.warmup:
-            times.append(r["seconds"] * 1e3); vals.append(r["value"])
-    r["value"] = float(np.mean(vals))
-    line = {"impl": "reference", "metric": f"{args.workload}_hbm_gbs", "value": r["value"], "unit": "GB/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(np.mean(times)), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int4 -> int32, f32 accumulate" if enc == "Q4_K" else "f32",
-            "data": "synthetic", "config": workload_config(args.workload, 1),
-            "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
-            "e2e": {"value": r["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+            vals.append(r["value"]); times.append(r["seconds"] * 1e3)
+    v = float(np.mean(vals))
+    line = {"impl": "reference", "metric": metric, "value": v, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": float(np.mean(times)), "higher_is_better": True,
+            "scaling": "weak" if args.workload in MATVEC_WORKLOADS else "strong", "vs_baseline": None, "dtype": dtype_of(args.workload),
+            "data": "synthetic", "config": workload_config(args, 1),
+            "cpu_baseline": {"value": v, "unit": unit, "cores": r["cores"], "kind": r["kind"], "sample": r["sample"]},
+            "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 
-def workload_config(workload: str, copies: int) -> dict:
-    enc, shapes, bb, be = WORKLOADS[workload]
-    return {"workload": workload, "encoding": enc, "shapes_out_in": shapes, "m": 1, "weights_per_shape": copies,
-            "l2": "rotating distinct weights larger than 2x L2 per sweep", "activation": "fp32 N(0,1)",
-            "weights": "N(0,0.02) packed on device, seeded"}
+def dtype_of(workload: str) -> str:
+    if workload == "q8_0_matvec":
+        return "int8 x int8 (two-term activation) -> int32, f32 accumulate"
+    return "int8 x int4 -> int32, f32 accumulate (attention and norms f32, KV f16)" if workload in DECODE_WORKLOADS \
+        else "int8 x int4 -> int32, f32 accumulate"
+
+
+def workload_config(args, world: int, extra: dict | None = None) -> dict:
+    if args.workload in MATVEC_WORKLOADS:
+        enc, shapes, _, _ = MATVEC_WORKLOADS[args.workload]
+        c = {"workload": args.workload, "encoding": enc, "shapes_out_in": shapes, "m": 1,
+             "l2": "rotating distinct weights larger than 2x L2 per sweep", "activation": "fp32 N(0,1)",
+             "weights": "N(0,0.02) packed on device, seeded"}
+    else:
+        model, ctx = DECODE_WORKLOADS[args.workload]
+        cfg = model_config(model)
+        c = {"workload": args.workload, "layers": cfg.n_layers, "d_model": cfg.d_model, "ffn": cfg.ffn_dim, "heads": cfg.n_heads,
+             "kv_heads": cfg.n_kv_heads, "vocab": cfg.vocab, "linear": cfg.linear_enc, "tables": cfg.table_enc, "batch": args.batch,
+             "context": ctx, "context_fill": "seeded noise K/V (no prompt pass)", "parallelism": f"tp{world}",
+             "l2": "weights per step far larger than L2", "weights": "N(0,0.02) packed on device, seeded"}
+    if extra:
+        c.update(extra)
+    return c
 
 
 # ---------------------------------------------------------------------------------------------------
-# our arm
+# our arm: matvec sweep
 # ---------------------------------------------------------------------------------------------------
-def run_ours(args) -> None:
-    import torch
-    import torch.distributed as dist
-    from skainet_b200 import _lib as L, device
-
-    rank, world, local = dist_env()
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    torch.cuda.set_device(local)
-    device.set_device(local)
-    info = device.device_info()
-    enc, shapes, bb, be = WORKLOADS[args.workload]
-    per_sweep_one_copy = sum(algorithmic_bytes(bb, be, r, c) for r, c in shapes)
-    copies = max(2, int(np.ceil(2.2 * info["l2_bytes"] / min(r * (c // be) * bb for r, c in shapes))))
-    weights = [[device.Weight.synth(enc, r, c, seed=1000 * rank + 10 * si + ci, std=0.02) for ci in range(copies)]
-               for si, (r, c) in enumerate(shapes)]
-    stream = torch.cuda.Stream()
+def matvec_sweep_rate(torch, device, L, weights_flat, stream, steps: int, warmup: int):
+    """Times `steps` sweeps of one fused-path matvec per weight (fp32 activation in HBM), one CUDA graph
+    per sweep, on `stream`. Returns (ms per sweep, launches per sweep)."""
+    xs, ys = {}, {}
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    for w in weights_flat:
+        if w.cols not in xs:
+            xs[w.cols] = torch.randn(w.cols, device="cuda", generator=gen, dtype=torch.float32)
+        if w.rows not in ys:
+            ys[w.rows] = torch.empty(w.rows, device="cuda", dtype=torch.float32)
     sp = stream.cuda_stream
-    gen = torch.Generator(device="cuda").manual_seed(5 + rank)
-    xs = [torch.randn(c, device="cuda", generator=gen, dtype=torch.float32) for _, c in shapes]
-    ys = [torch.empty(r, device="cuda", dtype=torch.float32) for r, _ in shapes]
-    launches_per_step = 0
 
     def sweep():
-        n = 0
-        for ci in range(copies):
-            for si in range(len(shapes)):
-                device.matmul(weights[si][ci], xs[si].data_ptr(), 1, ys[si].data_ptr(), L.ACT_NATIVE, sp)
-                n += 2          # activation quantizer + matvec
-        return n
+        for w in weights_flat:
+            device.matmul(w, xs[w.cols].data_ptr(), 1, ys[w.rows].data_ptr(), L.ACT_NATIVE, sp)
 
     with torch.cuda.stream(stream):
-        launches_per_step = sweep()          # allocates scratch outside capture
-        stream.synchronize()
+        sweep(); stream.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             sweep()
-    bytes_per_step = per_sweep_one_copy * copies
+        for _ in range(max(3, warmup)):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        stream.synchronize()
+        e0.record(stream)
+        for _ in range(steps):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+    return e0.elapsed_time(e1) / steps, 2 * len(weights_flat), graph, (xs, ys)
+
+
+def run_matvec(args) -> None:
+    import torch
+    import torch.distributed as dist
+    from skainet_b200 import _lib as L, device
+    rank, world, local = dist_env()
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local); device.set_device(local)
+    info = device.device_info()
+    enc, shapes, bb, be = MATVEC_WORKLOADS[args.workload]
+    copies = max(2, int(np.ceil(2.2 * info["l2_bytes"] / min(r * (c // be) * bb for r, c in shapes))))
+    weights = [device.Weight.synth(enc, r, c, seed=1000 * rank + 10 * si + ci, std=0.02) for ci in range(copies) for si, (r, c) in enumerate(shapes)]
+    bytes_per_step = sum(algorithmic_bytes(bb, be, w.rows, w.cols) for w in weights)
+    stream = torch.cuda.Stream()
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-resident timing -------------------------------------------------------------------------
-    for _ in range(max(3, args.warmup)):
-        with torch.cuda.stream(stream):
-            graph.replay()
     sampler = ClockSampler(local)
     barrier()
     if rank == 0:
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        e0.record(stream)
-        for _ in range(args.steps):
-            graph.replay()
-        e1.record(stream)
+    ms_step, launches, graph, bufs = matvec_sweep_rate(torch, device, L, weights, stream, args.steps, args.warmup)
     barrier()
-    ms = e0.elapsed_time(e1)
-    # keep the GPU busy long enough for the clock sampler to see it under load
-    if rank == 0 and not args.skip_cpu:
+    if rank == 0 and not args.skip_cpu:      # keep the GPU under load long enough for the clock sampler
         t_end = time.time() + 1.0
         with torch.cuda.stream(stream):
             while time.time() < t_end:
                 graph.replay(); stream.synchronize()
     clocks = sampler.stop() if rank == 0 else None
 
-    # ---- end to end through the C ABI with host activations/outputs ----------------------------------
-    hx = [torch.randn(c, dtype=torch.float32).pin_memory() for _, c in shapes]
-    hy = [torch.empty(r, dtype=torch.float32).pin_memory() for r, _ in shapes]
-    lib = L.lib()
+    # end to end: host activation in, host output out, per matvec
+    xs, ys = bufs
+    hx = {c: torch.randn(c, dtype=torch.float32).pin_memory() for c in xs}
+    hy = {r: torch.empty(r, dtype=torch.float32).pin_memory() for r in ys}
+    lib = L.lib(); sp = stream.cuda_stream
 
     def e2e_sweep():
-        for ci in range(copies):
-            for si in range(len(shapes)):
-                L.check(lib.skainet_cuda_memcpy_h2d(xs[si].data_ptr(), hx[si].data_ptr(), hx[si].numel() * 4, sp))
-                device.matmul(weights[si][ci], xs[si].data_ptr(), 1, ys[si].data_ptr(), L.ACT_NATIVE, sp)
-                L.check(lib.skainet_cuda_memcpy_d2h(hy[si].data_ptr(), ys[si].data_ptr(), hy[si].numel() * 4, sp))  # syncs
+        for w in weights:
+            L.check(lib.skainet_cuda_memcpy_h2d(xs[w.cols].data_ptr(), hx[w.cols].data_ptr(), w.cols * 4, sp))
+            device.matmul(w, xs[w.cols].data_ptr(), 1, ys[w.rows].data_ptr(), L.ACT_NATIVE, sp)
+            L.check(lib.skainet_cuda_memcpy_d2h(hy[w.rows].data_ptr(), ys[w.rows].data_ptr(), w.rows * 4, sp))   # synchronises
 
     e2e_steps = 0 if args.skip_e2e else max(1, min(args.steps, 5))
-    for _ in range(0 if args.skip_e2e else 2):
-        e2e_sweep()
-    barrier()
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record(stream)
-    for _ in range(e2e_steps):
-        e2e_sweep()
-    e3.record(stream)
-    barrier()
-    e2e_ms = e2.elapsed_time(e3)
-
-    t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+    e2e_ms = 0.0
+    if e2e_steps:
+        e2e_sweep(); barrier()
+        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2.record(stream)
+        for _ in range(e2e_steps):
+            e2e_sweep()
+        e3.record(stream); barrier()
+        e2e_ms = e2.elapsed_time(e3)
+    t = torch.tensor([ms_step, e2e_ms], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = float(t[0]), float(t[1])
-
+    ms_step, e2e_ms = float(t[0]), float(t[1])
     if rank == 0:
         peak, peak_kind = load_peaks()
-        value = bytes_per_step * world * args.steps / (ms * 1e-3) / 1e9
-        nmat = copies * len(shapes)
-        per_launch_us = ms * 1e3 / (args.steps * nmat)
-        achieved = (bytes_per_step / nmat) / (per_launch_us * 1e-6) / 1e9
-        cpu = cpu_matvec_rate(args.workload, 10.0) if (world == 1 and not args.skip_cpu) else None
+        per_launch_us = ms_step * 1e3 / len(weights)
+        achieved = bytes_per_step / (ms_step * 1e-3) / 1e9
         line = {
-            "metric": f"{args.workload}_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "int8 x int4 -> int32, f32 accumulate" if enc == "Q4_K" else "int8 x int8 (2-term) -> int32, f32 accumulate",
-            "data": "synthetic", "config": workload_config(args.workload, copies),
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_kind": peak_kind, "kernel": "q4k_matvec_kernel<1>" if enc == "Q4_K" else "q8_0_matvec_kernel<1>",
+            "metric": f"{args.workload}_hbm_gbs", "value": achieved * world, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": dtype_of(args.workload), "data": "synthetic", "config": workload_config(args, world, {"weights_per_shape": copies}),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "peak_kind": peak_kind, "kernel": "q4k_matvec_fused_kernel" if enc == "Q4_K" else "q8_0_matvec_fused_kernel",
                          "avg_launch_us": per_launch_us,
-                         "note": "avg launch = timed region / matvec launches (activation quantizer and launch gaps included)"},
+                         "note": "avg launch = timed region / matvec launches; the activation quantizer and launch gaps are inside it"},
             "e2e": {"value": (bytes_per_step * world * e2e_steps / (e2e_ms * 1e-3) / 1e9) if e2e_steps else None, "unit": "GB/s",
-                    "h2d_bytes_per_step": int(sum(4 * c for _, c in shapes) * copies),
-                    "d2h_bytes_per_step": int(sum(4 * r for r, _ in shapes) * copies),
-                    "note": "weights resident; each matvec copies its activation in and its output out"},
-            "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+                    "h2d_bytes_per_step": int(sum(4 * w.cols for w in weights)), "d2h_bytes_per_step": int(sum(4 * w.rows for w in weights)),
+                    "note": "weights resident; each matvec copies its activation in and its output out and synchronises"},
+            "gpu_launches": launches * args.steps, "clocks": clocks,
         }
-        if cpu is not None:
+        if world == 1 and not args.skip_cpu:
+            cpu = cpu_matvec_rate(args.workload, 10.0)
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------------
+# our arm: decode
+# ---------------------------------------------------------------------------------------------------
+def run_decode(args) -> None:
+    import torch
+    import torch.distributed as dist
+    from skainet_b200 import _lib as L, device
+    from skainet_b200.llama import Llama, W_HEAD, W_O, W_DOWN, W_QKV, W_GATE_UP
+    rank, world, local = dist_env()
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local); device.set_device(local)
+    model_name, ctx = DECODE_WORKLOADS[args.workload]
+    batch = args.batch
+    cfg = model_config(model_name, max_seq=ctx + 2048, max_batch=batch, tp_rank=rank, tp_world=world)
+    m = Llama(cfg)
+    m.synth(seed=100, std=0.02)
+    m.finalize()
+    if world > 1:
+        ids = [Llama.tp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        m.tp_init(ids[0])
+    for b in range(batch):
+        m.fake_prefill(ctx, seq=b, seed=7 + b)
+    first = np.arange(1, batch + 1, dtype=np.int32) * 17 % cfg.vocab
+    mstream = torch.cuda.ExternalStream(m.stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    warm = max(3, args.warmup)
+    m.generate(first, warm)
+    bytes_step, launches_step = m.step_cost(batch)
+    sampler = ClockSampler(local)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(mstream)
+    toks = m.generate(first, args.steps)                 # K graph replays, synchronises at the end
+    e1.record(mstream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if rank == 0 and ms < 1500 and not args.skip_cpu:    # keep the GPU loaded long enough for the clock sampler
+        m.generate(first, min(1024, int(1500 / max(ms / args.steps, 1e-3))))
+    clocks = sampler.stop() if rank == 0 else None
+
+    # end to end: one C-ABI call per step, token ids from pinned host memory and back
+    e2e_steps = 0 if args.skip_e2e else max(1, min(args.steps, 64))
+    e2e_ms = 0.0
+    if e2e_steps:
+        tin = torch.from_numpy(first.copy()).pin_memory(); tout = torch.zeros(batch, dtype=torch.int32).pin_memory()
+        for _ in range(2):
+            m.decode_ptr(batch, tin.data_ptr(), tout.data_ptr()); tin.copy_(tout)
+        barrier()
+        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2.record(mstream)
+        for _ in range(e2e_steps):
+            m.decode_ptr(batch, tin.data_ptr(), tout.data_ptr()); tin.copy_(tout)
+        e3.record(mstream); barrier()
+        e2e_ms = e2.elapsed_time(e3)
+
+    # the matvec kernel alone over this rank's own weights (every layer's four linears + the head)
+    ws = []
+    for l in range(cfg.n_layers):
+        ws += [m.weight(l, W_QKV), m.weight(l, W_O), m.weight(l, W_GATE_UP), m.weight(l, W_DOWN)]
+    ws.append(m.weight(0, W_HEAD))
+    mv_bytes = sum(algorithmic_bytes(*BLOCK[w.encoding], w.rows, w.cols) for w in ws)
+    stream = torch.cuda.Stream()
+    mv_ms, _, _, _ = matvec_sweep_rate(torch, device, L, ws, stream, max(2, min(args.steps, 10)), 3)
+
+    t = torch.tensor([ms, e2e_ms, mv_ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms, mv_ms = float(t[0]), float(t[1]), float(t[2])
+    if rank == 0:
+        peak, peak_kind = load_peaks()
+        achieved = mv_bytes / (mv_ms * 1e-3) / 1e9
+        step_gbs = bytes_step / (ms / args.steps * 1e-3) / 1e9
+        line = {
+            "metric": "decode_tokens_per_s", "value": batch * args.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": dtype_of(args.workload), "data": "synthetic", "config": workload_config(args, world),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "peak_kind": peak_kind, "kernel": "q4k_matvec_fused_kernel", "avg_launch_us": mv_ms * 1e3 / len(ws),
+                         "note": "per GPU: the fused matvec path (quantizer + matvec) swept over this rank's own weights, bytes / time",
+                         "step_bytes_per_gpu": bytes_step, "step_gbs_per_gpu": step_gbs, "step_frac": step_gbs / peak},
+            "e2e": {"value": (batch * e2e_steps / (e2e_ms * 1e-3)) if e2e_steps else None, "unit": "tokens/s",
+                    "h2d_bytes_per_step": 4 * batch, "d2h_bytes_per_step": 4 * batch,
+                    "note": "one skainet_cuda_llama_decode call per step: pinned host token ids in, arg-max ids out, host sync each step"},
+            "gpu_launches": launches_step * args.steps, "clocks": clocks, "tokens_head": [int(x) for x in toks[:4, 0]],
+        }
+        if world == 1 and not args.skip_cpu:
+            cpu = cpu_decode_rate(model_name, ctx, 20.0)
+            line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+    m.free()
     if world > 1:
         dist.destroy_process_group()
 
@@ -284,17 +464,20 @@ def run_ours(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="q4k_matvec", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="decode_70b", choices=sorted(MATVEC_WORKLOADS) + sorted(DECODE_WORKLOADS))
+    ap.add_argument("--batch", type=int, default=1, help="sequences decoded together (decode workloads)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-cpu", action="store_true", help="omit the cpu_baseline leg (profiling runs)")
     ap.add_argument("--skip-e2e", action="store_true", help="omit the end-to-end leg (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload in MATVEC_WORKLOADS:
+        run_matvec(args)
     else:
-        run_ours(args)
+        run_decode(args)
 
 
 if __name__ == "__main__":

@@ -52,6 +52,9 @@ typedef struct {
 #define SKAINET_W_GATE      9   /* [ffn_dim, d_model]                 rows sharded                    */
 #define SKAINET_W_UP        10
 #define SKAINET_W_DOWN      11  /* [d_model, ffn_dim]                 columns sharded                 */
+/* read-only, after finalize (the parts they were merged from are released then): */
+#define SKAINET_W_QKV       12  /* rows of q, k, v in one tensor                                      */
+#define SKAINET_W_GATE_UP   13  /* rows of gate then up in one tensor                                 */
 
 SKAINET_CUDA_API int32_t skainet_cuda_llama_create(const skainet_llama_config* cfg, skainet_model_t* out);
 SKAINET_CUDA_API int32_t skainet_cuda_llama_free(skainet_model_t m);
@@ -96,6 +99,9 @@ SKAINET_CUDA_API int32_t skainet_cuda_llama_logits(skainet_model_t m, int32_t ba
 /* Bytes one decode step must read from HBM at the current positions (weights once + KV visible),
  * and the number of kernels one step launches: the roofline inputs of the bench. out2 = {bytes, launches}. */
 SKAINET_CUDA_API int32_t skainet_cuda_llama_step_cost(skainet_model_t m, int32_t batch, int64_t* out2);
+/* Diagnostic: the first n floats of an activation buffer as the last step left it
+ * (0 residual stream, 1 merged q|k|v with q rotated, 2 attention output, 3 gate|up, 4 q). */
+SKAINET_CUDA_API int32_t skainet_cuda_llama_peek(skainet_model_t m, int32_t which, float* host_out, int64_t n);
 /* The stream the model runs on (for event timing by the caller). */
 SKAINET_CUDA_API int32_t skainet_cuda_llama_stream(skainet_model_t m, skainet_stream_t* out);
 

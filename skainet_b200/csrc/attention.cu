@@ -228,7 +228,7 @@ __global__ void __launch_bounds__(128)
 sdpa_rows_kernel(const float* __restrict__ q, const KV* __restrict__ k, const KV* __restrict__ v, float* __restrict__ out,
                  int heads, int kv_heads, int seq_q, int seq_kv, int64_t kv_stride, float scale, int causal, int window,
                  int right_context, const int32_t* __restrict__ lengths, const int32_t* __restrict__ q_abs_base,
-                 const float* __restrict__ mask, int mb, int mh, int mq, int mk) {
+                 const float* __restrict__ mask, int mb, int mh, int mq, int mk, int token_major) {
     constexpr int D = E * 32;
     __shared__ float sm_m[4], sm_l[4], sm_acc[4][D];
     const int64_t row = blockIdx.x;
@@ -237,6 +237,8 @@ sdpa_rows_kernel(const float* __restrict__ q, const KV* __restrict__ k, const KV
     const int b = (int) (row / ((int64_t) seq_q * heads));
     const int kvh = h / (heads / kv_heads);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // q/out are [batch, heads, seq_q, D] (the reference contract) or, token-major, [batch, seq_q, heads, D]
+    const int64_t qrow = token_major ? ((int64_t) b * seq_q + qi) * heads + h : row;
 
     // key range under the structural rules
     const int abs_q = q_abs_base ? q_abs_base[b] + qi : seq_kv - seq_q + qi;
@@ -256,7 +258,7 @@ sdpa_rows_kernel(const float* __restrict__ q, const KV* __restrict__ k, const KV
     }
     float qr[E];
 #pragma unroll
-    for (int e = 0; e < E; ++e) qr[e] = q[row * D + lane + 32 * e];
+    for (int e = 0; e < E; ++e) qr[e] = q[qrow * D + lane + 32 * e];
     const KV* kb = k + ((int64_t) b * kv_heads + kvh) * kv_stride * D;
     const KV* vb = v + ((int64_t) b * kv_heads + kvh) * kv_stride * D;
 
@@ -288,7 +290,7 @@ sdpa_rows_kernel(const float* __restrict__ q, const KV* __restrict__ k, const KV
         for (int w = 1; w < 4; ++w) mx = fmaxf(mx, sm_m[w]);
         float lt = 0.0f, at = 0.0f;
         for (int w = 0; w < 4; ++w) { const float c = expf(sm_m[w] - mx); lt += c * sm_l[w]; at += c * sm_acc[w][dd]; }
-        out[row * D + dd] = lt > 0.0f ? at / lt : 0.0f;
+        out[qrow * D + dd] = lt > 0.0f ? at / lt : 0.0f;
     }
 }
 
@@ -296,11 +298,11 @@ template <typename KV>
 static int32_t launch_sdpa_t(const float* q, const KV* k, const KV* v, float* out, int batch, int heads, int kv_heads,
                              int seq_q, int seq_kv, int64_t kv_stride, int d, float scale, int causal, int window,
                              int right_context, const int32_t* lengths, const int32_t* q_abs_base, const float* mask,
-                             int mb, int mh, int mq, int mk, cudaStream_t s) {
+                             int mb, int mh, int mq, int mk, int token_major, cudaStream_t s) {
     const int64_t rows = (int64_t) batch * heads * seq_q;
     if (rows <= 0) return SKAINET_CUDA_OK;
     if (rows > 0x7fffffff) { set_error("sdpa: too many query rows"); return SKAINET_CUDA_ERR_INVALID; }
-#define SK_SD(E) sdpa_rows_kernel<KV, E><<<(unsigned) rows, 128, 0, s>>>(q, k, v, out, heads, kv_heads, seq_q, seq_kv, kv_stride, scale, causal, window, right_context, lengths, q_abs_base, mask, mb, mh, mq, mk)
+#define SK_SD(E) sdpa_rows_kernel<KV, E><<<(unsigned) rows, 128, 0, s>>>(q, k, v, out, heads, kv_heads, seq_q, seq_kv, kv_stride, scale, causal, window, right_context, lengths, q_abs_base, mask, mb, mh, mq, mk, token_major)
     switch (d) {
         case 32: SK_SD(1); break;
         case 64: SK_SD(2); break;
@@ -317,16 +319,17 @@ int32_t launch_sdpa_f32(const float* q, const float* k, const float* v, float* o
                         int seq_q, int seq_kv, int d, float scale, int causal, int window, int right_context,
                         const int32_t* lengths, const float* mask, int mb, int mh, int mq, int mk, cudaStream_t s) {
     return launch_sdpa_t<float>(q, k, v, out, batch, heads, kv_heads, seq_q, seq_kv, seq_kv, d, scale, causal, window,
-                                right_context, lengths, nullptr, mask, mb, mh, mq, mk, s);
+                                right_context, lengths, nullptr, mask, mb, mh, mq, mk, 0, s);
 }
 
 // Causal attention of a block of new queries over an f16 cache (prefill): query qi of batch b sits at
-// absolute position q_abs_base[b] + qi and sees keys [0, that position].
+// absolute position q_abs_base[b] + qi and sees keys [0, that position]. q/out are token-major
+// [batch, seq_q, heads, D], the layout the projections produce.
 int32_t launch_sdpa_cache(const float* q, const __half* k, const __half* v, float* out, int batch, int heads,
                           int kv_heads, int seq_q, int seq_kv, int64_t cache_stride, int d, float scale, int window,
                           const int32_t* q_abs_base, cudaStream_t s) {
     return launch_sdpa_t<__half>(q, k, v, out, batch, heads, kv_heads, seq_q, seq_kv, cache_stride, d, scale, 1, window,
-                                 0, nullptr, q_abs_base, nullptr, 0, 0, 0, 0, s);
+                                 0, nullptr, q_abs_base, nullptr, 0, 0, 0, 0, 1, s);
 }
 
 }  // namespace sk

@@ -591,6 +591,8 @@ static Weight** weight_slot(Model& m, int layer, int which) {
         case SKAINET_W_GATE: return &m.layers[layer].wgate;
         case SKAINET_W_UP: return &m.layers[layer].wup;
         case SKAINET_W_DOWN: return &m.layers[layer].wdown;
+        case SKAINET_W_QKV: return &m.layers[layer].wqkv;
+        case SKAINET_W_GATE_UP: return &m.layers[layer].wgu;
         default: return nullptr;
     }
 }
@@ -603,8 +605,8 @@ int32_t skainet_cuda_llama_set_weight(skainet_model_t h, int32_t layer, int32_t 
     SK_REQUIRE(!m->finalized, "llama_set_weight: model already finalized");
     const bool model_level = which == SKAINET_W_EMBED || which == SKAINET_W_HEAD;
     SK_REQUIRE(model_level || (layer >= 0 && layer < m->cfg.n_layers), "llama_set_weight: layer %d out of range", layer);
-    Weight** slot = weight_slot(*m, model_level ? 0 : layer, which);
-    SK_REQUIRE(slot != nullptr, "llama_set_weight: %d is not a packed tensor", which);
+    Weight** slot = which >= SKAINET_W_QKV ? nullptr : weight_slot(*m, model_level ? 0 : layer, which);
+    SK_REQUIRE(slot != nullptr, "llama_set_weight: %d is not a settable packed tensor", which);
     int rows, cols, enc, fc; int64_t r0, c0;
     shard_shape(*m, which, &rows, &cols, &enc, &r0, &c0, &fc);
     SK_TRY(check_weight_shape(w, enc, rows, cols, "llama_set_weight"));
@@ -679,6 +681,8 @@ int32_t skainet_cuda_llama_finalize(skainet_model_t h) {
         SK_REQUIRE(L.wq && L.wk && L.wv && L.wo && L.wgate && L.wup && L.wdown, "llama_finalize: layer %d is missing a weight", l);
         SK_TRY(concat_rows(L.wq, L.wk, L.wv, &L.wqkv));
         SK_TRY(concat_rows(L.wgate, L.wup, nullptr, &L.wgu));
+        // the merged copies replace the parts
+        for (Weight** w : {&L.wq, &L.wk, &L.wv, &L.wgate, &L.wup}) { weight_release(*w); *w = nullptr; }
     }
     // rotation factors: angle = pos * theta^(-2i/d) in double, rounded once
     const int half = m->cfg.head_dim / 2;
@@ -874,6 +878,18 @@ int32_t skainet_cuda_llama_step_cost(skainet_model_t h, int32_t batch, int64_t* 
     }
     cudaGraphDestroy(g);
     out2[1] = kernels;
+    return SKAINET_CUDA_OK;
+}
+
+int32_t skainet_cuda_llama_peek(skainet_model_t h, int32_t which, float* host_out, int64_t n) {
+    Model* m = model_from_handle(h);
+    if (!m) return SKAINET_CUDA_ERR_HANDLE;
+    SK_REQUIRE(host_out && n >= 0, "llama_peek: bad arguments");
+    SK_TRY(set_device_of(*m));
+    const float* src = which == 0 ? m->x : which == 1 ? m->qkv : which == 2 ? m->attn : which == 3 ? m->gu : which == 4 ? m->q : nullptr;
+    SK_REQUIRE(src != nullptr, "llama_peek: unknown buffer %d", which);
+    SK_CUDA(cudaStreamSynchronize(m->stream));
+    SK_CUDA(cudaMemcpy(host_out, src, sizeof(float) * (size_t) n, cudaMemcpyDeviceToHost));
     return SKAINET_CUDA_OK;
 }
 

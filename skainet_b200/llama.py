@@ -10,7 +10,7 @@ import numpy as np
 from . import _lib as L
 from .device import Weight
 
-W_EMBED, W_HEAD, W_OUT_NORM, W_ATTN_NORM, W_Q, W_K, W_V, W_O, W_FFN_NORM, W_GATE, W_UP, W_DOWN = range(12)
+W_EMBED, W_HEAD, W_OUT_NORM, W_ATTN_NORM, W_Q, W_K, W_V, W_O, W_FFN_NORM, W_GATE, W_UP, W_DOWN, W_QKV, W_GATE_UP = range(14)
 
 
 class _Config(C.Structure):
@@ -86,6 +86,14 @@ class Llama:
         L.check(L.lib().skainet_cuda_weight_export(h.value, out.ctypes.data_as(L.u8p), out.size))
         return out
 
+    def weight(self, layer: int, which: int) -> Weight:
+        """A borrowed view of a tensor the model owns (do not free)."""
+        h = C.c_int64()
+        L.check(L.lib().skainet_cuda_llama_get_weight(self.handle, layer, which, C.byref(h)))
+        w = Weight(h.value)
+        w.free = lambda: None      # borrowed
+        return w
+
     def finalize(self) -> None:
         L.check(L.lib().skainet_cuda_llama_finalize(self.handle))
 
@@ -129,6 +137,12 @@ class Llama:
     def logits(self, batch: int = 1) -> np.ndarray:
         out = np.empty((batch, self.cfg.vocab), dtype=np.float32)
         L.check(L.lib().skainet_cuda_llama_logits(self.handle, batch, out.ctypes.data_as(L.f32p)))
+        return out
+
+    def peek(self, which: int, n: int) -> np.ndarray:
+        """Diagnostic read of an activation buffer (0 x, 1 q|k|v, 2 attention out, 3 gate|up, 4 q)."""
+        out = np.empty(n, dtype=np.float32)
+        L.check(L.lib().skainet_cuda_llama_peek(self.handle, which, out.ctypes.data_as(L.f32p), n))
         return out
 
     def step_cost(self, batch: int = 1) -> tuple[int, int]:
