@@ -32,7 +32,7 @@ def build(gpu, cfg, seed=100, norms=False):
 
 
 def step_err(got, ref):
-    ref = np.asarray(ref, np.float64); got = np.asarray(got, np.float64)
+    ref = np.asarray(ref, np.float64).reshape(-1); got = np.asarray(got, np.float64).reshape(-1)
     return float(np.abs(got - ref).max() / np.sqrt(np.mean(ref * ref)))
 
 
