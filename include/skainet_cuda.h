@@ -220,6 +220,27 @@ SKAINET_CUDA_API int32_t skainet_cuda_embed_dev(skainet_weight_t table, const in
 SKAINET_CUDA_API int32_t skainet_cuda_attn_decode_dev(const float* q, const uint16_t* k_cache, const uint16_t* v_cache,
     float* out, int32_t batch, int32_t heads, int32_t kv_heads, int32_t head_dim, int64_t cache_stride,
     const int32_t* kv_len_dev, int32_t max_kv_len, float scale, int32_t window, skainet_stream_t stream);
+/* The same decode attention for callers that must not allocate. It has no counterpart in the
+ * reference. skainet_cuda_attn_decode_dev keeps its split-K partial results in per-stream scratch that
+ * it grows with cudaMalloc when a larger problem arrives; some hosts cannot have that happen: a decode
+ * loop that runs under a fixed memory plan and asserts zero allocations per step (the reference's own
+ * acceptance harness does, DecodeAcceptanceTest.kt:24-90), a latency-critical thread for which the
+ * device-wide synchronisation inside cudaMalloc is a stall, or a process whose allocator hooks forbid
+ * device allocation after start-up. This entry takes the same arguments and computes the same result
+ * with the same kernels, but its partials live in an array built into the library image: 2^20 floats
+ * (4 MiB) per GPU, held from library load to process exit. It calls no cudaMalloc, cudaFree or other
+ * allocating routine.
+ *   Limit: batch * heads * key_splits * (head_dim + 2) <= 2^20 floats, where key_splits is what the
+ *   launcher picks for (batch, kv_heads, max_kv_len) — at most 256. Larger problems are refused with
+ *   SKAINET_CUDA_ERR_INVALID and a message naming the size; nothing is launched.
+ *   First call on a device: resolves the array's device address (cudaGetSymbolAddress, with that device
+ *   current). Make that first call before any stream capture begins.
+ *   Sharing: every call on a device uses the one array. The kernels overwrite every partial record they
+ *   later read, so nothing has to be cleared between calls; but two calls whose kernels overlap on the
+ *   GPU (different streams, no ordering between them) race on it and both results are undefined. */
+SKAINET_CUDA_API int32_t skainet_cuda_attn_decode_noalloc_dev(const float* q, const uint16_t* k_cache, const uint16_t* v_cache,
+    float* out, int32_t batch, int32_t heads, int32_t kv_heads, int32_t head_dim, int64_t cache_stride,
+    const int32_t* kv_len_dev, int32_t max_kv_len, float scale, int32_t window, skainet_stream_t stream);
 /* fp32 [n] -> binary16 [n], round to nearest even (filling the cache from host-prepared K/V). */
 SKAINET_CUDA_API int32_t skainet_cuda_f32_to_f16_dev(const float* in, uint16_t* out, int64_t n, skainet_stream_t stream);
 

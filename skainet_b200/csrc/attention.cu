@@ -12,6 +12,8 @@
 // skainet-lang/skainet-lang-core/src/commonMain/kotlin/sk/ainet/lang/tensor/ops/AttentionMask.kt:57-78.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace sk {
 
 constexpr float MASKED = -1.0e30f;
@@ -332,4 +334,54 @@ int32_t launch_sdpa_cache(const float* q, const __half* k, const __half* v, floa
                                  0, nullptr, q_abs_base, nullptr, 0, 0, 0, 0, 1, s);
 }
 
+// =================================================================================================
+// Decode attention without any allocation: the split-K partials live in a fixed device array.
+// =================================================================================================
+// Capacity of the built-in partials area, in floats (4 MiB). Every GPU that loads the library holds it
+// until the process exits.
+constexpr size_t ATTN_STATIC_FLOATS = (size_t) 1 << 20;
+static __device__ __align__(256) float g_attn_static_partials[ATTN_STATIC_FLOATS];
+
+// The array's name is only a host-side stand-in; the address kernels may use comes from the runtime,
+// once per device, with that device current.
+static float* g_attn_static_ptr[64] = {nullptr};
+static std::mutex g_attn_static_mu;
+
+static int32_t attn_static_partials(float** out) {
+    int dev = 0;
+    SK_CUDA(cudaGetDevice(&dev));
+    SK_REQUIRE(dev >= 0 && dev < 64, "attn_decode_noalloc: device ordinal %d not supported", dev);
+    std::lock_guard<std::mutex> lk(g_attn_static_mu);
+    if (!g_attn_static_ptr[dev]) {
+        float* p = nullptr;
+        SK_CUDA(cudaGetSymbolAddress((void**) &p, g_attn_static_partials));
+        g_attn_static_ptr[dev] = p;
+    }
+    *out = g_attn_static_ptr[dev];
+    return SKAINET_CUDA_OK;
+}
+
 }  // namespace sk
+
+extern "C" int32_t skainet_cuda_attn_decode_noalloc_dev(const float* q, const uint16_t* k_cache, const uint16_t* v_cache, float* out,
+                                                        int32_t batch, int32_t heads, int32_t kv_heads, int32_t head_dim,
+                                                        int64_t cache_stride, const int32_t* kv_len_dev, int32_t max_kv_len,
+                                                        float scale, int32_t window, skainet_stream_t stream) {
+    using namespace sk;
+    if (batch <= 0 || heads <= 0) return SKAINET_CUDA_OK;
+    SK_REQUIRE(kv_heads > 0 && heads % kv_heads == 0, "attn_decode_noalloc: heads %d not a multiple of kv_heads %d", heads, kv_heads);
+    SK_REQUIRE(head_dim == 64 || head_dim == 128, "attn_decode_noalloc: head_dim %d not in {64,128}", head_dim);
+    SK_REQUIRE(max_kv_len >= 0 && cache_stride >= max_kv_len, "attn_decode_noalloc: cache_stride %lld < max_kv_len %d", (long long) cache_stride, max_kv_len);
+    SK_REQUIRE(q && k_cache && v_cache && out && kv_len_dev, "attn_decode_noalloc: null pointer");
+    SK_REQUIRE((((uintptr_t) q | (uintptr_t) k_cache | (uintptr_t) v_cache) & 15) == 0, "attn_decode_noalloc: q/k/v must be 16-byte aligned");
+    SK_TRY(ensure_device());
+    const int splits = decode_splits(batch, kv_heads, std::max(1, max_kv_len));
+    const size_t need = (size_t) batch * heads * splits * (head_dim + 2);
+    SK_REQUIRE(need <= ATTN_STATIC_FLOATS,
+               "attn_decode_noalloc: batch %d x heads %d x %d key splits needs %zu floats of partials, the built-in area holds %zu; "
+               "use skainet_cuda_attn_decode_dev for this size", batch, heads, splits, need, (size_t) ATTN_STATIC_FLOATS);
+    float* partials = nullptr;
+    SK_TRY(attn_static_partials(&partials));
+    return launch_attn_decode(q, (const __half*) k_cache, (const __half*) v_cache, out, batch, heads, kv_heads, head_dim, cache_stride,
+                              kv_len_dev, max_kv_len, scale, window, partials, as_stream(stream));
+}

@@ -175,3 +175,11 @@ def attn_decode(q_ptr: int, k_ptr: int, v_ptr: int, out_ptr: int, batch: int, he
 
 def sync(stream: int = 0) -> None:
     L.check(L.lib().skainet_cuda_stream_sync(stream))
+
+
+def attn_decode_noalloc(q_ptr: int, k_ptr: int, v_ptr: int, out_ptr: int, batch: int, heads: int, kv_heads: int, head_dim: int,
+                        cache_stride: int, kv_len_ptr: int, max_kv_len: int, scale: float, window: int = 0, stream: int = 0) -> None:
+    """attn_decode for hosts that must not allocate: split-K partials in the library's built-in 4 MiB area.
+    Raises ValueError when the problem does not fit it. Calls that overlap on the GPU race on that area."""
+    L.check(L.lib().skainet_cuda_attn_decode_noalloc_dev(q_ptr, k_ptr, v_ptr, out_ptr, batch, heads, kv_heads, head_dim,
+                                                         cache_stride, kv_len_ptr, max_kv_len, scale, window, stream))
