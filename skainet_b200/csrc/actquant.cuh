@@ -19,6 +19,10 @@ struct ActSplit {
     float* d;         // [m][cols/32]    amax / 16256
 };
 ActQ8K act_q8k_layout(void* scratch, int m, int cols);
+// attention.cu
+int32_t launch_attn_decode_quant(const float* q, int64_t q_row_stride, const __half* k, const __half* v, float* out, int batch,
+                                 int heads, int kv_heads, int d, int64_t cache_stride, const int32_t* kv_len, int max_kv_len,
+                                 float scale, int window, void* scratch, bool split, ActQ8K oq, ActSplit os, cudaStream_t s);
 ActSplit act_split_layout(void* scratch, int m, int cols);
 
 }  // namespace sk

@@ -11,6 +11,8 @@
 // max-subtracted exp and divide-by-sum :194-218, fully masked row -> uniform :347-351) and
 // skainet-lang/skainet-lang-core/src/commonMain/kotlin/sk/ainet/lang/tensor/ops/AttentionMask.kt:57-78.
 #include "common.cuh"
+#include "actquant.cuh"
+#include "tma.cuh"
 
 #include <mutex>
 
@@ -43,8 +45,11 @@ template <int D, int G>
 __global__ void __launch_bounds__(AD_THREADS)
 attn_decode_kernel(const float* __restrict__ q, const __half* __restrict__ kc, const __half* __restrict__ vc,
                    float* __restrict__ out, float* __restrict__ part, int heads, int kv_heads, int64_t cache_stride,
-                   const int32_t* __restrict__ kv_len, float scale, int window, int chunk, int splits) {
+                   const int32_t* __restrict__ kv_len, float scale, int window, int chunk, int splits,
+                   int64_t q_row_stride, int always_partials) {
     static_assert(D == 128 || D == 64, "head_dim");
+    skd::pdl_launch_dependents();
+    skd::pdl_wait();
     constexpr int LPK = D / 8;            // lanes per key (16 B = 8 halves per lane)
     constexpr int KPW = 32 / LPK;         // keys per warp-load
     constexpr int NW = AD_THREADS / LPK;  // workers in the CTA
@@ -61,7 +66,7 @@ attn_decode_kernel(const float* __restrict__ q, const __half* __restrict__ kc, c
     float qr[G][8];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-        const float* qp = q + ((int64_t) b * heads + kvh * G + g) * D + wl * 8;
+        const float* qp = q + (int64_t) b * q_row_stride + (int64_t) (kvh * G + g) * D + wl * 8;
         const float4 a = __ldg((const float4*) qp), c = __ldg((const float4*) qp + 1);
         qr[g][0] = a.x; qr[g][1] = a.y; qr[g][2] = a.z; qr[g][3] = a.w;
         qr[g][4] = c.x; qr[g][5] = c.y; qr[g][6] = c.z; qr[g][7] = c.w;
@@ -146,7 +151,7 @@ attn_decode_kernel(const float* __restrict__ q, const __half* __restrict__ kc, c
             at += c * sm_acc[w][g][dd];
         }
         const int head = kvh * G + g;
-        if (splits == 1) {
+        if (splits == 1 && !always_partials) {
             out[((int64_t) b * heads + head) * D + dd] = lt > 0.0f ? at / lt : 0.0f;
         } else {
             float* rec = part + (((int64_t) b * heads + head) * splits + split) * (D + 2);
@@ -158,6 +163,8 @@ attn_decode_kernel(const float* __restrict__ q, const __half* __restrict__ kc, c
 
 template <int D>
 __global__ void attn_merge_kernel(const float* __restrict__ part, float* __restrict__ out, int splits) {
+    skd::pdl_launch_dependents();
+    skd::pdl_wait();
     const int64_t bh = blockIdx.x;
     const float* rec = part + bh * splits * (D + 2);
     float mx = MASKED;
@@ -187,26 +194,104 @@ size_t attn_scratch_bytes(int batch, int heads, int head_dim, int max_kv_len) {
     return (size_t) batch * heads * splits * (head_dim + 2) * sizeof(float);
 }
 
+// Merge of the key splits fused with the activation quantizer of the projection that follows: one CTA
+// per 256 consecutive outputs of a row (two 128-wide heads or four 64-wide ones), fp32 result kept as
+// well. grid (heads*D/256, batch), 256 threads.
+template <int D, bool SPLIT>
+__global__ void __launch_bounds__(256)
+attn_merge_quant_kernel(const float* __restrict__ part, float* __restrict__ out, int splits, int heads, ActQ8K oq, ActSplit os) {
+    __shared__ float red[8];
+    skd::pdl_launch_dependents();
+    skd::pdl_wait();
+    const int b = blockIdx.y, e = blockIdx.x * 256 + threadIdx.x, n = heads * D;
+    const int head = e / D, dd = e % D, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* rec = part + ((int64_t) b * heads + head) * splits * (D + 2);
+    float mx = MASKED;
+    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, rec[s * (D + 2)]);
+    float lt = 0.0f, at = 0.0f;
+    for (int s = 0; s < splits; ++s) {
+        const float c = expf(rec[s * (D + 2)] - mx);
+        lt += c * rec[s * (D + 2) + 1];
+        at += c * rec[s * (D + 2) + 2 + dd];
+    }
+    const float v = lt > 0.0f ? at / lt : 0.0f;
+    out[(int64_t) b * n + e] = v;
+    if (SPLIT) {                 // one scale per 32 values = per warp
+        const float amax = skd::warp_max(fabsf(v));
+        const float inv = amax > 0.0f ? 16256.0f / amax : 0.0f;
+        const int q = max(-16256, min(16256, __float2int_rn(v * inv)));
+        const int hi = (q + 64) >> 7, lo = q - (hi << 7);
+        os.hi[(int64_t) b * n + e] = (int8_t) hi; os.lo[(int64_t) b * n + e] = (int8_t) lo;
+        if (lane == 0) os.d[((int64_t) b * n + e) >> 5] = amax > 0.0f ? amax / 16256.0f : 0.0f;
+    } else {                     // one scale per 256 values = per CTA, code sums per warp
+        float amax = skd::warp_max(fabsf(v));
+        if (lane == 0) red[warp] = amax;
+        __syncthreads();
+        amax = fmaxf(fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3])), fmaxf(fmaxf(red[4], red[5]), fmaxf(red[6], red[7])));
+        const float inv = amax > 0.0f ? 127.0f / amax : 0.0f;
+        const int q = max(-127, min(127, __float2int_rn(v * inv)));
+        oq.q[(int64_t) b * n + e] = (int8_t) q;
+        int sum = q;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) oq.bsums[((int64_t) b * n + e) >> 5] = (int16_t) sum;
+        if (threadIdx.x == 0) oq.d[((int64_t) b * n + e) >> 8] = amax > 0.0f ? amax / 127.0f : 0.0f;
+    }
+}
+
 template <int D, int G>
 static void launch_decode_dg(const float* q, const __half* k, const __half* v, float* out, float* part, int batch,
                              int heads, int kv_heads, int64_t cache_stride, const int32_t* kv_len, float scale,
-                             int window, int chunk, int splits, cudaStream_t s) {
+                             int window, int chunk, int splits, int64_t q_row_stride, int always_partials, cudaStream_t s) {
     dim3 grid(splits, kv_heads, batch);
-    attn_decode_kernel<D, G><<<grid, AD_THREADS, 0, s>>>(q, k, v, out, part, heads, kv_heads, cache_stride, kv_len,
-                                                        scale, window, chunk, splits);
-    if (splits > 1) attn_merge_kernel<D><<<batch * heads, D, 0, s>>>(part, out, splits);
+    launch_pdl(attn_decode_kernel<D, G>, grid, dim3(AD_THREADS), 0, s, q, k, v, out, part, heads, kv_heads, cache_stride, kv_len,
+               scale, window, chunk, splits, q_row_stride, always_partials);
+    if (splits > 1 && !always_partials) launch_pdl(attn_merge_kernel<D>, dim3(batch * heads), dim3(D), 0, s, (const float*) part, out, splits);
 }
+
+static int32_t attn_decode_impl(const float* q, int64_t q_row_stride, const __half* k, const __half* v, float* out, int batch, int heads,
+                                int kv_heads, int d, int64_t cache_stride, const int32_t* kv_len, int max_kv_len,
+                                float scale, int window, void* scratch, int always_partials, int* splits_out, cudaStream_t s);
 
 int32_t launch_attn_decode(const float* q, const __half* k, const __half* v, float* out, int batch, int heads,
                            int kv_heads, int d, int64_t cache_stride, const int32_t* kv_len, int max_kv_len,
                            float scale, int window, void* scratch, cudaStream_t s) {
+    return attn_decode_impl(q, (int64_t) heads * d, k, v, out, batch, heads, kv_heads, d, cache_stride, kv_len, max_kv_len, scale, window,
+                            scratch, 0, nullptr, s);
+}
+
+// Decode attention whose result is also quantized for the projection that follows (q8 per 256 for
+// K-quant weights, two-term split for Q8_0): split-K kernel, then one merge+quantize kernel. q rows may
+// be strided (read straight out of a merged q|k|v buffer). heads*d must be a multiple of 256.
+int32_t launch_attn_decode_quant(const float* q, int64_t q_row_stride, const __half* k, const __half* v, float* out, int batch,
+                                 int heads, int kv_heads, int d, int64_t cache_stride, const int32_t* kv_len, int max_kv_len,
+                                 float scale, int window, void* scratch, bool split, ActQ8K oq, ActSplit os, cudaStream_t s) {
+    if (batch <= 0 || heads <= 0) return SKAINET_CUDA_OK;
+    if ((heads * d) % 256 != 0) { set_error("attn_decode_quant: heads*head_dim %d is not a multiple of 256", heads * d); return SKAINET_CUDA_ERR_INVALID; }
+    int splits = 1;
+    SK_TRY(attn_decode_impl(q, q_row_stride, k, v, out, batch, heads, kv_heads, d, cache_stride, kv_len, max_kv_len, scale, window, scratch, 1, &splits, s));
+    dim3 grid(heads * d / 256, batch);
+    if (d == 128) {
+        if (split) SK_CUDA(launch_pdl(attn_merge_quant_kernel<128, true>, grid, dim3(256), 0, s, (const float*) scratch, out, splits, heads, oq, os));
+        else SK_CUDA(launch_pdl(attn_merge_quant_kernel<128, false>, grid, dim3(256), 0, s, (const float*) scratch, out, splits, heads, oq, os));
+    } else {
+        if (split) SK_CUDA(launch_pdl(attn_merge_quant_kernel<64, true>, grid, dim3(256), 0, s, (const float*) scratch, out, splits, heads, oq, os));
+        else SK_CUDA(launch_pdl(attn_merge_quant_kernel<64, false>, grid, dim3(256), 0, s, (const float*) scratch, out, splits, heads, oq, os));
+    }
+    return SKAINET_CUDA_OK;
+}
+
+static int32_t attn_decode_impl(const float* q, int64_t q_row_stride, const __half* k, const __half* v, float* out, int batch, int heads,
+                                int kv_heads, int d, int64_t cache_stride, const int32_t* kv_len, int max_kv_len,
+                                float scale, int window, void* scratch, int always_partials, int* splits_out, cudaStream_t s) {
     if (batch <= 0 || heads <= 0) return SKAINET_CUDA_OK;
     const int G = heads / kv_heads;
     const int splits = decode_splits(batch, kv_heads, std::max(1, max_kv_len));
     int chunk = (std::max(1, max_kv_len) + splits - 1) / splits;
     chunk = (chunk + 31) & ~31;
     float* part = (float*) scratch;
-#define SK_AD(DD, GG) launch_decode_dg<DD, GG>(q, k, v, out, part, batch, heads, kv_heads, cache_stride, kv_len, scale, window, chunk, splits, s)
+    if (splits_out) *splits_out = splits;
+#define SK_AD(DD, GG) launch_decode_dg<DD, GG>(q, k, v, out, part, batch, heads, kv_heads, cache_stride, kv_len, scale, window, chunk, splits, q_row_stride, always_partials, s)
     if (d == 128) {
         switch (G) { case 1: SK_AD(128, 1); break; case 2: SK_AD(128, 2); break; case 4: SK_AD(128, 4); break; case 8: SK_AD(128, 8); break;
             default: set_error("attn_decode: heads/kv_heads = %d not in {1,2,4,8}", G); return SKAINET_CUDA_ERR_INVALID; }

@@ -29,23 +29,32 @@ namespace sk {
 // ================================================================================================
 enum { PK_QUANT = 0, PK_NORM = 1, PK_SWIGLU = 2 };
 
-// One CTA per activation row: (optional RMSNorm | SwiGLU) then quantization for the next matvec,
-// q8 per 256 (K-quant weights) or the two-term split per 32 (Q8_0 weights).
-// in: [rows][n] (PK_SWIGLU: [rows][2n] = gate | up). 256 threads.
+// Activation prep between two matvecs: (optional RMSNorm | SwiGLU) then quantization for the next
+// matvec, q8 per 256 (K-quant weights) or the two-term split per 32 (Q8_0 weights).
+// grid (ceil(n/2048), rows), 256 threads: a CTA quantizes 2048 consecutive elements of one row (eight
+// per thread; a warp = one 256-block, four lanes = one 32-block). For RMSNorm every CTA of the row sums
+// the whole row's squares itself (n fp32 values out of L2) instead of synchronising across CTAs.
+// in: [rows][n] (PK_SWIGLU: [rows][2n] = gate | up).
 template <int MODE, bool SPLIT>
 __global__ void __launch_bounds__(256)
 prep_kernel(const float* __restrict__ in, const float* __restrict__ gamma, float eps, int n, ActQ8K oq, ActSplit os) {
     __shared__ float red[8];
     skd::pdl_launch_dependents();
     skd::pdl_wait();
-    const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* x = in + (size_t) row * (MODE == PK_SWIGLU ? 2 * n : n);
     float nscale = 1.0f;
     if (MODE == PK_NORM) {
         float ss = 0.0f;
-        for (int i = threadIdx.x; i < (n >> 2); i += 256) {
-            const float4 v = __ldg(reinterpret_cast<const float4*>(x) + i);
-            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        for (int i0 = threadIdx.x; i0 < (n >> 2); i0 += 256 * 4) {      // four loads in flight per thread
+            float4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int i = i0 + j * 256;
+                v[j] = i < (n >> 2) ? __ldg(reinterpret_cast<const float4*>(x) + i) : make_float4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
         }
         ss = skd::warp_sum(ss);
         if (lane == 0) red[warp] = ss;
@@ -55,45 +64,39 @@ prep_kernel(const float* __restrict__ in, const float* __restrict__ gamma, float
         for (int i = 0; i < 8; ++i) t += red[i];
         nscale = 1.0f / sqrtf(t * (1.0f / (float) n) + eps);
     }
-    // eight consecutive elements per thread per step
     const int n8 = n >> 3;
-    const int n8_pad = (n8 + 31) & ~31;                    // whole warps take part in the shuffles
-    for (int c = threadIdx.x; c < n8_pad; c += 256) {
-        float v[8];
-        const bool ok = c < n8;
-        const int cc = ok ? c : 0;
-        {
-            const float4 a = __ldg(reinterpret_cast<const float4*>(x) + 2 * cc), b = __ldg(reinterpret_cast<const float4*>(x) + 2 * cc + 1);
-            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-        }
-        if (MODE == PK_NORM) {
-            const float4 a = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * cc), b = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * cc + 1);
-            const float g[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    const int c = blockIdx.x * 256 + threadIdx.x;          // this thread's 8-element chunk of the row
+    const bool ok = c < n8;
+    const int cc = ok ? c : 0;
+    float v[8];
+    {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(x) + 2 * cc), b = __ldg(reinterpret_cast<const float4*>(x) + 2 * cc + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    if (MODE == PK_NORM) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * cc), b = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * cc + 1);
+        const float g[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = (v[i] * nscale) * g[i];
-        }
-        if (MODE == PK_SWIGLU) {
-            const float4 a = __ldg(reinterpret_cast<const float4*>(x + n) + 2 * cc), b = __ldg(reinterpret_cast<const float4*>(x + n) + 2 * cc + 1);
-            const float u[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        for (int i = 0; i < 8; ++i) v[i] = (v[i] * nscale) * g[i];
+    }
+    if (MODE == PK_SWIGLU) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(x + n) + 2 * cc), b = __ldg(reinterpret_cast<const float4*>(x + n) + 2 * cc + 1);
+        const float u[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = (v[i] * (1.0f / (1.0f + expf(-v[i])))) * u[i];
-        }
-        if (!ok) {
+        for (int i = 0; i < 8; ++i) v[i] = (v[i] * (1.0f / (1.0f + expf(-v[i])))) * u[i];
+    }
+    if (!ok) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = 0.0f;
-        }
-        if (SPLIT) {
-            ActSplit o = os;
-            o.hi += (size_t) row * n; o.lo += (size_t) row * n; o.d += (size_t) row * (n >> 5);
-            skd::quant_split_regs(v, o, cc >> 2, cc & 3, ok);
-        } else {
-            // a 256-block is 32 consecutive threads = one warp
-            const int blk = cc >> 5;
-            if (c - lane < n8) {       // warp-uniform: the warp's first chunk is inside the row
-                skd::quant_q8k_regs(v, oq.q + (size_t) row * n + (size_t) blk * 256, oq.d + (size_t) row * (n >> 8) + blk,
-                                    oq.bsums + (size_t) row * (n >> 5) + (size_t) blk * 8, lane);
-            }
-        }
+        for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+    }
+    if (SPLIT) {
+        ActSplit o = os;
+        o.hi += (size_t) row * n; o.lo += (size_t) row * n; o.d += (size_t) row * (n >> 5);
+        skd::quant_split_regs(v, o, cc >> 2, cc & 3, ok);
+    } else if (c - lane < n8) {       // warp-uniform: the warp's 256-block lies inside the row
+        const int blk = cc >> 5;
+        skd::quant_q8k_regs(v, oq.q + (size_t) row * n + (size_t) blk * 256, oq.d + (size_t) row * (n >> 8) + blk,
+                            oq.bsums + (size_t) row * (n >> 5) + (size_t) blk * 8, lane);
     }
 }
 
@@ -297,10 +300,10 @@ static int32_t prep(Model& m, const float* in, const float* gamma, int rows, int
     ActQ8K oq = {nullptr, nullptr, nullptr}; ActSplit os = {nullptr, nullptr, nullptr};
     if (split) {
         os = act_split_layout(m.act, rows, n);
-        SK_CUDA(launch_pdl(prep_kernel<MODE, true>, dim3(rows), dim3(256), 0, s, in, gamma, m.cfg.rms_eps, n, oq, os));
+        SK_CUDA(launch_pdl(prep_kernel<MODE, true>, dim3((n + 2047) / 2048, rows), dim3(256), 0, s, in, gamma, m.cfg.rms_eps, n, oq, os));
     } else {
         oq = act_q8k_layout(m.act, rows, n);
-        SK_CUDA(launch_pdl(prep_kernel<MODE, false>, dim3(rows), dim3(256), 0, s, in, gamma, m.cfg.rms_eps, n, oq, os));
+        SK_CUDA(launch_pdl(prep_kernel<MODE, false>, dim3((n + 2047) / 2048, rows), dim3(256), 0, s, in, gamma, m.cfg.rms_eps, n, oq, os));
     }
     return SKAINET_CUDA_OK;
 }
@@ -326,15 +329,21 @@ static int32_t body(Model& m, int rows, bool prefill, int seq, int kv_bound, cud
         SK_CUDA(launch_pdl(rope_append_kernel, dim3(rows, H + 2 * HK), dim3(D / 2), 0, s, m.qkv, H, HK, D, (const float*) m.cos_t,
                            (const float*) m.sin_t, (const int32_t*) m.pos, (const int32_t*) (prefill ? m.row_seq : nullptr), prefill ? 1 : 0,
                            L.kc, L.vc, (int64_t) c.max_seq, c.rope_mode));
-        SK_CUDA(launch_pdl(gather_q_kernel, dim3(rows), dim3(256), 0, s, (const float*) m.qkv, m.q, H * D, qkv_dim));
+        const bool fused_attn = !prefill && (H * D) % 256 == 0;
+        if (!fused_attn) SK_CUDA(launch_pdl(gather_q_kernel, dim3(rows), dim3(256), 0, s, (const float*) m.qkv, m.q, H * D, qkv_dim));
         if (prefill) {
             const __half* kc = L.kc + (size_t) seq * HK * c.max_seq * D;
             const __half* vc = L.vc + (size_t) seq * HK * c.max_seq * D;
             SK_TRY(launch_sdpa_cache(m.q, kc, vc, m.attn, 1, H, HK, rows, kv_bound, c.max_seq, D, scale, 0, m.pos + seq, s));
+        } else if (fused_attn) {   // q read in place from the merged buffer; merge of the key splits quantizes for o_proj
+            ActQ8K oq = {nullptr, nullptr, nullptr}; ActSplit os = {nullptr, nullptr, nullptr};
+            if (lin_split) os = act_split_layout(m.act, rows, H * D); else oq = act_q8k_layout(m.act, rows, H * D);
+            SK_TRY(launch_attn_decode_quant(m.qkv, qkv_dim, L.kc, L.vc, m.attn, rows, H, HK, D, c.max_seq, m.kv_len, kv_bound, scale, 0,
+                                            m.attn_scratch, lin_split, oq, os, s));
         } else {
             SK_TRY(launch_attn_decode(m.q, L.kc, L.vc, m.attn, rows, H, HK, D, c.max_seq, m.kv_len, kv_bound, scale, 0, m.attn_scratch, s));
         }
-        SK_TRY(prep<PK_QUANT>(m, m.attn, nullptr, rows, H * D, lin_split, s));
+        if (!fused_attn) SK_TRY(prep<PK_QUANT>(m, m.attn, nullptr, rows, H * D, lin_split, s));
         // row-parallel projections under TP: rank 0 carries the residual, then the group sums
         if (tp && !rank0) SK_TRY(linear(m, *L.wo, rows, m.x, nullptr, s)); else SK_TRY(linear(m, *L.wo, rows, nullptr, m.x, s));
         SK_TRY(tp_sum(m, m.x, (int64_t) rows * c.d_model, s));
