@@ -14,6 +14,8 @@
 #include "actquant.cuh"
 #include "tma.cuh"
 
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 namespace sk {
@@ -180,6 +182,173 @@ __global__ void attn_merge_kernel(const float* __restrict__ part, float* __restr
     }
 }
 
+// =================================================================================================
+// Decode attention on the tensor cores (mma.sync m16n8k16, f16 x f16 -> f32): the kernel used for every
+// group size. Scores and P.V are small contractions (heads x dims x keys) whose operands are the f16
+// cache rows themselves, so the CUDA cores only do the softmax. Rows of the 16-row MMA tile hold the
+// group's query heads twice: rows 0..7 the f16 high part of q (resp. of the probabilities), rows 8..15
+// the f16 low part, so one MMA yields both halves of a two-term product and fp32 accuracy is kept
+// although the cache is f16 (exact) and q / p are split hi + lo.
+//
+// Lane (g = lane/4, t = lane%4). K tile as B operand (dims x 8 keys): the lane loads 16-byte chunks
+// t, t+4, .. of key g straight from HBM; the four half2 of a chunk are the B registers of two k-steps
+// (the order of dims inside the contraction is free as long as q uses the same order). The scores come
+// out as C[head g][keys 2t, 2t+1] — exactly the A layout P.V needs. V tile as B operand (keys x 8 dims):
+// the lane loads chunk g (+8) of keys 2t, 2t+1, 2t+8, 2t+9 and pairs equal dims of adjacent keys with
+// one prmt each. Each warp walks its own keys with an online softmax; warps, then key splits, are merged
+// in a fixed order.
+// =================================================================================================
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// (x, y) -> f16 high parts packed, f16 low parts (x - hi(x)) packed
+__device__ __forceinline__ void split_pack(float x, float y, uint32_t& hi, uint32_t& lo) {
+    const __half hx = __float2half_rn(x), hy = __float2half_rn(y);
+    const __half lx = __float2half_rn(x - __half2float(hx)), ly = __float2half_rn(y - __half2float(hy));
+    hi = (uint32_t) __half_as_ushort(hx) | ((uint32_t) __half_as_ushort(hy) << 16);
+    lo = (uint32_t) __half_as_ushort(lx) | ((uint32_t) __half_as_ushort(ly) << 16);
+}
+
+constexpr int AM_WARPS = 4;
+
+template <int D>
+__global__ void __launch_bounds__(AM_WARPS * 32)
+attn_decode_mma_kernel(const float* __restrict__ q, int64_t q_row_stride, const __half* __restrict__ kc, const __half* __restrict__ vc,
+                       float* __restrict__ part, int heads, int kv_heads, int G, int64_t cache_stride,
+                       const int32_t* __restrict__ kv_len, float scale, int window, int chunk, int splits) {
+    constexpr int S4 = D / 32;     // chunks of a K row per lane
+    constexpr int KS = D / 16;     // k-steps of the score contraction
+    constexpr int U = D / 64;      // chunks of a V row per lane
+    constexpr int NT = D / 8;      // 8-dim output tiles
+    __shared__ float sm_m[AM_WARPS][8], sm_l[AM_WARPS][8];
+    __shared__ float sm_acc[AM_WARPS][8][D];
+    skd::pdl_launch_dependents();
+    skd::pdl_wait();
+
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int len = kv_len[b];
+    int first = 0;
+    if (window > 0 && len - window > first) first = len - window;
+    const int begin = max(first, split * chunk), stop = min(len, (split + 1) * chunk);
+
+    // q of head g as A fragments: per k-step {hi(k 2t..), lo(k 2t..), hi(k 2t+8..), lo(k 2t+8..)}
+    uint32_t qa[KS][4];
+    {
+        const float* qp = q + (int64_t) b * q_row_stride + (int64_t) (kvh * G + g) * D;
+#pragma unroll
+        for (int s = 0; s < S4; ++s) {
+            float f[8];
+            if (g < G) {
+                const float4 a = __ldg((const float4*) (qp + (t + 4 * s) * 8)), c = __ldg((const float4*) (qp + (t + 4 * s) * 8) + 1);
+                f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = c.x; f[5] = c.y; f[6] = c.z; f[7] = c.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] = 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                split_pack(f[4 * j], f[4 * j + 1], qa[2 * s + j][0], qa[2 * s + j][1]);
+                split_pack(f[4 * j + 2], f[4 * j + 3], qa[2 * s + j][2], qa[2 * s + j][3]);
+            }
+        }
+    }
+    float m = MASKED, l = 0.0f;
+    float o[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) { o[i][0] = 0.f; o[i][1] = 0.f; o[i][2] = 0.f; o[i][3] = 0.f; }
+
+    const __half* kb = kc + ((int64_t) b * kv_heads + kvh) * cache_stride * D;
+    const __half* vb = vc + ((int64_t) b * kv_heads + kvh) * cache_stride * D;
+    const uint4 zero4 = make_uint4(0, 0, 0, 0);
+
+    for (int k0 = begin + warp * 16; k0 < stop; k0 += AM_WARPS * 16) {
+        // ---- loads of the 16-key tile: K as (key g | g+8, chunks t+4s), V as (keys 2t,2t+1,2t+8,2t+9, chunks g+8u)
+        uint4 kr[2][S4], vr[4][U];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const int key = k0 + 8 * nt + g;
+#pragma unroll
+            for (int s = 0; s < S4; ++s) kr[nt][s] = key < stop ? skd::ld_stream(kb + (int64_t) key * D + (t + 4 * s) * 8) : zero4;
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            const int key = k0 + 2 * t + (kk & 1) + 8 * (kk >> 1);
+#pragma unroll
+            for (int u = 0; u < U; ++u) vr[kk][u] = key < stop ? skd::ld_stream(vb + (int64_t) key * D + (g + 8 * u) * 8) : zero4;
+        }
+        // ---- scores of head g for keys k0 + {2t, 2t+1, 8+2t, 8+2t+1}
+        float sc[4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int s = 0; s < S4; ++s) {
+                mma_f16(c, qa[2 * s], kr[nt][s].x, kr[nt][s].y);
+                mma_f16(c, qa[2 * s + 1], kr[nt][s].z, kr[nt][s].w);
+            }
+            const int key = k0 + 8 * nt + 2 * t;
+            sc[2 * nt] = key < stop ? (c[0] + c[2]) * scale : MASKED;
+            sc[2 * nt + 1] = key + 1 < stop ? (c[1] + c[3]) * scale : MASKED;
+        }
+        float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float mnew = fmaxf(m, mx);
+        const float corr = expf(m - mnew);
+        m = mnew;
+        float p[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p[i] = sc[i] > 0.5f * MASKED ? expf(sc[i] - mnew) : 0.0f;
+        l = l * corr + (p[0] + p[1]) + (p[2] + p[3]);
+#pragma unroll
+        for (int i = 0; i < NT; ++i) { o[i][0] *= corr; o[i][1] *= corr; o[i][2] *= corr; o[i][3] *= corr; }
+        uint32_t pa[4];
+        split_pack(p[0], p[1], pa[0], pa[1]);
+        split_pack(p[2], p[3], pa[2], pa[3]);
+        // ---- out[head g][dims] += P . V ; tile (u, i): column n <-> dim 8*(n + 8u) + i
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t v0[4] = {vr[0][u].x, vr[0][u].y, vr[0][u].z, vr[0][u].w}, v1[4] = {vr[1][u].x, vr[1][u].y, vr[1][u].z, vr[1][u].w};
+            const uint32_t v8[4] = {vr[2][u].x, vr[2][u].y, vr[2][u].z, vr[2][u].w}, v9[4] = {vr[3][u].x, vr[3][u].y, vr[3][u].z, vr[3][u].w};
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                mma_f16(o[u * 8 + 2 * r], pa, __byte_perm(v0[r], v1[r], 0x5410), __byte_perm(v8[r], v9[r], 0x5410));
+                mma_f16(o[u * 8 + 2 * r + 1], pa, __byte_perm(v0[r], v1[r], 0x7632), __byte_perm(v8[r], v9[r], 0x7632));
+            }
+        }
+    }
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    // ---- merge the warps (fixed order), one partial record per (batch, head, split)
+    if (t == 0) { sm_m[warp][g] = m; sm_l[warp][g] = l; }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            sm_acc[warp][g][8 * (2 * t + 8 * u) + i] = o[u * 8 + i][0] + o[u * 8 + i][2];
+            sm_acc[warp][g][8 * (2 * t + 1 + 8 * u) + i] = o[u * 8 + i][1] + o[u * 8 + i][3];
+        }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * D; idx += AM_WARPS * 32) {
+        const int hg = idx / D, dd = idx % D;
+        float mxx = MASKED;
+#pragma unroll
+        for (int w = 0; w < AM_WARPS; ++w) mxx = fmaxf(mxx, sm_m[w][hg]);
+        float lt = 0.0f, at = 0.0f;
+#pragma unroll
+        for (int w = 0; w < AM_WARPS; ++w) {
+            const float c = expf(sm_m[w][hg] - mxx);
+            lt += c * sm_l[w][hg];
+            at += c * sm_acc[w][hg][dd];
+        }
+        float* rec = part + (((int64_t) b * heads + kvh * G + hg) * splits + split) * (D + 2);
+        rec[2 + dd] = at;
+        if (dd == 0) { rec[0] = mxx; rec[1] = lt; }
+    }
+}
+
 static int decode_splits(int batch, int kv_heads, int max_kv_len) {
     const int ctas = batch * kv_heads;
     int want = (sm_count() * 4 + ctas - 1) / ctas;            // ~4 CTAs of 128 threads per SM
@@ -207,12 +376,14 @@ attn_merge_quant_kernel(const float* __restrict__ part, float* __restrict__ out,
     const int head = e / D, dd = e % D, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* rec = part + ((int64_t) b * heads + head) * splits * (D + 2);
     float mx = MASKED;
-    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, rec[s * (D + 2)]);
+#pragma unroll 8
+    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, __ldg(rec + s * (D + 2)));
     float lt = 0.0f, at = 0.0f;
+#pragma unroll 8
     for (int s = 0; s < splits; ++s) {
-        const float c = expf(rec[s * (D + 2)] - mx);
-        lt += c * rec[s * (D + 2) + 1];
-        at += c * rec[s * (D + 2) + 2 + dd];
+        const float c = expf(__ldg(rec + s * (D + 2)) - mx);
+        lt += c * __ldg(rec + s * (D + 2) + 1);
+        at += c * __ldg(rec + s * (D + 2) + 2 + dd);
     }
     const float v = lt > 0.0f ? at / lt : 0.0f;
     out[(int64_t) b * n + e] = v;
@@ -244,9 +415,17 @@ static void launch_decode_dg(const float* q, const __half* k, const __half* v, f
                              int heads, int kv_heads, int64_t cache_stride, const int32_t* kv_len, float scale,
                              int window, int chunk, int splits, int64_t q_row_stride, int always_partials, cudaStream_t s) {
     dim3 grid(splits, kv_heads, batch);
-    launch_pdl(attn_decode_kernel<D, G>, grid, dim3(AD_THREADS), 0, s, q, k, v, out, part, heads, kv_heads, cache_stride, kv_len,
-               scale, window, chunk, splits, q_row_stride, always_partials);
-    if (splits > 1 && !always_partials) launch_pdl(attn_merge_kernel<D>, dim3(batch * heads), dim3(D), 0, s, (const float*) part, out, splits);
+    // SKAINET_ATTN=simt selects the CUDA-core kernel (kept for A/B measurements)
+    static const bool simt = []() { const char* e = getenv("SKAINET_ATTN"); return e && strcmp(e, "simt") == 0; }();
+    if (simt) {
+        launch_pdl(attn_decode_kernel<D, G>, grid, dim3(AD_THREADS), 0, s, q, k, v, out, part, heads, kv_heads, cache_stride, kv_len,
+                   scale, window, chunk, splits, q_row_stride, always_partials);
+        if (splits > 1 && !always_partials) launch_pdl(attn_merge_kernel<D>, dim3(batch * heads), dim3(D), 0, s, (const float*) part, out, splits);
+        return;
+    }
+    launch_pdl(attn_decode_mma_kernel<D>, grid, dim3(AM_WARPS * 32), 0, s, q, q_row_stride, k, v, part, heads, kv_heads, G, cache_stride, kv_len,
+               scale, window, chunk, splits);
+    if (!always_partials) launch_pdl(attn_merge_kernel<D>, dim3(batch * heads), dim3(D), 0, s, (const float*) part, out, splits);
 }
 
 static int32_t attn_decode_impl(const float* q, int64_t q_row_stride, const __half* k, const __half* v, float* out, int batch, int heads,
