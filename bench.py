@@ -241,6 +241,29 @@ def workload_config(args, world: int, extra: dict | None = None) -> dict:
 # ---------------------------------------------------------------------------------------------------
 # our arm: matvec sweep
 # ---------------------------------------------------------------------------------------------------
+def read_floor_ms(torch, L, weights_flat, stream, steps: int) -> float:
+    """ms per sweep of a kernel that only reads the same weights (one launch per weight, one graph per sweep)."""
+    lib = L.lib(); sp = stream.cuda_stream
+    with torch.cuda.stream(stream):
+        for w in weights_flat:
+            L.check(lib.skainet_cuda_probe_read_dev(w.handle, sp))
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for w in weights_flat:
+                L.check(lib.skainet_cuda_probe_read_dev(w.handle, sp))
+        for _ in range(3):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        stream.synchronize()
+        e0.record(stream)
+        for _ in range(steps):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
 def matvec_sweep_rate(torch, device, L, weights_flat, stream, steps: int, warmup: int):
     """Times `steps` sweeps of one fused-path matvec per weight (fp32 activation in HBM), one CUDA graph
     per sweep, on `stream`. Returns (ms per sweep, launches per sweep)."""
@@ -299,6 +322,7 @@ def run_matvec(args) -> None:
     if rank == 0:
         sampler.start()
     ms_step, launches, graph, bufs = matvec_sweep_rate(torch, device, L, weights, stream, args.steps, args.warmup)
+    floor_ms = read_floor_ms(torch, L, weights, stream, args.steps)
     barrier()
     if rank == 0 and not args.skip_cpu:      # keep the GPU under load long enough for the clock sampler
         t_end = time.time() + 1.0
@@ -344,7 +368,9 @@ def run_matvec(args) -> None:
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
                          "peak_kind": peak_kind, "kernel": "q4k_matvec_fused_kernel" if enc == "Q4_K" else "q8_0_matvec_fused_kernel",
                          "avg_launch_us": per_launch_us,
-                         "note": "avg launch = timed region / matvec launches; the activation quantizer and launch gaps are inside it"},
+                         "read_floor_us": floor_ms * 1e3 / len(weights), "read_floor_gbs": bytes_per_step / (floor_ms * 1e-3) / 1e9,
+                         "note": "avg launch = timed region / matvec launches; the activation quantizer and launch gaps are inside it. "
+                                 "read_floor = a kernel that only reads the same weights, same launch count, same graph protocol"},
             "e2e": {"value": (bytes_per_step * world * e2e_steps / (e2e_ms * 1e-3) / 1e9) if e2e_steps else None, "unit": "GB/s",
                     "h2d_bytes_per_step": int(sum(4 * w.cols for w in weights)), "d2h_bytes_per_step": int(sum(4 * w.rows for w in weights)),
                     "note": "weights resident; each matvec copies its activation in and its output out and synchronises"},

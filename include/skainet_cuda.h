@@ -190,6 +190,11 @@ SKAINET_CUDA_API int32_t skainet_cuda_matmul_dev(skainet_weight_t w, const float
 SKAINET_CUDA_API int32_t skainet_cuda_matvec_fused_dev(skainet_weight_t w, const float* x_dev, const float* gamma_dev,
     float eps, const float* resid_dev, float* y_dev, skainet_stream_t stream);
 
+/* Measurement aid with no counterpart in the reference: reads every byte of a resident weight once
+ * with plain vector loads and computes nothing. The bench times it over the same weights as the matvec
+ * to report the floor a launch of that many bytes can reach on this GPU. */
+SKAINET_CUDA_API int32_t skainet_cuda_probe_read_dev(skainet_weight_t w, skainet_stream_t stream);
+
 /* Row kernels on the device (contracts as the twins above). */
 SKAINET_CUDA_API int32_t skainet_cuda_rms_norm_dev(const float* in, const float* gamma, float* out,
     int32_t rows, int32_t cols, float eps, skainet_stream_t stream);

@@ -63,6 +63,7 @@ SIGNATURES = {
     "skainet_cuda_weight_free": [i64],
     "skainet_cuda_weight_dequant": [i64, vp, vp],
     "skainet_cuda_matmul_dev": [i64, vp, i32, vp, i32, vp],
+    "skainet_cuda_probe_read_dev": [i64, vp],
     "skainet_cuda_matvec_fused_dev": [i64, vp, vp, f32, vp, vp, vp],
     "skainet_cuda_rms_norm_dev": [vp, vp, vp, i32, i32, f32, vp],
     "skainet_cuda_unary_dev": [i32, vp, vp, i64, vp],

@@ -401,6 +401,15 @@ int32_t skainet_cuda_matmul_dev(skainet_weight_t h, const float* x_dev, int32_t 
     return launch_matvec(*w, x_dev, scratch, m, y_dev, act_mode, s);
 }
 
+int32_t skainet_cuda_probe_read_dev(skainet_weight_t h, skainet_stream_t stream) {
+    Weight* w = weight_from_handle(h);
+    if (!w) return SKAINET_CUDA_ERR_HANDLE;
+    SK_TRY(ensure_device());
+    void* sink = nullptr;
+    SK_TRY(scratch_get(as_stream(stream), SCRATCH_FUSED2, 64, &sink));
+    return launch_probe_read(*w, (uint32_t*) sink, as_stream(stream));
+}
+
 int32_t skainet_cuda_matvec_fused_dev(skainet_weight_t h, const float* x_dev, const float* gamma_dev, float eps,
                                       const float* resid_dev, float* y_dev, skainet_stream_t stream) {
     Weight* w = weight_from_handle(h);

@@ -105,6 +105,8 @@ int32_t launch_matvec(const Weight& w, const float* x, const void* act_scratch, 
                       cudaStream_t s);
 // matvec_stream.cu: rows m0..m0+mm of the quantized activation; returns 1 when the shape is not taken
 int32_t launch_matvec_stream(const Weight& w, const void* act_scratch, int m_total, int m0, int mm, float* y, cudaStream_t s);
+// probe.cu
+int32_t launch_probe_read(const Weight& w, uint32_t* sink, cudaStream_t s);
 // rowops.cu
 int32_t launch_rms_norm(const float* in, const float* gamma, float* out, int rows, int cols, float eps, cudaStream_t s);
 int32_t launch_unary(int op, const float* in, float* out, int64_t n, cudaStream_t s);

@@ -20,6 +20,8 @@
 #include "tma.cuh"
 #include "matvec_fused.cuh"
 
+#include <cstdlib>
+
 namespace sk {
 
 constexpr int MF_WARPS = 4;
@@ -449,6 +451,12 @@ static int32_t launch_q8_f(const Weight& w, const MatvecIn& in, float* y, const 
 int32_t launch_matvec_fused(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s) {
     int* flag = device_timeout_flag();
     if (w.rows <= 0) return 1;
+    // Large weights go to the persistent ring kernel (SKAINET_RING_MIN_MB overrides the size threshold).
+    static const int64_t ring_min = []() { const char* e = getenv("SKAINET_RING_MIN_MB"); return (int64_t) (e ? atoi(e) : 12) << 20; }();
+    if (prep == PREP_QUANTIZED && w.packed_bytes >= ring_min) {
+        const int32_t st = launch_matvec_ring(w, in, y, resid, s);
+        if (st != 1) return st;
+    }
     const int epi = resid ? EPI_ADD : EPI_STORE;
     if (w.enc == SKAINET_ENC_Q4_K) {
         const size_t fixed = (size_t) w.cols + w.cols / 16 + ((w.bpr * 4 + 15) & ~15) + 16 + MF_MAX_RW * 8 + 64;

@@ -23,4 +23,8 @@ struct MatvecIn {
 // outside what the kernel takes (the caller then uses the general kernels).
 int32_t launch_matvec_fused(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s);
 
+// matvec_ring.cu: the persistent ring kernel for large weights (activation already quantized); same
+// return convention.
+int32_t launch_matvec_ring(const Weight& w, const MatvecIn& in, float* y, const float* resid, cudaStream_t s);
+
 }  // namespace sk

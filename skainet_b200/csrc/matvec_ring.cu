@@ -1,0 +1,354 @@
+// Persistent ring matvec for LARGE weights (m = 1): when a weight is hundreds of KB per SM, a few CTAs
+// per SM each keep a ring of shared-memory stages filled by a producer warp (cp.async.bulk / TMA, one
+// "full" mbarrier per stage counted in bytes) while NC consumer warps — one output row of the stage each
+// — drain it and hand stages back through "empty" mbarriers. The rings are the SM's bytes in flight
+// (up to ~190 KB), so HBM stays busy for the whole launch and the quantized activation is staged once
+// per CTA instead of once per tile. The one-tile kernel (matvec_fused.cu) remains the choice for small
+// weights, where a CTA's prologue would not amortise.
+//
+// Stage = NC rows x one column group (16 Q4_K super-blocks / 2048 Q8_0 codes). Consumers read stages
+// bank-conflict free with the same lane mapping and arithmetic as matvec_fused.cu. Every mbarrier wait
+// is bounded and reports through the device flag. Reference arithmetic: native/src/q4k_matmul.c:143-251,
+// native/src/q8_0_matmul.c:68-118.
+#include "common.cuh"
+#include "actquant.cuh"
+#include "tma.cuh"
+#include "matvec_fused.cuh"
+
+#include <cstdlib>
+
+namespace sk {
+
+constexpr int RG_MAX_STAGES = 8;
+constexpr size_t RG_SMEM_MAX = 200 * 1024;
+// SKAINET_RING_KB overrides the per-SM ring budget (A/B measurements)
+static size_t ring_budget() { static const size_t v = []() { const char* e = getenv("SKAINET_RING_KB"); return (size_t) (e ? atoi(e) : 190) << 10; }(); return std::min(v, RG_SMEM_MAX); }
+
+template <int NC>
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NC * 32) : "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(skd::smem_u32(bar)) : "memory");
+}
+
+// ================================================================================================
+// Q4_K. Stage: qs part [NC][16][128] then hdr part [NC][16][16].
+// ================================================================================================
+template <int NC, int EPI>
+__global__ void __launch_bounds__((NC + 1) * 32)
+q4k_matvec_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ hdr, int rows, int bpr, ActQ8K act,
+                       int cols, float* __restrict__ y, const float* __restrict__ resid, int nstages, int* __restrict__ timeout_flag) {
+    constexpr int S_QS = NC * 16 * 128, S_HDR = NC * 16 * 16, S_BYTES = S_QS + S_HDR;
+    extern __shared__ __align__(128) uint8_t smem[];
+    // layout: ring | q8 (swizzled) | split sub-block sums | d | barriers
+    uint8_t* s_ring = smem;
+    int8_t* s_q8 = (int8_t*) (s_ring + (size_t) nstages * S_BYTES);
+    uint8_t* s_bs = (uint8_t*) (s_q8 + cols);                      // 16 bytes per block
+    float* s_d = (float*) (s_bs + cols / 16);
+    uint64_t* full = (uint64_t*) ((uint8_t*) s_d + ((bpr * 4 + 15) & ~15));
+    uint64_t* empty = full + RG_MAX_STAGES;
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nrg = (rows + NC - 1) / NC;                     // row groups in the matrix
+    const int ncg = (bpr + 15) >> 4;                          // column groups per row
+    const int my_rgs = (int) blockIdx.x < nrg ? (nrg - 1 - (int) blockIdx.x) / (int) gridDim.x + 1 : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < nstages; ++s) { skd::mbar_init(full + s, 1); skd::mbar_init(empty + s, NC); }
+        skd::mbar_fence_init();
+    }
+    __syncthreads();
+    skd::pdl_launch_dependents();
+
+    if (warp == NC) {
+        // ---------------- producer: the weights depend on no predecessor ----------------
+        int stage = 0, round = 0;
+        for (int rgi = 0; rgi < my_rgs; ++rgi) {
+            const int row0 = ((int) blockIdx.x + rgi * (int) gridDim.x) * NC, nr = min(NC, rows - row0);
+            for (int cg = 0; cg < ncg; ++cg) {
+                if (round > 0 && !skd::mbar_wait_bounded(empty + stage, (round - 1) & 1, timeout_flag)) return;
+                const int b0 = cg * 16, nb = min(16, bpr - b0);
+                uint8_t* dst = s_ring + (size_t) stage * S_BYTES;
+                if (lane == 0) skd::mbar_expect_tx(full + stage, (uint32_t) nr * nb * 144);
+                __syncwarp();
+                if (bpr == 16) {               // rows are contiguous: two copies move the whole stage
+                    if (lane == 0) skd::bulk_g2s(dst, qs + (size_t) row0 * 16 * 128, (uint32_t) nr * 16 * 128, full + stage);
+                    if (lane == 1) skd::bulk_g2s(dst + S_QS, hdr + (size_t) row0 * 16 * 16, (uint32_t) nr * 16 * 16, full + stage);
+                } else if (lane < 2 * nr) {    // one row segment per lane: qs by lanes 0..nr-1, hdr by the next nr
+                    const int r = lane < nr ? lane : lane - nr;
+                    const size_t blk = (size_t) (row0 + r) * bpr + b0;
+                    if (lane < nr) skd::bulk_g2s(dst + (size_t) r * 16 * 128, qs + blk * 128, (uint32_t) nb * 128, full + stage);
+                    else skd::bulk_g2s(dst + S_QS + (size_t) r * 16 * 16, hdr + blk * 16, (uint32_t) nb * 16, full + stage);
+                }
+                if (++stage == nstages) { stage = 0; ++round; }
+            }
+        }
+        skd::pdl_wait();
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    skd::pdl_wait();                                   // the quantized activation is the predecessor's output
+    {
+        const int t = threadIdx.x;                     // 0 .. NC*32-1
+        for (int c = t; c < (cols >> 4); c += NC * 32) {
+            const int blk = c >> 4, ch = c & 15;
+            *reinterpret_cast<uint4*>(s_q8 + (size_t) blk * 256 + (ch ^ (((blk >> 1) & 1) << 1)) * 16) = skd::ld_ro(act.q + (size_t) c * 16);
+        }
+        // sub-block sums as two int8 planes (sum = 128*hi + lo): per block [hi 0..3 | lo 0..3 | hi 4..7 | lo 4..7]
+        for (int c = t; c < (cols >> 5); c += NC * 32) {
+            const int sum = (int) __ldg(act.bsums + c), hi = (sum + 64) >> 7, lo = sum - (hi << 7);
+            int8_t* dst = (int8_t*) s_bs + (size_t) (c >> 3) * 16 + ((c >> 2) & 1) * 8 + (c & 3);
+            dst[0] = (int8_t) hi; dst[4] = (int8_t) lo;
+        }
+        for (int c = t; c < bpr; c += NC * 32) s_d[c] = __ldg(act.d + c);
+    }
+    consumer_sync<NC>();
+
+    const int h = lane & 1, slot = lane >> 1, s1 = (slot >> 1) & 1;
+    const int off_lo = (h ^ (s1 << 1)) * 16, off_hi = ((2 + h) ^ (s1 << 1)) * 16;
+    int woff[4], aoff[4];
+    uint32_t ssel[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int g = (k + slot) & 3;
+        woff[k] = 32 * g; aoff[k] = 64 * g;
+        ssel[k] = (uint32_t) (2 * g) | ((uint32_t) (2 * g + 1) << 4);
+    }
+    uint4 a_lo[4], a_hi[4];
+    uint2 bs = make_uint2(0, 0);
+    float di = 0.0f;
+    int stage = 0, phase = 0;
+
+    for (int rgi = 0; rgi < my_rgs; ++rgi) {
+        const int row = ((int) blockIdx.x + rgi * (int) gridDim.x) * NC + warp;
+        float acc = 0.0f;
+        for (int cg = 0; cg < ncg; ++cg) {
+            const int b = cg * 16 + slot;
+            const bool live = b < bpr;
+            if ((ncg > 1 || rgi == 0) && live) {       // this lane's activation slice of column group cg
+                const int8_t* qa = s_q8 + (size_t) b * 256;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    a_lo[k] = skd::lds128(qa + aoff[k] + off_lo);
+                    a_hi[k] = skd::lds128(qa + aoff[k] + off_hi);
+                }
+                bs = *reinterpret_cast<const uint2*>(s_bs + (size_t) b * 16 + 8 * h);
+                di = s_d[b];
+            }
+            if (!skd::mbar_wait_bounded(full + stage, phase, timeout_flag)) return;
+            if (live && row < rows) {
+                const uint8_t* st = s_ring + (size_t) stage * S_BYTES;
+                const uint8_t* qp = st + ((size_t) warp * 16 + slot) * 128 + h * 16;
+                const uint4 hd = skd::lds128(st + S_QS + ((size_t) warp * 16 + slot) * 16);
+                const float d = __half2float(__ushort_as_half((unsigned short) (hd.x & 0xffff)));
+                const float dmin = __half2float(__ushort_as_half((unsigned short) (hd.x >> 16)));
+                uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
+                skd::k4_unpack(hd.y, hd.z, hd.w, sc_lo, sc_hi, mn_lo, mn_hi);
+                int sdot = 0;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint4 w = skd::lds128(qp + woff[k]);
+                    const uint32_t scw = __byte_perm(sc_lo, sc_hi, ssel[k]);
+                    int dl = 0, dh = 0;   // dh carries the high nibbles in place: 16 x the dot
+                    dl = __dp4a((int) (w.x & 0x0f0f0f0fu), (int) a_lo[k].x, dl);
+                    dl = __dp4a((int) (w.y & 0x0f0f0f0fu), (int) a_lo[k].y, dl);
+                    dl = __dp4a((int) (w.z & 0x0f0f0f0fu), (int) a_lo[k].z, dl);
+                    dl = __dp4a((int) (w.w & 0x0f0f0f0fu), (int) a_lo[k].w, dl);
+                    dh = skd::dp4a_us(w.x & 0xf0f0f0f0u, a_hi[k].x, dh);
+                    dh = skd::dp4a_us(w.y & 0xf0f0f0f0u, a_hi[k].y, dh);
+                    dh = skd::dp4a_us(w.z & 0xf0f0f0f0u, a_hi[k].z, dh);
+                    dh = skd::dp4a_us(w.w & 0xf0f0f0f0u, a_hi[k].w, dh);
+                    sdot = __dp2a_lo((int) __byte_perm((uint32_t) dl, (uint32_t) (dh >> 4), 0x5410), (int) scw, sdot);
+                }
+                const uint32_t mn = h ? mn_hi : mn_lo;   // lane h accounts the mins of sub-blocks 4h..4h+3
+                const int msum = (__dp4a((int) mn, (int) bs.x, 0) << 7) + __dp4a((int) mn, (int) bs.y, 0);
+                acc += di * (d * (float) sdot - dmin * (float) msum);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty + stage);   // this warp is done reading the stage
+            if (++stage == nstages) { stage = 0; phase ^= 1; }
+        }
+        const float v = skd::warp_sum(acc);
+        if (lane == 0 && row < rows) y[row] = EPI == EPI_ADD ? resid[row] + v : v;
+    }
+}
+
+// ================================================================================================
+// Q8_0. Stage: codes [NC][2048] then scales [NC][64] f16.
+// ================================================================================================
+constexpr int RG8_COLS = 2048;
+
+template <int NC, int EPI>
+__global__ void __launch_bounds__((NC + 1) * 32)
+q8_0_matvec_ring_kernel(const int8_t* __restrict__ codes, const __half* __restrict__ scales, int rows, int cols, ActSplit act,
+                        float* __restrict__ y, const float* __restrict__ resid, int nstages, int* __restrict__ timeout_flag) {
+    constexpr int S_CODES = NC * RG8_COLS, S_SC = NC * (RG8_COLS / 32) * 2, S_BYTES = S_CODES + S_SC;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int bpr = cols >> 5;
+    uint8_t* s_ring = smem;
+    int8_t* s_hi = (int8_t*) (s_ring + (size_t) nstages * S_BYTES);
+    int8_t* s_lo = s_hi + cols;
+    float* s_dx = (float*) (s_lo + cols);
+    uint64_t* full = (uint64_t*) ((uint8_t*) s_dx + ((bpr * 4 + 15) & ~15));
+    uint64_t* empty = full + RG_MAX_STAGES;
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nrg = (rows + NC - 1) / NC;
+    const int ncg = (cols + RG8_COLS - 1) / RG8_COLS;
+    const int my_rgs = (int) blockIdx.x < nrg ? (nrg - 1 - (int) blockIdx.x) / (int) gridDim.x + 1 : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < nstages; ++s) { skd::mbar_init(full + s, 1); skd::mbar_init(empty + s, NC); }
+        skd::mbar_fence_init();
+    }
+    __syncthreads();
+    skd::pdl_launch_dependents();
+
+    if (warp == NC) {
+        int stage = 0, round = 0;
+        for (int rgi = 0; rgi < my_rgs; ++rgi) {
+            const int row0 = ((int) blockIdx.x + rgi * (int) gridDim.x) * NC, nr = min(NC, rows - row0);
+            for (int cg = 0; cg < ncg; ++cg) {
+                if (round > 0 && !skd::mbar_wait_bounded(empty + stage, (round - 1) & 1, timeout_flag)) return;
+                const int c0 = cg * RG8_COLS, nc = min(RG8_COLS, cols - c0);
+                uint8_t* dst = s_ring + (size_t) stage * S_BYTES;
+                if (lane == 0) skd::mbar_expect_tx(full + stage, (uint32_t) nr * (nc + nc / 16));
+                __syncwarp();
+                if (lane < 2 * nr) {
+                    const int r = lane < nr ? lane : lane - nr;
+                    if (lane < nr) skd::bulk_g2s(dst + (size_t) r * RG8_COLS, codes + (size_t) (row0 + r) * cols + c0, (uint32_t) nc, full + stage);
+                    else skd::bulk_g2s(dst + S_CODES + (size_t) r * (RG8_COLS / 16), scales + (size_t) (row0 + r) * bpr + (c0 >> 5), (uint32_t) nc / 16, full + stage);
+                }
+                if (++stage == nstages) { stage = 0; ++round; }
+            }
+        }
+        skd::pdl_wait();
+        return;
+    }
+
+    skd::pdl_wait();
+    {
+        const int t = threadIdx.x;
+        for (int c = t; c < (cols >> 4); c += NC * 32) {
+            *reinterpret_cast<uint4*>(s_hi + (size_t) c * 16) = skd::ld_ro(act.hi + (size_t) c * 16);
+            *reinterpret_cast<uint4*>(s_lo + (size_t) c * 16) = skd::ld_ro(act.lo + (size_t) c * 16);
+        }
+        for (int c = t; c < bpr; c += NC * 32) s_dx[c] = __ldg(act.d + c);
+    }
+    consumer_sync<NC>();
+
+    uint4 ah[4], al[4];
+    float dx[4];
+    int stage = 0, phase = 0;
+    for (int rgi = 0; rgi < my_rgs; ++rgi) {
+        const int row = ((int) blockIdx.x + rgi * (int) gridDim.x) * NC + warp;
+        float acc = 0.0f;
+        for (int cg = 0; cg < ncg; ++cg) {
+            const int c0 = cg * RG8_COLS, nc = min(RG8_COLS, cols - c0);
+            if (ncg > 1 || rgi == 0) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int c = j * 512 + lane * 16;            // code offset inside the column group
+                    if (c < nc) {
+                        ah[j] = skd::lds128(s_hi + c0 + c); al[j] = skd::lds128(s_lo + c0 + c);
+                        dx[j] = s_dx[(c0 + c) >> 5];
+                    } else { ah[j] = make_uint4(0, 0, 0, 0); al[j] = ah[j]; dx[j] = 0.0f; }
+                }
+            }
+            if (!skd::mbar_wait_bounded(full + stage, phase, timeout_flag)) return;
+            if (row < rows) {
+                const uint8_t* st = s_ring + (size_t) stage * S_BYTES;
+                const int8_t* wr = (const int8_t*) st + (size_t) warp * RG8_COLS;
+                const __half* sr = (const __half*) (st + S_CODES) + (size_t) warp * (RG8_COLS / 32);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int c = j * 512 + lane * 16;
+                    if (c < nc) {
+                        const uint4 w = skd::lds128(wr + c);
+                        int dh = 0, dl = 0;
+                        dh = __dp4a((int) w.x, (int) ah[j].x, dh); dh = __dp4a((int) w.y, (int) ah[j].y, dh);
+                        dh = __dp4a((int) w.z, (int) ah[j].z, dh); dh = __dp4a((int) w.w, (int) ah[j].w, dh);
+                        dl = __dp4a((int) w.x, (int) al[j].x, dl); dl = __dp4a((int) w.y, (int) al[j].y, dl);
+                        dl = __dp4a((int) w.z, (int) al[j].z, dl); dl = __dp4a((int) w.w, (int) al[j].w, dl);
+                        acc += (__half2float(sr[c >> 5]) * dx[j]) * (float) (dh * 128 + dl);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty + stage);
+            if (++stage == nstages) { stage = 0; phase ^= 1; }
+        }
+        const float v = skd::warp_sum(acc);
+        if (lane == 0 && row < rows) y[row] = EPI == EPI_ADD ? resid[row] + v : v;
+    }
+}
+
+// ================================================================================================
+// dispatch (m = 1, activation already quantized). Returns 1 when the shape is outside what these take.
+// ================================================================================================
+struct RingPlan { int nc, cps, nstages; size_t smem; };
+
+// As many consumer warps per SM as the shared-memory budget allows with at least three stages per ring.
+static bool plan_ring(size_t fixed, size_t stage_bytes_per_row, RingPlan* p) {
+    const int ncs[4] = {4, 4, 8, 8}, cpss[4] = {4, 3, 2, 1};
+    for (int i = 0; i < 4; ++i) {
+        const size_t per_cta = ring_budget() / cpss[i];
+        const size_t sb = stage_bytes_per_row * ncs[i];
+        if (per_cta <= fixed + 256) continue;
+        const int ns = (int) std::min<size_t>(RG_MAX_STAGES, (per_cta - fixed - 256) / sb);
+        if (ns >= 3) { p->nc = ncs[i]; p->cps = cpss[i]; p->nstages = ns; p->smem = fixed + 256 + ns * sb; return true; }
+    }
+    return false;
+}
+
+template <typename K>
+static int32_t set_smem_once(K kernel, bool* done) {
+    if (!*done) {
+        SK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) RG_SMEM_MAX + 1024));
+        *done = true;
+    }
+    return SKAINET_CUDA_OK;
+}
+
+#define SK_RG_LAUNCH(KERNEL, NCV, ...)                                                                        \
+    do {                                                                                                      \
+        static bool done = false;                                                                             \
+        SK_TRY(set_smem_once(KERNEL, &done));                                                                 \
+        const int nrg = (w.rows + NCV - 1) / NCV;                                                             \
+        const int grid = std::min(sm_count() * plan.cps, nrg);                                                \
+        SK_CUDA(launch_pdl(KERNEL, dim3(grid), dim3((NCV + 1) * 32), plan.smem, s, __VA_ARGS__));             \
+        return SKAINET_CUDA_OK;                                                                               \
+    } while (0)
+
+template <int EPI>
+static int32_t launch_q4k_ring(const Weight& w, ActQ8K a, float* y, const float* resid, const RingPlan& plan, int* flag, cudaStream_t s) {
+    if (plan.nc == 4)
+        SK_RG_LAUNCH((q4k_matvec_ring_kernel<4, EPI>), 4, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr, a, w.cols, y, resid, plan.nstages, flag);
+    SK_RG_LAUNCH((q4k_matvec_ring_kernel<8, EPI>), 8, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr, a, w.cols, y, resid, plan.nstages, flag);
+}
+template <int EPI>
+static int32_t launch_q8_ring(const Weight& w, ActSplit a, float* y, const float* resid, const RingPlan& plan, int* flag, cudaStream_t s) {
+    if (plan.nc == 4)
+        SK_RG_LAUNCH((q8_0_matvec_ring_kernel<4, EPI>), 4, (const int8_t*) w.qs, (const __half*) w.hdr, w.rows, w.cols, a, y, resid, plan.nstages, flag);
+    SK_RG_LAUNCH((q8_0_matvec_ring_kernel<8, EPI>), 8, (const int8_t*) w.qs, (const __half*) w.hdr, w.rows, w.cols, a, y, resid, plan.nstages, flag);
+}
+
+int32_t launch_matvec_ring(const Weight& w, const MatvecIn& in, float* y, const float* resid, cudaStream_t s) {
+    int* flag = device_timeout_flag();
+    if (w.rows <= 0) return 1;
+    RingPlan plan;
+    if (w.enc == SKAINET_ENC_Q4_K) {
+        const size_t fixed = (size_t) w.cols + w.cols / 16 + ((w.bpr * 4 + 15) & ~15) + 2 * RG_MAX_STAGES * 8;
+        if (!plan_ring(fixed, 16 * 144, &plan)) return 1;
+        return resid ? launch_q4k_ring<EPI_ADD>(w, in.q8, y, resid, plan, flag, s) : launch_q4k_ring<EPI_STORE>(w, in.q8, y, resid, plan, flag, s);
+    }
+    if (w.enc == SKAINET_ENC_Q8_0) {
+        if (w.cols % 256 != 0) return 1;
+        const size_t fixed = (size_t) 2 * w.cols + ((w.bpr * 4 + 15) & ~15) + 2 * RG_MAX_STAGES * 8;
+        if (!plan_ring(fixed, RG8_COLS + RG8_COLS / 16, &plan)) return 1;
+        return resid ? launch_q8_ring<EPI_ADD>(w, in.split, y, resid, plan, flag, s) : launch_q8_ring<EPI_STORE>(w, in.split, y, resid, plan, flag, s);
+    }
+    return 1;
+}
+
+}  // namespace sk
