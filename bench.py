@@ -55,6 +55,12 @@ def algorithmic_bytes(enc_bytes: int, enc_elems: int, rows: int, cols: int, m: i
     return rows * (cols // enc_elems) * enc_bytes + 4 * m * (rows + cols)
 
 
+# DRAM bytes (read + write) per algorithmic byte of the weight-streaming matvec kernels, from ncu captures of
+# q4k_matvec_ring_kernel: 25.387 MB per 11008x4096 launch against 25.362 MB algorithmic, 264.27 MB per
+# 57344x8192 launch against 264.24 MB.  Traffic grows in proportion to the weight bytes (each byte is read once).
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.001
+
+
 def load_peaks() -> tuple[float, str]:
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -365,8 +371,10 @@ def run_matvec(args) -> None:
             "metric": f"{args.workload}_hbm_gbs", "value": achieved * world, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": dtype_of(args.workload), "data": "synthetic", "config": workload_config(args, world, {"weights_per_shape": copies}),
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                         "peak_kind": peak_kind, "kernel": "q4k_matvec_fused_kernel" if enc == "Q4_K" else "q8_0_matvec_fused_kernel",
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": bytes_per_step / len(weights) * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE,
+                         "traffic_source": "ncu dram bytes per launch of the 11008x4096 Q4_K capture, scaled by weight bytes",
+                         "peak_kind": peak_kind, "kernel": "q4k_matvec_ring_kernel" if enc == "Q4_K" else "q8_0_matvec_fused_kernel",
                          "avg_launch_us": per_launch_us,
                          "read_floor_us": floor_ms * 1e3 / len(weights), "read_floor_gbs": bytes_per_step / (floor_ms * 1e-3) / 1e9,
                          "note": "avg launch = timed region / matvec launches; the activation quantizer and launch gaps are inside it. "
@@ -469,8 +477,10 @@ def run_decode(args) -> None:
             "metric": "decode_tokens_per_s", "value": batch * args.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": dtype_of(args.workload), "data": "synthetic", "config": workload_config(args, world),
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                         "peak_kind": peak_kind, "kernel": "q4k_matvec_fused_kernel", "avg_launch_us": mv_ms * 1e3 / len(ws),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": mv_bytes / len(ws) * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE,
+                         "traffic_source": "ncu dram bytes per launch of q4k_matvec_ring_kernel captures, scaled by weight bytes",
+                         "peak_kind": peak_kind, "kernel": "q4k_matvec_ring_kernel", "avg_launch_us": mv_ms * 1e3 / len(ws),
                          "note": "per GPU: the fused matvec path (quantizer + matvec) swept over this rank's own weights, bytes / time",
                          "step_bytes_per_gpu": bytes_step, "step_gbs_per_gpu": step_gbs, "step_frac": step_gbs / peak},
             "e2e": {"value": (batch * e2e_steps / (e2e_ms * 1e-3)) if e2e_steps else None, "unit": "tokens/s",

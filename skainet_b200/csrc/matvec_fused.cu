@@ -452,7 +452,7 @@ int32_t launch_matvec_fused(const Weight& w, const MatvecIn& in, int prep, float
     int* flag = device_timeout_flag();
     if (w.rows <= 0) return 1;
     // Large weights go to the persistent ring kernel (SKAINET_RING_MIN_MB overrides the size threshold).
-    static const int64_t ring_min = []() { const char* e = getenv("SKAINET_RING_MIN_MB"); return (int64_t) (e ? atoi(e) : 12) << 20; }();
+    static const int64_t ring_min = []() { const char* e = getenv("SKAINET_RING_MIN_MB"); return (int64_t) (e ? atoi(e) : 20) << 20; }();
     if (prep == PREP_QUANTIZED && w.packed_bytes >= ring_min) {
         const int32_t st = launch_matvec_ring(w, in, y, resid, s);
         if (st != 1) return st;
