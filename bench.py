@@ -47,6 +47,8 @@ MATVEC_WORKLOADS = {
     "q8_0_matvec": ("Q8_0", [(4096, 4096)], 34, 32),
 }
 DECODE_WORKLOADS = {"decode_70b": ("70b", 4096), "decode_7b": ("7b", 512)}
+# decode attention alone: (query heads, kv heads, head_dim); context from --context
+ATTN_WORKLOADS = {"attn_decode": (64, 8, 128)}
 BLOCK = {"Q4_K": (144, 256), "Q8_0": (34, 32)}
 
 
@@ -195,6 +197,25 @@ def cpu_decode_rate(model: str, ctx: int, budget_s: float) -> dict:
             "seconds": t_tok}
 
 
+def cpu_attn_rate(workload: str, ctx: int, batch: int) -> dict:
+    """The reference's fused fp32 SDPA (skainet_f32_sdpa, one query row per head) on the same shape; the
+    rate is quoted on the f16 cache bytes the GPU path reads, so the two are comparable."""
+    from oracle import ref as R
+    h, hkv, d = ATTN_WORKLOADS[workload]
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal((1, h, 1, d), dtype=np.float32)
+    k = rng.standard_normal((1, hkv, ctx, d), dtype=np.float32)
+    v = rng.standard_normal((1, hkv, ctx, d), dtype=np.float32)
+    use_ref = R.ref() is not None
+    R.sdpa(q, k, v, d ** -0.5, causal=False, use_ref=use_ref)
+    t0 = time.perf_counter(); n = 0
+    while time.perf_counter() - t0 < 3.0:
+        R.sdpa(q, k, v, d ** -0.5, causal=False, use_ref=use_ref); n += 1
+    dt = (time.perf_counter() - t0) / n
+    return {"value": 2 * hkv * ctx * d * 2 / dt / 1e9, "unit": "GB/s", "cores": 1, "kind": "reference" if use_ref else "port",
+            "sample": f"one sequence of the batch, fp32 K/V on the host, {n} calls", "seconds": dt * n}
+
+
 def run_reference(args) -> None:
     rank, _, _ = dist_env()
     if rank != 0:
@@ -204,6 +225,8 @@ def run_reference(args) -> None:
     for i in range(args.warmup + args.steps):
         if args.workload in MATVEC_WORKLOADS:
             r = cpu_matvec_rate(args.workload, budget); unit = "GB/s"; metric = f"{args.workload}_hbm_gbs"
+        elif args.workload in ATTN_WORKLOADS:
+            r = cpu_attn_rate(args.workload, args.context, max(1, args.batch)); unit = "GB/s"; metric = "attn_decode_hbm_gbs"
         else:
             model, ctx = DECODE_WORKLOADS[args.workload]
             r = cpu_decode_rate(model, ctx, budget); unit = "tokens/s"; metric = "decode_tokens_per_s"
@@ -220,6 +243,8 @@ def run_reference(args) -> None:
 
 
 def dtype_of(workload: str) -> str:
+    if workload in ATTN_WORKLOADS:
+        return "f16 K/V, f32 q split in two f16 terms, f32 accumulate"
     if workload == "q8_0_matvec":
         return "int8 x int8 (two-term activation) -> int32, f32 accumulate"
     return "int8 x int4 -> int32, f32 accumulate (attention and norms f32, KV f16)" if workload in DECODE_WORKLOADS \
@@ -227,7 +252,11 @@ def dtype_of(workload: str) -> str:
 
 
 def workload_config(args, world: int, extra: dict | None = None) -> dict:
-    if args.workload in MATVEC_WORKLOADS:
+    if args.workload in ATTN_WORKLOADS:
+        h, hkv, d = ATTN_WORKLOADS[args.workload]
+        c = {"workload": args.workload, "heads": h, "kv_heads": hkv, "head_dim": d, "batch": max(1, args.batch), "context": args.context,
+             "kv": "f16 resident, N(0,1)", "l2": "rotating distinct caches larger than 2x L2 per sweep"}
+    elif args.workload in MATVEC_WORKLOADS:
         enc, shapes, _, _ = MATVEC_WORKLOADS[args.workload]
         c = {"workload": args.workload, "encoding": enc, "shapes_out_in": shapes, "m": 1,
              "l2": "rotating distinct weights larger than 2x L2 per sweep", "activation": "fp32 N(0,1)",
@@ -395,6 +424,79 @@ def run_matvec(args) -> None:
 # ---------------------------------------------------------------------------------------------------
 # our arm: decode
 # ---------------------------------------------------------------------------------------------------
+def run_attn(args) -> None:
+    """Decode attention alone through skainet_cuda_attn_decode_dev: one query row per head against a
+    resident f16 cache. Bytes per call = the K and V rows it must read."""
+    import torch
+    from skainet_b200 import _lib as L, device
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local); device.set_device(local)
+    info = device.device_info()
+    h, hkv, d = ATTN_WORKLOADS[args.workload]
+    batch, ctx = max(1, args.batch), args.context
+    stride = ctx + 64
+    call_bytes = 2 * batch * hkv * ctx * d * 2
+    copies = int(min(max(2, np.ceil(2.2 * info["l2_bytes"] / call_bytes)), max(2, (4 << 30) // (2 * batch * hkv * stride * d * 2))))
+    gen = torch.Generator(device="cuda").manual_seed(7 + rank)
+    ks = [torch.randn(batch, hkv, stride, d, device="cuda", generator=gen).half() for _ in range(copies)]
+    vs = [torch.randn(batch, hkv, stride, d, device="cuda", generator=gen).half() for _ in range(copies)]
+    q = torch.randn(batch, h * d, device="cuda", generator=gen)
+    out = torch.empty(batch, h * d, device="cuda")
+    lens = torch.full((batch,), ctx, device="cuda", dtype=torch.int32)
+    stream = torch.cuda.Stream(); sp = stream.cuda_stream
+
+    def sweep():
+        for k, v in zip(ks, vs):
+            device.attn_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), batch, h, hkv, d, stride, lens.data_ptr(), ctx,
+                               d ** -0.5, 0, sp)
+
+    warm = max(3, args.warmup)
+    with torch.cuda.stream(stream):
+        sweep(); stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            sweep()
+        for _ in range(warm):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        clk = ClockSampler(local); clk.start()
+        stream.synchronize(); e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream); stream.synchronize()
+        clocks = clk.stop()
+    ms_step = e0.elapsed_time(e1) / args.steps
+    # end to end: q from pinned host memory, result back, per call
+    hq = torch.randn(batch, h * d).pin_memory(); hout = torch.empty(batch, h * d).pin_memory()
+    e2e_ms = None
+    if not args.skip_e2e:
+        with torch.cuda.stream(stream):
+            def e2e_sweep():
+                for k, v in zip(ks, vs):
+                    q.copy_(hq, non_blocking=True)
+                    device.attn_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), batch, h, hkv, d, stride, lens.data_ptr(),
+                                       ctx, d ** -0.5, 0, sp)
+                    hout.copy_(out, non_blocking=True); stream.synchronize()
+            e2e_sweep()
+            t0 = time.perf_counter(); e2e_sweep(); e2e_ms = (time.perf_counter() - t0) * 1e3
+    peak, peak_kind = load_peaks()
+    achieved = call_bytes * copies / (ms_step * 1e-3) / 1e9
+    line = {"metric": "attn_decode_hbm_gbs", "value": achieved, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": warm,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 K/V, f32 q split in two f16 terms, f32 accumulate", "data": "synthetic",
+            "config": workload_config(args, 1, {"caches": copies}),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "peak_kind": peak_kind, "kernel": "attn_decode_mma_kernel", "avg_launch_us": ms_step * 1e3 / copies,
+                         "note": "avg launch = timed region / calls; each call is the split-K kernel plus its merge"},
+            "e2e": {"value": (call_bytes * copies / (e2e_ms * 1e-3) / 1e9) if e2e_ms else None, "unit": "GB/s",
+                    "h2d_bytes_per_step": 4 * batch * h * d * copies, "d2h_bytes_per_step": 4 * batch * h * d * copies},
+            "gpu_launches": 2 * copies * args.steps, "clocks": clocks}
+    if not args.skip_cpu:
+        cpu = cpu_attn_rate(args.workload, ctx, batch)
+        line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line), flush=True)
+
+
 def run_decode(args) -> None:
     import torch
     import torch.distributed as dist
@@ -502,7 +604,8 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="decode_70b", choices=sorted(MATVEC_WORKLOADS) + sorted(DECODE_WORKLOADS))
+    ap.add_argument("--workload", default="decode_70b", choices=sorted(MATVEC_WORKLOADS) + sorted(DECODE_WORKLOADS) + sorted(ATTN_WORKLOADS))
+    ap.add_argument("--context", type=int, default=4096, help="keys per sequence (attn_decode workload)")
     ap.add_argument("--batch", type=int, default=1, help="sequences decoded together (decode workloads)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-cpu", action="store_true", help="omit the cpu_baseline leg (profiling runs)")
@@ -512,6 +615,8 @@ def main() -> None:
         run_reference(args)
     elif args.workload in MATVEC_WORKLOADS:
         run_matvec(args)
+    elif args.workload in ATTN_WORKLOADS:
+        run_attn(args)
     else:
         run_decode(args)
 

@@ -163,23 +163,62 @@ attn_decode_kernel(const float* __restrict__ q, const __half* __restrict__ kc, c
     }
 }
 
+// Merge of split-K partial records {max, sum, acc[D]}: thread (group, element) folds the splits
+// group, group+MG, .. in chunks of eight whose loads are all issued before the first use (one memory
+// round trip per chunk), then the MG groups are folded in a fixed order through shared memory. Returns
+// the merged output element to the threads of group 0; the other groups get 0.
+constexpr int MG = 4;          // split groups per CTA
+template <int D, int E>        // E = elements per CTA
+__device__ __forceinline__ float merge_splits(const float* __restrict__ rec, int splits, int dd, int e, int grp, float (*sm)[MG][E]) {
+    float mx = MASKED, lt = 0.0f, at = 0.0f;
+    for (int s0 = grp * 8; s0 < splits; s0 += MG * 8) {
+        float mm[8], ll[8], aa[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const bool live = s0 + i < splits;
+            const float* r = rec + (int64_t) (s0 + i) * (D + 2);
+            mm[i] = live ? __ldg(r) : MASKED;
+            ll[i] = live ? __ldg(r + 1) : 0.0f;
+            aa[i] = live ? __ldg(r + 2 + dd) : 0.0f;
+        }
+        float cm = mx;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) cm = fmaxf(cm, mm[i]);
+        const float c0 = expf(mx - cm);
+        lt *= c0; at *= c0; mx = cm;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float c = expf(mm[i] - cm);
+            lt += c * ll[i];
+            at += c * aa[i];
+        }
+    }
+    sm[0][grp][e] = mx; sm[1][grp][e] = lt; sm[2][grp][e] = at;
+    __syncthreads();
+    if (grp != 0) return 0.0f;
+    float m2 = mx;
+#pragma unroll
+    for (int g2 = 1; g2 < MG; ++g2) m2 = fmaxf(m2, sm[0][g2][e]);
+    float l2 = 0.0f, a2 = 0.0f;
+#pragma unroll
+    for (int g2 = 0; g2 < MG; ++g2) {
+        const float c = expf(sm[0][g2][e] - m2);
+        l2 += c * sm[1][g2][e];
+        a2 += c * sm[2][g2][e];
+    }
+    return l2 > 0.0f ? a2 / l2 : 0.0f;
+}
+
+// grid batch*heads, D*MG threads
 template <int D>
-__global__ void attn_merge_kernel(const float* __restrict__ part, float* __restrict__ out, int splits) {
+__global__ void __launch_bounds__(D * MG) attn_merge_kernel(const float* __restrict__ part, float* __restrict__ out, int splits) {
+    __shared__ float sm[3][MG][D];
     skd::pdl_launch_dependents();
     skd::pdl_wait();
     const int64_t bh = blockIdx.x;
-    const float* rec = part + bh * splits * (D + 2);
-    float mx = MASKED;
-    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, rec[s * (D + 2)]);
-    for (int dd = threadIdx.x; dd < D; dd += blockDim.x) {
-        float lt = 0.0f, at = 0.0f;
-        for (int s = 0; s < splits; ++s) {
-            const float c = expf(rec[s * (D + 2)] - mx);
-            lt += c * rec[s * (D + 2) + 1];
-            at += c * rec[s * (D + 2) + 2 + dd];
-        }
-        out[bh * D + dd] = lt > 0.0f ? at / lt : 0.0f;
-    }
+    const int dd = threadIdx.x % D, grp = threadIdx.x / D;
+    const float v = merge_splits<D, D>(part + bh * splits * (D + 2), splits, dd, dd, grp, sm);
+    if (grp == 0) out[bh * D + dd] = v;
 }
 
 // =================================================================================================
@@ -210,7 +249,10 @@ __device__ __forceinline__ void split_pack(float x, float y, uint32_t& hi, uint3
     lo = (uint32_t) __half_as_ushort(lx) | ((uint32_t) __half_as_ushort(ly) << 16);
 }
 
-constexpr int AM_WARPS = 4;
+constexpr int AM_WARPS = 8;
+constexpr float LOG2E = 1.4426950408889634f;
+// exp(x) for x <= 0 through the ex2 unit (relative error ~1e-7 after the fp32 pre-scale)
+__device__ __forceinline__ float fast_exp(float x) { return exp2f(x * LOG2E); }
 
 template <int D>
 __global__ void __launch_bounds__(AM_WARPS * 32)
@@ -221,51 +263,28 @@ attn_decode_mma_kernel(const float* __restrict__ q, int64_t q_row_stride, const 
     constexpr int KS = D / 16;     // k-steps of the score contraction
     constexpr int U = D / 64;      // chunks of a V row per lane
     constexpr int NT = D / 8;      // 8-dim output tiles
-    __shared__ float sm_m[AM_WARPS][8], sm_l[AM_WARPS][8];
-    __shared__ float sm_acc[AM_WARPS][8][D];
+    __shared__ float sm_m[AM_WARPS][8], sm_l[AM_WARPS][8], sm_c[AM_WARPS][8];
+    __shared__ uint32_t sm_q[KS][4][32];
+    __shared__ float sm_acc[AM_WARPS][8][D + 4];
     skd::pdl_launch_dependents();
     skd::pdl_wait();
 
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    const int len = kv_len[b];
+    const int len = __ldg(kv_len + b);
     int first = 0;
     if (window > 0 && len - window > first) first = len - window;
     const int begin = max(first, split * chunk), stop = min(len, (split + 1) * chunk);
-
-    // q of head g as A fragments: per k-step {hi(k 2t..), lo(k 2t..), hi(k 2t+8..), lo(k 2t+8..)}
-    uint32_t qa[KS][4];
-    {
-        const float* qp = q + (int64_t) b * q_row_stride + (int64_t) (kvh * G + g) * D;
-#pragma unroll
-        for (int s = 0; s < S4; ++s) {
-            float f[8];
-            if (g < G) {
-                const float4 a = __ldg((const float4*) (qp + (t + 4 * s) * 8)), c = __ldg((const float4*) (qp + (t + 4 * s) * 8) + 1);
-                f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = c.x; f[5] = c.y; f[6] = c.z; f[7] = c.w;
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) f[i] = 0.0f;
-            }
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                split_pack(f[4 * j], f[4 * j + 1], qa[2 * s + j][0], qa[2 * s + j][1]);
-                split_pack(f[4 * j + 2], f[4 * j + 3], qa[2 * s + j][2], qa[2 * s + j][3]);
-            }
-        }
-    }
-    float m = MASKED, l = 0.0f;
-    float o[NT][4];
-#pragma unroll
-    for (int i = 0; i < NT; ++i) { o[i][0] = 0.f; o[i][1] = 0.f; o[i][2] = 0.f; o[i][3] = 0.f; }
 
     const __half* kb = kc + ((int64_t) b * kv_heads + kvh) * cache_stride * D;
     const __half* vb = vc + ((int64_t) b * kv_heads + kvh) * cache_stride * D;
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
 
-    for (int k0 = begin + warp * 16; k0 < stop; k0 += AM_WARPS * 16) {
-        // ---- loads of the 16-key tile: K as (key g | g+8, chunks t+4s), V as (keys 2t,2t+1,2t+8,2t+9, chunks g+8u)
-        uint4 kr[2][S4], vr[4][U];
+    // loads of a 16-key tile: K as (key g | g+8, chunks t+4s), V as (keys 2t,2t+1,2t+8,2t+9, chunks g+8u).
+    // Two tiles (A, B) are kept in flight per warp: with one CTA of eight warps per SM that is 128 KB of
+    // loads outstanding per SM, enough to cover the HBM latency at full bandwidth.
+    uint4 krA[2][S4], vrA[4][U], krB[2][S4], vrB[4][U];
+    auto load_tile = [&](uint4 (&kr)[2][S4], uint4 (&vr)[4][U], int k0) {
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
             const int key = k0 + 8 * nt + g;
@@ -278,6 +297,35 @@ attn_decode_mma_kernel(const float* __restrict__ q, int64_t q_row_stride, const 
 #pragma unroll
             for (int u = 0; u < U; ++u) vr[kk][u] = key < stop ? skd::ld_stream(vb + (int64_t) key * D + (g + 8 * u) * 8) : zero4;
         }
+    };
+    constexpr int STEP = AM_WARPS * 16;
+    int k0 = begin + warp * 16;
+    if (k0 < stop) load_tile(krA, vrA, k0);          // in flight while q is fetched and split below
+    if (k0 + STEP < stop) load_tile(krB, vrB, k0 + STEP);
+
+    // q of head g as A fragments, per k-step {hi(k 2t..), lo(k 2t..), hi(k 2t+8..), lo(k 2t+8..)}: warp w
+    // converts k-step w (k-step 2s+j covers floats 4j..4j+3 of chunk t+4s) and all warps read the result.
+    for (int ks = warp; ks < KS; ks += AM_WARPS) {
+        float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (g < G) f = __ldg((const float4*) (q + (int64_t) b * q_row_stride + (int64_t) (kvh * G + g) * D + (t + 4 * (ks >> 1)) * 8 + 4 * (ks & 1)));
+        uint32_t h0, l0, h1, l1;
+        split_pack(f.x, f.y, h0, l0);
+        split_pack(f.z, f.w, h1, l1);
+        sm_q[ks][0][lane] = h0; sm_q[ks][1][lane] = l0; sm_q[ks][2][lane] = h1; sm_q[ks][3][lane] = l1;
+    }
+    __syncthreads();
+    uint32_t qa[KS][4];
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) qa[ks][j] = sm_q[ks][j][lane];
+
+    float m = MASKED, l = 0.0f;
+    float o[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) { o[i][0] = 0.f; o[i][1] = 0.f; o[i][2] = 0.f; o[i][3] = 0.f; }
+
+    auto tile = [&](const uint4 (&kr)[2][S4], const uint4 (&vr)[4][U], int k0) {
         // ---- scores of head g for keys k0 + {2t, 2t+1, 8+2t, 8+2t+1}
         float sc[4];
 #pragma unroll
@@ -296,14 +344,17 @@ attn_decode_mma_kernel(const float* __restrict__ q, int64_t q_row_stride, const 
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
         const float mnew = fmaxf(m, mx);
-        const float corr = expf(m - mnew);
+        const float corr = fast_exp(m - mnew);
+        const bool rescale = m != mnew && l != 0.0f;      // nothing to rescale before the first key or when the max holds
         m = mnew;
         float p[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) p[i] = sc[i] > 0.5f * MASKED ? expf(sc[i] - mnew) : 0.0f;
+        for (int i = 0; i < 4; ++i) p[i] = sc[i] > 0.5f * MASKED ? fast_exp(sc[i] - mnew) : 0.0f;
         l = l * corr + (p[0] + p[1]) + (p[2] + p[3]);
+        if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
-        for (int i = 0; i < NT; ++i) { o[i][0] *= corr; o[i][1] *= corr; o[i][2] *= corr; o[i][3] *= corr; }
+            for (int i = 0; i < NT; ++i) { o[i][0] *= corr; o[i][1] *= corr; o[i][2] *= corr; o[i][3] *= corr; }
+        }
         uint32_t pa[4];
         split_pack(p[0], p[1], pa[0], pa[1]);
         split_pack(p[2], p[3], pa[2], pa[3]);
@@ -318,7 +369,17 @@ attn_decode_mma_kernel(const float* __restrict__ q, int64_t q_row_stride, const 
                 mma_f16(o[u * 8 + 2 * r + 1], pa, __byte_perm(v0[r], v1[r], 0x7632), __byte_perm(v8[r], v9[r], 0x7632));
             }
         }
+    };
+    while (k0 < stop) {
+        tile(krA, vrA, k0);
+        if (k0 + 2 * STEP < stop) load_tile(krA, vrA, k0 + 2 * STEP);
+        k0 += STEP;
+        if (k0 >= stop) break;
+        tile(krB, vrB, k0);
+        if (k0 + 2 * STEP < stop) load_tile(krB, vrB, k0 + 2 * STEP);
+        k0 += STEP;
     }
+    // the per-lane sums of l cover different keys; m is already uniform over the four lanes of a head
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
     // ---- merge the warps (fixed order), one partial record per (batch, head, split)
@@ -331,61 +392,66 @@ attn_decode_mma_kernel(const float* __restrict__ q, int64_t q_row_stride, const 
             sm_acc[warp][g][8 * (2 * t + 1 + 8 * u) + i] = o[u * 8 + i][1] + o[u * 8 + i][3];
         }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < G * D; idx += AM_WARPS * 32) {
-        const int hg = idx / D, dd = idx % D;
+    if (threadIdx.x < 8 * AM_WARPS) {       // weight of (warp w, head hg) in the merged record
+        const int w = threadIdx.x >> 3, hg = threadIdx.x & 7;
         float mxx = MASKED;
 #pragma unroll
-        for (int w = 0; w < AM_WARPS; ++w) mxx = fmaxf(mxx, sm_m[w][hg]);
-        float lt = 0.0f, at = 0.0f;
+        for (int w2 = 0; w2 < AM_WARPS; ++w2) mxx = fmaxf(mxx, sm_m[w2][hg]);
+        sm_c[w][hg] = fast_exp(sm_m[w][hg] - mxx);
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * D; idx += AM_WARPS * 32) {
+        const int hg = idx / D, dd = idx % D;
+        float at = 0.0f;
 #pragma unroll
-        for (int w = 0; w < AM_WARPS; ++w) {
-            const float c = expf(sm_m[w][hg] - mxx);
-            lt += c * sm_l[w][hg];
-            at += c * sm_acc[w][hg][dd];
-        }
+        for (int w = 0; w < AM_WARPS; ++w) at += sm_c[w][hg] * sm_acc[w][hg][dd];
         float* rec = part + (((int64_t) b * heads + kvh * G + hg) * splits + split) * (D + 2);
         rec[2 + dd] = at;
-        if (dd == 0) { rec[0] = mxx; rec[1] = lt; }
+        if (dd == 0) {
+            float mxx = MASKED, lt = 0.0f;
+#pragma unroll
+            for (int w = 0; w < AM_WARPS; ++w) { mxx = fmaxf(mxx, sm_m[w][hg]); lt += sm_c[w][hg] * sm_l[w][hg]; }
+            rec[0] = mxx; rec[1] = lt;
+        }
     }
 }
 
+static int attn_min_keys() {
+    static const int min_keys = []() { const char* e = getenv("SKAINET_ATTN_MIN_KEYS"); return e ? std::max(16, atoi(e)) : 128; }();
+    return min_keys;
+}
 static int decode_splits(int batch, int kv_heads, int max_kv_len) {
+    // One wave: the split-K kernel holds one CTA of eight warps per SM (register-bound), and a second wave
+    // would double its time. Each split gets at least min_keys keys (one 16-key tile per warp at 128).
     const int ctas = batch * kv_heads;
-    int want = (sm_count() * 4 + ctas - 1) / ctas;            // ~4 CTAs of 128 threads per SM
-    const int by_len = (max_kv_len + 127) / 128;              // at least 128 keys per split
+    int want = std::max(1, sm_count() / ctas);
+    const int min_keys = attn_min_keys();
+    const int by_len = (max_kv_len + min_keys - 1) / min_keys;
     want = std::max(1, std::min(want, by_len));
     return std::min(want, 256);
 }
 
 size_t attn_scratch_bytes(int batch, int heads, int head_dim, int max_kv_len) {
     // kv_heads is not known here; the bound below holds for any grouping (splits <= 256).
-    const int splits = std::min(256, std::max(1, (max_kv_len + 127) / 128));
+    const int splits = std::min(256, std::max(1, (max_kv_len + attn_min_keys() - 1) / attn_min_keys()));
     return (size_t) batch * heads * splits * (head_dim + 2) * sizeof(float);
 }
 
 // Merge of the key splits fused with the activation quantizer of the projection that follows: one CTA
 // per 256 consecutive outputs of a row (two 128-wide heads or four 64-wide ones), fp32 result kept as
-// well. grid (heads*D/256, batch), 256 threads.
+// well. grid (heads*D/256, batch), 256*MG threads (MG split groups, see merge_splits).
 template <int D, bool SPLIT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256 * MG)
 attn_merge_quant_kernel(const float* __restrict__ part, float* __restrict__ out, int splits, int heads, ActQ8K oq, ActSplit os) {
     __shared__ float red[8];
+    __shared__ float sm[3][MG][256];
     skd::pdl_launch_dependents();
     skd::pdl_wait();
-    const int b = blockIdx.y, e = blockIdx.x * 256 + threadIdx.x, n = heads * D;
-    const int head = e / D, dd = e % D, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const float* rec = part + ((int64_t) b * heads + head) * splits * (D + 2);
-    float mx = MASKED;
-#pragma unroll 8
-    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, __ldg(rec + s * (D + 2)));
-    float lt = 0.0f, at = 0.0f;
-#pragma unroll 8
-    for (int s = 0; s < splits; ++s) {
-        const float c = expf(__ldg(rec + s * (D + 2)) - mx);
-        lt += c * __ldg(rec + s * (D + 2) + 1);
-        at += c * __ldg(rec + s * (D + 2) + 2 + dd);
-    }
-    const float v = lt > 0.0f ? at / lt : 0.0f;
+    const int el = threadIdx.x & 255, grp = threadIdx.x >> 8;
+    const int b = blockIdx.y, e = blockIdx.x * 256 + el, n = heads * D;
+    const int head = e / D, dd = e % D, lane = threadIdx.x & 31, warp = el >> 5;
+    const float v = merge_splits<D, 256>(part + ((int64_t) b * heads + head) * splits * (D + 2), splits, dd, el, grp, sm);
+    if (grp != 0) return;        // the quantizer below runs on the first 256 threads and synchronises them by a named barrier
     out[(int64_t) b * n + e] = v;
     if (SPLIT) {                 // one scale per 32 values = per warp
         const float amax = skd::warp_max(fabsf(v));
@@ -397,7 +463,7 @@ attn_merge_quant_kernel(const float* __restrict__ part, float* __restrict__ out,
     } else {                     // one scale per 256 values = per CTA, code sums per warp
         float amax = skd::warp_max(fabsf(v));
         if (lane == 0) red[warp] = amax;
-        __syncthreads();
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         amax = fmaxf(fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3])), fmaxf(fmaxf(red[4], red[5]), fmaxf(red[6], red[7])));
         const float inv = amax > 0.0f ? 127.0f / amax : 0.0f;
         const int q = max(-127, min(127, __float2int_rn(v * inv)));
@@ -420,12 +486,12 @@ static void launch_decode_dg(const float* q, const __half* k, const __half* v, f
     if (simt) {
         launch_pdl(attn_decode_kernel<D, G>, grid, dim3(AD_THREADS), 0, s, q, k, v, out, part, heads, kv_heads, cache_stride, kv_len,
                    scale, window, chunk, splits, q_row_stride, always_partials);
-        if (splits > 1 && !always_partials) launch_pdl(attn_merge_kernel<D>, dim3(batch * heads), dim3(D), 0, s, (const float*) part, out, splits);
+        if (splits > 1 && !always_partials) launch_pdl(attn_merge_kernel<D>, dim3(batch * heads), dim3(D * MG), 0, s, (const float*) part, out, splits);
         return;
     }
     launch_pdl(attn_decode_mma_kernel<D>, grid, dim3(AM_WARPS * 32), 0, s, q, q_row_stride, k, v, part, heads, kv_heads, G, cache_stride, kv_len,
                scale, window, chunk, splits);
-    if (!always_partials) launch_pdl(attn_merge_kernel<D>, dim3(batch * heads), dim3(D), 0, s, (const float*) part, out, splits);
+    if (!always_partials) launch_pdl(attn_merge_kernel<D>, dim3(batch * heads), dim3(D * MG), 0, s, (const float*) part, out, splits);
 }
 
 static int32_t attn_decode_impl(const float* q, int64_t q_row_stride, const __half* k, const __half* v, float* out, int batch, int heads,
@@ -451,11 +517,11 @@ int32_t launch_attn_decode_quant(const float* q, int64_t q_row_stride, const __h
     SK_TRY(attn_decode_impl(q, q_row_stride, k, v, out, batch, heads, kv_heads, d, cache_stride, kv_len, max_kv_len, scale, window, scratch, 1, &splits, s));
     dim3 grid(heads * d / 256, batch);
     if (d == 128) {
-        if (split) SK_CUDA(launch_pdl(attn_merge_quant_kernel<128, true>, grid, dim3(256), 0, s, (const float*) scratch, out, splits, heads, oq, os));
-        else SK_CUDA(launch_pdl(attn_merge_quant_kernel<128, false>, grid, dim3(256), 0, s, (const float*) scratch, out, splits, heads, oq, os));
+        if (split) SK_CUDA(launch_pdl(attn_merge_quant_kernel<128, true>, grid, dim3(256 * MG), 0, s, (const float*) scratch, out, splits, heads, oq, os));
+        else SK_CUDA(launch_pdl(attn_merge_quant_kernel<128, false>, grid, dim3(256 * MG), 0, s, (const float*) scratch, out, splits, heads, oq, os));
     } else {
-        if (split) SK_CUDA(launch_pdl(attn_merge_quant_kernel<64, true>, grid, dim3(256), 0, s, (const float*) scratch, out, splits, heads, oq, os));
-        else SK_CUDA(launch_pdl(attn_merge_quant_kernel<64, false>, grid, dim3(256), 0, s, (const float*) scratch, out, splits, heads, oq, os));
+        if (split) SK_CUDA(launch_pdl(attn_merge_quant_kernel<64, true>, grid, dim3(256 * MG), 0, s, (const float*) scratch, out, splits, heads, oq, os));
+        else SK_CUDA(launch_pdl(attn_merge_quant_kernel<64, false>, grid, dim3(256 * MG), 0, s, (const float*) scratch, out, splits, heads, oq, os));
     }
     return SKAINET_CUDA_OK;
 }

@@ -41,7 +41,7 @@ def test_noalloc_decode_attention_equals_the_scratch_version_on_two_calls_in_a_r
 
 
 def test_noalloc_refuses_sizes_beyond_the_builtin_area(gpu):
-    # batch 64 x 64 heads at 32768 keys needs 64*64*2*130 floats of partials > 2^20: refused, nothing launched
+    # batch 128 x 64 heads needs 128*64*1*130 floats of partials > 2^20 even unsplit: refused, nothing launched
     dummy = gpu.DeviceBuffer(1 << 16)
     with pytest.raises(ValueError, match="built-in area"):
-        gpu.attn_decode_noalloc(dummy.ptr, dummy.ptr, dummy.ptr, dummy.ptr, 64, 64, 8, 128, 32768, dummy.ptr, 32768, 0.088)
+        gpu.attn_decode_noalloc(dummy.ptr, dummy.ptr, dummy.ptr, dummy.ptr, 128, 64, 8, 128, 32768, dummy.ptr, 32768, 0.088)
