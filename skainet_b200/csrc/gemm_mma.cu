@@ -1,0 +1,213 @@
+// Batched rows (m >= 2): Q4_K weights x int8-quantized activations on the tensor cores
+// (mma.sync m16n8k32, u8 x s8 -> s32). Used by prefill (m = prompt tokens) and by decode with several
+// sequences in a batch; one activation row is left to the matvec kernels.
+//
+// Arithmetic is the reference's integer path (native/src/q4k_matmul.c:143-251): per 32-element sub-block
+// an exact integer dot of the 4-bit codes with the activation codes, scaled by the 6-bit sub-block scale,
+// minus the 6-bit min times the sum of the activation codes, then d_in * (d * sum_sc - dmin * sum_mn) in
+// fp32. The MMA's A tile is 16 weight rows x 32 codes of one sub-block, its B tile the same 32 codes of
+// 8 activation rows, so an output tile reuses every weight byte for all its activation rows.
+//
+// CTA = NW warps x 16 weight rows, MT = 8*NT activation rows, looping over the 256-element super-blocks
+// of the contraction through an NS-stage cp.async pipeline:
+//   weight stage  [16*NW rows][144 B]: 128 B of nibbles then the 16-byte header; the 144-byte row stride
+//                 makes ldmatrix (8 rows x 16 B) and the header reads bank-conflict free;
+//   activation stage [MT rows][272 B]: 256 codes then the 8 int16 sub-block sums; 272-byte stride makes the
+//                 B-fragment reads (8 rows x 4 words) conflict free; plus [MT] fp32 block scales.
+// A lane's ldmatrix.x4 of 32 raw bytes per row yields the A fragments of two sub-blocks: low nibbles are
+// sub-block 2g, high nibbles sub-block 2g+1 of 64-element group g.
+#include "common.cuh"
+#include "actquant.cuh"
+#include "tma.cuh"
+#include "matvec_fused.cuh"
+
+namespace sk {
+
+namespace {
+
+constexpr int GW_STRIDE = 144;      // bytes per weight row per stage
+constexpr int GX_STRIDE = 272;      // bytes per activation row per stage
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(skd::smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(skd::smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(skd::smem_u32(p)));
+}
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int NW, int NT, int NS, int EPI>
+__global__ void __launch_bounds__(NW * 32)
+q4k_gemm_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ hdr, int rows, int bpr, ActQ8K act, int m,
+                    float* __restrict__ y, const float* __restrict__ resid) {
+    constexpr int RT = NW * 16, MT = NT * 8;
+    constexpr int W_BYTES = RT * GW_STRIDE, X_BYTES = MT * GX_STRIDE, S_BYTES = W_BYTES + X_BYTES + MT * 4;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int row0 = blockIdx.x * RT, col0 = blockIdx.y * MT;
+    const int cols = bpr * 256;
+    skd::pdl_launch_dependents();
+
+    auto issue_w = [&](int kb) {
+        uint8_t* st = smem + (size_t) (kb % NS) * S_BYTES;
+        for (int c = threadIdx.x; c < RT * 9; c += NW * 32) {
+            const int r = c / 9, ch = c % 9;
+            const size_t blk = (size_t) min(row0 + r, rows - 1) * bpr + kb;
+            cp_async16(st + r * GW_STRIDE + ch * 16, ch < 8 ? qs + blk * 128 + ch * 16 : hdr + blk * 16);
+        }
+    };
+    auto issue_x = [&](int kb) {
+        uint8_t* st = smem + (size_t) (kb % NS) * S_BYTES + W_BYTES;
+        for (int c = threadIdx.x; c < MT * 17; c += NW * 32) {
+            const int r = c / 17, ch = c % 17;
+            const size_t arow = (size_t) min(col0 + r, m - 1);
+            cp_async16(st + r * GX_STRIDE + ch * 16,
+                       ch < 16 ? (const void*) (act.q + arow * cols + (size_t) kb * 256 + ch * 16) : (const void*) (act.bsums + (arow * bpr + kb) * 8));
+        }
+        if (threadIdx.x < MT) cp_async4(st + X_BYTES + threadIdx.x * 4, act.d + (size_t) min(col0 + (int) threadIdx.x, m - 1) * bpr + kb);
+    };
+
+    // The weights depend on no predecessor: their first stages are in flight before the wait.
+    for (int s = 0; s < NS - 1 && s < bpr; ++s) issue_w(s);
+    skd::pdl_wait();
+    for (int s = 0; s < NS - 1; ++s) {
+        if (s < bpr) issue_x(s);
+        cp_async_commit();
+    }
+
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) { acc[nt][0] = 0.f; acc[nt][1] = 0.f; acc[nt][2] = 0.f; acc[nt][3] = 0.f; }
+
+    // ldmatrix source of this lane: matrix (lane/8): rows +8 for odd matrices, bytes +16 for matrices 2, 3
+    const int lm_row = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), lm_byte = 16 * (lane >> 4);
+
+    for (int kb = 0; kb < bpr; ++kb) {
+        cp_async_wait<NS - 2>();
+        __syncthreads();
+        if (kb + NS - 1 < bpr) { issue_w(kb + NS - 1); issue_x(kb + NS - 1); }
+        cp_async_commit();
+
+        const uint8_t* ws = smem + (size_t) (kb % NS) * S_BYTES;
+        const uint8_t* xs = ws + W_BYTES;
+        const float* xd = (const float*) (xs + X_BYTES);
+
+        // headers of rows g and g+8 of this warp's tile
+        float dw[2], dminw[2];
+        uint32_t sc_lo[2], sc_hi[2], mn_lo[2], mn_hi[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint4 hd = skd::lds128(ws + (warp * 16 + g + 8 * r) * GW_STRIDE + 128);
+            dw[r] = __half2float(__ushort_as_half((unsigned short) (hd.x & 0xffff)));
+            dminw[r] = __half2float(__ushort_as_half((unsigned short) (hd.x >> 16)));
+            skd::k4_unpack(hd.y, hd.z, hd.w, sc_lo[r], sc_hi[r], mn_lo[r], mn_hi[r]);
+        }
+        int isum[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) { isum[nt][0] = 0; isum[nt][1] = 0; isum[nt][2] = 0; isum[nt][3] = 0; }
+
+#pragma unroll
+        for (int gq = 0; gq < 4; ++gq) {
+            uint32_t raw[4], lo[4], hi[4];
+            ldmatrix_x4(raw, ws + lm_row * GW_STRIDE + 32 * gq + lm_byte);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { lo[i] = raw[i] & 0x0f0f0f0fu; hi[i] = (raw[i] >> 4) & 0x0f0f0f0fu; }
+            // scales of sub-blocks 2gq (low nibbles) and 2gq+1 (high nibbles) for rows g, g+8
+            int s_lo[2], s_hi[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const uint32_t word = gq < 2 ? sc_lo[r] : sc_hi[r];
+                s_lo[r] = (int) ((word >> (16 * (gq & 1))) & 0xff);
+                s_hi[r] = (int) ((word >> (16 * (gq & 1) + 8)) & 0xff);
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint8_t* xr = xs + (nt * 8 + g) * GX_STRIDE + 64 * gq + 4 * t;
+                int c[4] = {0, 0, 0, 0};
+                mma_u8s8(c, lo, *(const uint32_t*) xr, *(const uint32_t*) (xr + 16));
+                isum[nt][0] += s_lo[0] * c[0]; isum[nt][1] += s_lo[0] * c[1];
+                isum[nt][2] += s_lo[1] * c[2]; isum[nt][3] += s_lo[1] * c[3];
+                int e[4] = {0, 0, 0, 0};
+                mma_u8s8(e, hi, *(const uint32_t*) (xr + 32), *(const uint32_t*) (xr + 48));
+                isum[nt][0] += s_hi[0] * e[0]; isum[nt][1] += s_hi[0] * e[1];
+                isum[nt][2] += s_hi[1] * e[2]; isum[nt][3] += s_hi[1] * e[3];
+            }
+        }
+        // mins and the fp32 update; accumulator j: row g + 8*(j/2), activation row 2t + (j&1)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+                const int col = nt * 8 + 2 * t + cc;
+                const uint4 bs = skd::lds128(xs + col * GX_STRIDE + 256);     // eight int16 sums
+                const float dx = xd[col];
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    int ms = __dp2a_lo((int) bs.x, (int) mn_lo[r], 0);
+                    ms = __dp2a_hi((int) bs.y, (int) mn_lo[r], ms);
+                    ms = __dp2a_lo((int) bs.z, (int) mn_hi[r], ms);
+                    ms = __dp2a_hi((int) bs.w, (int) mn_hi[r], ms);
+                    acc[nt][2 * r + cc] += dx * (dw[r] * (float) isum[nt][2 * r + cc] - dminw[r] * (float) ms);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+
+    // y[activation row][weight row]
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int row = row0 + warp * 16 + g + 8 * (j >> 1), col = col0 + nt * 8 + 2 * t + (j & 1);
+            if (row < rows && col < m) {
+                const size_t o = (size_t) col * rows + row;
+                y[o] = EPI == EPI_ADD ? resid[o] + acc[nt][j] : acc[nt][j];
+            }
+        }
+}
+
+template <int NW, int NT, int NS>
+int32_t launch_cfg(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s) {
+    constexpr int RT = NW * 16, MT = NT * 8;
+    constexpr size_t smem = (size_t) NS * (RT * GW_STRIDE + MT * GX_STRIDE + MT * 4);
+    static bool done[2] = {false, false};
+    dim3 grid((w.rows + RT - 1) / RT, (m + MT - 1) / MT);
+    if (resid) {
+        if (!done[1]) { SK_CUDA(cudaFuncSetAttribute(q4k_gemm_mma_kernel<NW, NT, NS, EPI_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem)); done[1] = true; }
+        SK_CUDA(launch_pdl(q4k_gemm_mma_kernel<NW, NT, NS, EPI_ADD>, grid, dim3(NW * 32), smem, s, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows,
+                           w.bpr, a, m, y, resid));
+    } else {
+        if (!done[0]) { SK_CUDA(cudaFuncSetAttribute(q4k_gemm_mma_kernel<NW, NT, NS, EPI_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem)); done[0] = true; }
+        SK_CUDA(launch_pdl(q4k_gemm_mma_kernel<NW, NT, NS, EPI_STORE>, grid, dim3(NW * 32), smem, s, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows,
+                           w.bpr, a, m, y, resid));
+    }
+    return SKAINET_CUDA_OK;
+}
+
+}  // namespace
+
+// y[m][w.rows] (= resid +) act . W^T for m >= 2 activation rows already quantized (ActQ8K). Returns 1 when
+// the weight is not Q4_K (the caller falls back to the per-row kernels).
+int32_t launch_gemm_mma(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s) {
+    if (w.enc != SKAINET_ENC_Q4_K) return 1;
+    // Up to four activation rows stay with the streaming matvec kernels (faster there). Few rows: weight
+    // streaming decides, so small row tiles (many CTAs) and a deep pipeline; many rows: 128 x 32 output tiles.
+    if (m <= 4) return 1;
+    if (m <= 8) return launch_cfg<4, 1, 8>(w, a, m, y, resid, s);
+    if (m <= 16) return launch_cfg<4, 2, 6>(w, a, m, y, resid, s);
+    return launch_cfg<8, 4, 4>(w, a, m, y, resid, s);
+}
+
+}  // namespace sk

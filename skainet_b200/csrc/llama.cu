@@ -286,6 +286,10 @@ static int32_t linear(Model& m, const Weight& w, int rows, float* y, float* resi
         const int32_t st = launch_matvec_fused(w, in, PREP_QUANTIZED, resid_inplace ? resid_inplace : y, resid_inplace, s);
         if (st != 1) return st;
     }
+    if (rows >= 2 && matvec_env_mode() == 0) {
+        const int32_t st = launch_gemm_mma(w, act_q8k_layout(m.act, rows, w.cols), rows, resid_inplace ? resid_inplace : y, resid_inplace, s);
+        if (st != 1) return st;
+    }
     float* out = resid_inplace ? m.tmp : y;
     SK_TRY(launch_matvec(w, nullptr, m.act, rows, out, SKAINET_ACT_NATIVE, s));
     if (resid_inplace) {

@@ -11,6 +11,7 @@
 //         ScalarQ4_KMatmulKernel.kt:66-75 and ScalarQ8_0MatmulKernel.kt:56-59.
 #include "common.cuh"
 #include "actquant.cuh"
+#include "matvec_fused.cuh"
 #include "tma.cuh"
 
 #include <cstdlib>
@@ -307,6 +308,10 @@ int32_t launch_matvec(const Weight& w, const float* x, const void* act_scratch, 
     }
     // SKAINET_MATVEC=direct|stream selects the earlier kernel generations (kept for A/B measurements).
     static const bool force_direct = matvec_env_mode() == 1;
+    if (m >= 2 && matvec_env_mode() == 0) {       // several activation rows: tensor-core tile kernel
+        const int32_t st = launch_gemm_mma(w, act_q8k_layout(const_cast<void*>(act_scratch), m, w.cols), m, y, nullptr, s);
+        if (st != 1) return st;
+    }
     for (int m0 = 0; m0 < m;) {
         const int left = m - m0;
         const int mm = left >= 8 ? 8 : (left >= 4 ? 4 : (left >= 2 ? 2 : 1));
