@@ -539,8 +539,12 @@ def run_decode(args) -> None:
     e1.record(mstream)
     barrier()
     ms = e0.elapsed_time(e1)
-    if rank == 0 and ms < 1500 and not args.skip_cpu:    # keep the GPU loaded long enough for the clock sampler
-        m.generate(first, min(1024, int(1500 / max(ms / args.steps, 1e-3))))
+    if not args.skip_cpu:                                # keep the GPUs loaded long enough for the clock sampler;
+        tm = torch.tensor([ms], device="cuda", dtype=torch.float64)   # every rank takes the same number of extra steps
+        if world > 1:
+            dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        if float(tm[0]) < 1500:
+            m.generate(first, min(1024, int(1500 / max(float(tm[0]) / args.steps, 1e-3))))
     clocks = sampler.stop() if rank == 0 else None
 
     # end to end: one C-ABI call per step, token ids from pinned host memory and back

@@ -1,9 +1,21 @@
-// NCCL binding by dlopen (see comm.cuh). Only the five entry points the decoder needs.
+// NCCL binding by dlopen (see comm.cuh), only the five entry points the decoder needs, plus a one-shot
+// all-reduce over peer memory for the small sums of a decode step.
+//
+// One-shot all-reduce (n <= P2P_MAX_ELEMS floats): every rank owns an "inbox" of world slots (two copies,
+// used alternately) and a flag word per (sender, CTA). A CTA stores its slice of the local vector into its
+// slot of every peer's inbox (plain stores over NVLink), publishes a sequence number with a system-scope
+// release store, waits (bounded) until every peer's number for this round has arrived, and sums the world
+// slots in rank order, so all ranks get bit-identical results. Nothing is reset between rounds: numbers only
+// grow, and a peer can be at most one round ahead, which the second inbox copy absorbs. Latency is one NVLink
+// store round instead of NCCL's multi-step protocol: what matters for a 32 KB sum issued 160 times per token.
 #include "comm.cuh"
+#include "tma.cuh"
 
 #include <dlfcn.h>
 #include <cstring>
 #include <mutex>
+#include <vector>
+#include <cstdlib>
 
 namespace sk {
 
@@ -55,7 +67,126 @@ static int32_t nccl_fail(ncclResult_t r, const char* what) {
     return SKAINET_CUDA_ERR_COMM;
 }
 
-struct Comm { ncclComm_t comm = nullptr; int rank = 0, world = 1; };
+constexpr int P2P_MAX_WORLD = 8;
+constexpr int P2P_CTA_ELEMS = 1024;                 // floats per CTA (256 threads x float4)
+constexpr int P2P_MAX_CTAS = 64;
+constexpr int P2P_MAX_ELEMS = P2P_CTA_ELEMS * P2P_MAX_CTAS;
+constexpr int P2P_SPIN_LIMIT = 1 << 24;             // ~1 s of polling, then the kernel gives up and reports
+
+// Per-rank region, identical layout on every rank:
+//   inbox [2][world][P2P_MAX_ELEMS] float | flags [world][P2P_MAX_CTAS] int | seq [P2P_MAX_CTAS] int (local only)
+struct P2PView {
+    float* inbox[P2P_MAX_WORLD];    // base of each rank's region as mapped into this process
+    int rank, world;
+};
+static size_t p2p_region_bytes(int world) {
+    return (size_t) 2 * world * P2P_MAX_ELEMS * 4 + (size_t) world * P2P_MAX_CTAS * 4 + P2P_MAX_CTAS * 4;
+}
+__device__ __forceinline__ int* p2p_flags(float* base, int world) { return (int*) (base + (size_t) 2 * world * P2P_MAX_ELEMS); }
+
+__global__ void __launch_bounds__(256)
+allreduce_oneshot_kernel(P2PView v, float* __restrict__ buf, int n, int* __restrict__ timeout_flag) {
+    __shared__ int s_seq;
+    skd::pdl_launch_dependents();
+    const int cta = blockIdx.x, world = v.world, rank = v.rank;
+    float* mine = v.inbox[rank];
+    int* my_flags = p2p_flags(mine, world);
+    int* seq_slot = my_flags + world * P2P_MAX_CTAS + cta;
+    const int i = cta * P2P_CTA_ELEMS + threadIdx.x * 4;          // this thread's float4
+    const bool live = i < n;                                      // n is a multiple of 4
+    // buf is the predecessor's output, and the round counter is the previous round's: nothing is read before
+    // every earlier kernel of the stream has completed
+    skd::pdl_wait();
+    if (threadIdx.x == 0) s_seq = *seq_slot + 1;
+    __syncthreads();
+    const int seq = s_seq, par = seq & 1;
+    float4 own = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live) {
+        own = *reinterpret_cast<const float4*>(buf + i);
+        for (int p = 0; p < world; ++p)
+            if (p != rank) *reinterpret_cast<float4*>(v.inbox[p] + ((size_t) par * world + rank) * P2P_MAX_ELEMS + i) = own;
+    }
+    __syncthreads();
+    if (threadIdx.x < world && (int) threadIdx.x != rank) {
+        // publish: the barrier above ordered the CTA's stores before this thread; the fence and the release
+        // store make them visible system-wide before the number is
+        __threadfence_system();
+        int* peer_flag = p2p_flags(v.inbox[threadIdx.x], world) + rank * P2P_MAX_CTAS + cta;
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(peer_flag), "r"(seq) : "memory");
+        // wait for the same peer's number (bounded)
+        const int* f = my_flags + threadIdx.x * P2P_MAX_CTAS + cta;
+        int got = 0, spins = 0;
+        do {
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(got) : "l"(f) : "memory");
+        } while (got < seq && ++spins < P2P_SPIN_LIMIT);
+        if (got < seq && timeout_flag) atomicExch(timeout_flag, 2);
+    }
+    __syncthreads();
+    if (live) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int p = 0; p < world; ++p) {
+            const float4 x = p == rank ? own : __ldcg(reinterpret_cast<const float4*>(mine + ((size_t) par * world + p) * P2P_MAX_ELEMS + i));
+            acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+        }
+        *reinterpret_cast<float4*>(buf + i) = acc;
+    }
+    if (threadIdx.x == 0) *seq_slot = seq;
+}
+
+struct Comm {
+    ncclComm_t comm = nullptr;
+    int rank = 0, world = 1;
+    bool p2p = false;
+    P2PView view = {};
+    void* region = nullptr;          // this rank's region (cudaMalloc)
+    void* peers[P2P_MAX_WORLD] = {}; // opened IPC mappings (null for self)
+};
+
+// Exchanges IPC handles of the per-rank regions through NCCL and maps every peer's region. Any failure
+// leaves the communicator on NCCL only.
+static void p2p_setup(Comm* c) {
+    static const bool off = []() { const char* e = getenv("SKAINET_TP_ALLREDUCE"); return e && strcmp(e, "nccl") == 0; }();
+    if (off || c->world < 2 || c->world > P2P_MAX_WORLD) return;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return;
+    const size_t bytes = p2p_region_bytes(c->world);
+    if (cudaMalloc(&c->region, bytes) != cudaSuccess) { c->region = nullptr; cudaGetLastError(); return; }
+    cudaMemset(c->region, 0, bytes);
+    cudaIpcMemHandle_t h;
+    void* d_send = nullptr; void* d_recv = nullptr;
+    std::vector<cudaIpcMemHandle_t> all(c->world);
+    bool ok = cudaIpcGetMemHandle(&h, c->region) == cudaSuccess && cudaMalloc(&d_send, sizeof(h)) == cudaSuccess &&
+              cudaMalloc(&d_recv, sizeof(h) * c->world) == cudaSuccess;
+    // every rank takes part in the gather even when its own preparation failed (a zero handle then fails to open)
+    if (!ok) memset(&h, 0, sizeof(h));
+    if (d_send && d_recv) {
+        cudaMemcpy(d_send, &h, sizeof(h), cudaMemcpyHostToDevice);
+        ok = g_nccl.AllGather(d_send, d_recv, sizeof(h), ncclInt8, c->comm, (cudaStream_t) 0) == 0 && ok;
+        ok = cudaStreamSynchronize(0) == cudaSuccess && ok;
+        cudaMemcpy(all.data(), d_recv, sizeof(h) * c->world, cudaMemcpyDeviceToHost);
+    } else ok = false;
+    cudaFree(d_send); cudaFree(d_recv);
+    for (int p = 0; ok && p < c->world; ++p) {
+        if (p == c->rank) { c->view.inbox[p] = (float*) c->region; continue; }
+        if (cudaIpcOpenMemHandle(&c->peers[p], all[p], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { ok = false; c->peers[p] = nullptr; break; }
+        c->view.inbox[p] = (float*) c->peers[p];
+    }
+    // agree: the fast path is used only when every rank mapped every peer
+    int* d_ok = nullptr;
+    int mine = ok ? 1 : 0, sum = 0;
+    if (cudaMalloc(&d_ok, sizeof(int)) == cudaSuccess) {
+        float f = (float) mine;
+        cudaMemcpy(d_ok, &f, sizeof(float), cudaMemcpyHostToDevice);
+        if (g_nccl.AllReduce(d_ok, d_ok, 1, ncclFloat32, ncclSum, c->comm, (cudaStream_t) 0) == 0 && cudaStreamSynchronize(0) == cudaSuccess) {
+            cudaMemcpy(&f, d_ok, sizeof(float), cudaMemcpyDeviceToHost);
+            sum = (int) f;
+        }
+        cudaFree(d_ok);
+    }
+    cudaGetLastError();
+    c->view.rank = c->rank; c->view.world = c->world;
+    c->p2p = sum == c->world;
+}
 
 int32_t comm_unique_id(uint8_t* id128) {
     SK_TRY(nccl_ready());
@@ -74,18 +205,27 @@ int32_t comm_create(int rank, int world, const uint8_t* id128, Comm** out) {
     c->rank = rank; c->world = world;
     const ncclResult_t r = g_nccl.CommInitRank(&c->comm, world, id, rank);
     if (r != 0) { delete c; return nccl_fail(r, "ncclCommInitRank"); }
+    p2p_setup(c);
     *out = c;
     return SKAINET_CUDA_OK;
 }
 
 void comm_destroy(Comm* c) {
     if (!c) return;
+    for (int p = 0; p < P2P_MAX_WORLD; ++p)
+        if (c->peers[p]) cudaIpcCloseMemHandle(c->peers[p]);
+    if (c->region) cudaFree(c->region);
     if (c->comm && g_nccl.ok) g_nccl.CommDestroy(c->comm);
     delete c;
 }
 
 int32_t comm_all_reduce_sum(Comm* c, float* buf, int64_t n, cudaStream_t s) {
     if (!c) { set_error("tensor-parallel model without a communicator (call llama_tp_init)"); return SKAINET_CUDA_ERR_COMM; }
+    if (c->p2p && n <= P2P_MAX_ELEMS && n % 4 == 0 && ((uintptr_t) buf & 15) == 0) {
+        const int ctas = (int) ((n + P2P_CTA_ELEMS - 1) / P2P_CTA_ELEMS);
+        SK_CUDA(launch_pdl(allreduce_oneshot_kernel, dim3(ctas), dim3(256), 0, s, c->view, buf, (int) n, device_timeout_flag()));
+        return SKAINET_CUDA_OK;
+    }
     const ncclResult_t r = g_nccl.AllReduce(buf, buf, (size_t) n, ncclFloat32, ncclSum, c->comm, s);
     return r == 0 ? SKAINET_CUDA_OK : nccl_fail(r, "ncclAllReduce");
 }
