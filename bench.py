@@ -9,13 +9,17 @@ Prints ONE JSON line (rank 0). Workloads (all inputs synthetic and seeded):
       heads, vocab 128256, all Q4_K, random-init N(0,0.02) packed on the device; greedy decode at
       batch 1 behind a 4096-token context, tensor-parallel over the N GPUs (strong scaling: the same
       model and batch at every N). metric = decode tokens/s. A step is one decode step (one token per
-      sequence). The context's K/V are seeded noise, not a real prefill: the reference has no batched
-      GEMM and 4096 prompt rows through matvecs is out of reach for both sides.
+      sequence). The context's K/V are seeded noise, not a real prefill (the reference has no batched
+      GEMM, so a 4096-row prompt is out of reach for its side). --batch B decodes B sequences.
   decode_7b — BASELINE config 4: 32 layers, d 4096, FFN 11008, 32 heads, vocab 32000; Q4_K linears,
       Q8_0 embedding/output; batch 1 behind a 512-token context.
   q4k_matvec — BASELINE config 2 at M=1: W[11008,4096] and W[4096,11008]; metric = algorithmic HBM
       GB/s over a sweep of distinct weights larger than 2x L2.
   q8_0_matvec — BASELINE config 1: Q8_0 W[4096,4096], same protocol.
+  attn_decode — BASELINE config 3: GQA decode attention, 32 query / 8 KV heads, head_dim 128, f16 cache of
+      --context keys (default 4096) for --batch sequences; metric = K/V bytes read per second.
+  q4k_gemm — BASELINE config 2 at M = --batch rows (default 512) through the tensor-core tile kernel;
+      metric = 2*M*rows*cols operations per second, roofline against the measured cuBLAS bf16 burst.
 
 `value` is timed on the device with everything resident in HBM (decode: one CUDA-graph replay per
 step, tokens fed back on the device). `e2e` is the same metric through the C ABI with HOST buffers
@@ -48,7 +52,9 @@ MATVEC_WORKLOADS = {
 }
 DECODE_WORKLOADS = {"decode_70b": ("70b", 4096), "decode_7b": ("7b", 512)}
 # decode attention alone: (query heads, kv heads, head_dim); context from --context
-ATTN_WORKLOADS = {"attn_decode": (64, 8, 128)}
+ATTN_WORKLOADS = {"attn_decode": (32, 8, 128)}
+# batched rows through the tensor-core tile kernel: the Q4_K sweep shapes with --batch activation rows (default 512)
+GEMM_WORKLOADS = {"q4k_gemm": [(11008, 4096), (4096, 11008)]}
 BLOCK = {"Q4_K": (144, 256), "Q8_0": (34, 32)}
 
 
@@ -61,6 +67,13 @@ def algorithmic_bytes(enc_bytes: int, enc_elems: int, rows: int, cols: int, m: i
 # q4k_matvec_ring_kernel: 25.387 MB per 11008x4096 launch against 25.362 MB algorithmic, 264.27 MB per
 # 57344x8192 launch against 264.24 MB.  Traffic grows in proportion to the weight bytes (each byte is read once).
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.001
+
+
+def load_tensor_peak() -> tuple[float, str]:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["bf16_tflops"]), "measured (cuBLAS bf16 burst)"
+    return 1590.0, "fallback"
 
 
 def load_peaks() -> tuple[float, str]:
@@ -227,6 +240,8 @@ def run_reference(args) -> None:
             r = cpu_matvec_rate(args.workload, budget); unit = "GB/s"; metric = f"{args.workload}_hbm_gbs"
         elif args.workload in ATTN_WORKLOADS:
             r = cpu_attn_rate(args.workload, args.context, max(1, args.batch)); unit = "GB/s"; metric = "attn_decode_hbm_gbs"
+        elif args.workload in GEMM_WORKLOADS:
+            r = cpu_gemm_rate(args.workload, args.batch if args.batch > 1 else 512, budget); unit = "TFLOP/s"; metric = "q4k_gemm_tflops"
         else:
             model, ctx = DECODE_WORKLOADS[args.workload]
             r = cpu_decode_rate(model, ctx, budget); unit = "tokens/s"; metric = "decode_tokens_per_s"
@@ -243,6 +258,8 @@ def run_reference(args) -> None:
 
 
 def dtype_of(workload: str) -> str:
+    if workload in GEMM_WORKLOADS:
+        return "u8 (4-bit codes) x s8 -> s32 on mma.sync, f32 accumulate"
     if workload in ATTN_WORKLOADS:
         return "f16 K/V, f32 q split in two f16 terms, f32 accumulate"
     if workload == "q8_0_matvec":
@@ -252,7 +269,11 @@ def dtype_of(workload: str) -> str:
 
 
 def workload_config(args, world: int, extra: dict | None = None) -> dict:
-    if args.workload in ATTN_WORKLOADS:
+    if args.workload in GEMM_WORKLOADS:
+        c = {"workload": args.workload, "encoding": "Q4_K", "shapes_out_in": GEMM_WORKLOADS[args.workload],
+             "m": args.batch if args.batch > 1 else 512, "activation": "fp32 N(0,1), quantized to int8 per 256 on the device inside the timed region",
+             "weights": "N(0,0.02) packed on device, seeded", "l2": "rotating distinct weights larger than 2x L2 per sweep"}
+    elif args.workload in ATTN_WORKLOADS:
         h, hkv, d = ATTN_WORKLOADS[args.workload]
         c = {"workload": args.workload, "heads": h, "kv_heads": hkv, "head_dim": d, "batch": max(1, args.batch), "context": args.context,
              "kv": "f16 resident, N(0,1)", "l2": "rotating distinct caches larger than 2x L2 per sweep"}
@@ -424,6 +445,86 @@ def run_matvec(args) -> None:
 # ---------------------------------------------------------------------------------------------------
 # our arm: decode
 # ---------------------------------------------------------------------------------------------------
+def cpu_gemm_rate(workload: str, m: int, seconds: float) -> dict:
+    """The reference has no batched kernel: its row-major Q4_K matvec is called once per activation row."""
+    from oracle import ref as R
+    shapes = GEMM_WORKLOADS[workload]
+    use_ref = R.ref() is not None
+    rng = np.random.default_rng(5)
+    items = [(r, c, random_blocks(rng, "Q4_K", r, c), rng.standard_normal(c).astype(np.float32)) for r, c in shapes]
+    t0 = time.perf_counter(); calls = 0; flops = 0
+    while time.perf_counter() - t0 < seconds:
+        for r, c, packed, x in items:
+            R.matmul("Q4_K", x, packed, c, r, "rm", use_ref=use_ref); calls += 1; flops += 2 * r * c
+    dt = time.perf_counter() - t0
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": 4 if use_ref else 1, "kind": "reference" if use_ref else "port",
+            "sample": f"{calls} single-row calls of the reference's row-major Q4_K kernel (it has no batched form); the rate per row "
+                      f"does not depend on m = {m}", "seconds": dt}
+
+
+def run_gemm(args) -> None:
+    """m activation rows x Q4_K weights through skainet_cuda_matmul_dev: quantizer + tensor-core tile kernel.
+    Operations = 2 * m * rows * cols per weight."""
+    import torch
+    from skainet_b200 import _lib as L, device
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local); device.set_device(local)
+    info = device.device_info()
+    shapes = GEMM_WORKLOADS[args.workload]
+    m = args.batch if args.batch > 1 else 512
+    copies = max(2, int(np.ceil(2.2 * info["l2_bytes"] / min(r * (c // 256) * 144 for r, c in shapes))) // 2)
+    ws = [device.Weight.synth("Q4_K", r, c, seed=10 * si + ci, std=0.02) for ci in range(copies) for si, (r, c) in enumerate(shapes)]
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    xs = {c: torch.randn(m, c, device="cuda", generator=gen) for _, c in shapes}
+    ys = {r: torch.empty(m, r, device="cuda") for r, _ in shapes}
+    stream = torch.cuda.Stream(); sp = stream.cuda_stream
+    ops = sum(2 * m * w.rows * w.cols for w in ws)
+
+    def sweep():
+        for w in ws:
+            device.matmul(w, xs[w.cols].data_ptr(), m, ys[w.rows].data_ptr(), L.ACT_NATIVE, sp)
+
+    warm = max(3, args.warmup)
+    with torch.cuda.stream(stream):
+        for _ in range(warm):
+            sweep()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        clk = ClockSampler(local); clk.start()
+        stream.synchronize(); e0.record(stream)
+        for _ in range(args.steps):
+            sweep()
+        e1.record(stream); stream.synchronize()
+        clocks = clk.stop()
+    ms_step = e0.elapsed_time(e1) / args.steps
+    e2e_ms = None
+    if not args.skip_e2e:                     # activations from pinned host memory, results back, per call
+        hx = {c: torch.randn(m, c).pin_memory() for _, c in shapes}
+        hy = {r: torch.empty(m, r).pin_memory() for r, _ in shapes}
+        with torch.cuda.stream(stream):
+            def e2e_sweep():
+                for w in ws:
+                    xs[w.cols].copy_(hx[w.cols], non_blocking=True)
+                    device.matmul(w, xs[w.cols].data_ptr(), m, ys[w.rows].data_ptr(), L.ACT_NATIVE, sp)
+                    hy[w.rows].copy_(ys[w.rows], non_blocking=True); stream.synchronize()
+            e2e_sweep()
+            t0 = time.perf_counter(); e2e_sweep(); e2e_ms = (time.perf_counter() - t0) * 1e3
+    peak, peak_kind = load_tensor_peak()
+    achieved = ops / (ms_step * 1e-3) / 1e12
+    line = {"metric": "q4k_gemm_tflops", "value": achieved, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": warm,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype_of(args.workload),
+            "data": "synthetic", "config": workload_config(args, 1, {"weights_per_shape": copies}),
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                         "peak_kind": peak_kind, "kernel": "q4k_gemm_mma_kernel", "avg_launch_us": ms_step * 1e3 / len(ws),
+                         "note": "integer multiply-adds counted as 2 operations each; avg launch = timed region / calls (quantizer inside)"},
+            "e2e": {"value": (ops / (e2e_ms * 1e-3) / 1e12) if e2e_ms else None, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": int(sum(4 * m * w.cols for w in ws)), "d2h_bytes_per_step": int(sum(4 * m * w.rows for w in ws))},
+            "gpu_launches": 2 * len(ws) * args.steps, "clocks": clocks}
+    if not args.skip_cpu:
+        cpu = cpu_gemm_rate(args.workload, m, 10.0)
+        line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line), flush=True)
+
+
 def run_attn(args) -> None:
     """Decode attention alone through skainet_cuda_attn_decode_dev: one query row per head against a
     resident f16 cache. Bytes per call = the K and V rows it must read."""
@@ -608,7 +709,7 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="decode_70b", choices=sorted(MATVEC_WORKLOADS) + sorted(DECODE_WORKLOADS) + sorted(ATTN_WORKLOADS))
+    ap.add_argument("--workload", default="decode_70b", choices=sorted(MATVEC_WORKLOADS) + sorted(DECODE_WORKLOADS) + sorted(ATTN_WORKLOADS) + sorted(GEMM_WORKLOADS))
     ap.add_argument("--context", type=int, default=4096, help="keys per sequence (attn_decode workload)")
     ap.add_argument("--batch", type=int, default=1, help="sequences decoded together (decode workloads)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -621,6 +722,8 @@ def main() -> None:
         run_matvec(args)
     elif args.workload in ATTN_WORKLOADS:
         run_attn(args)
+    elif args.workload in GEMM_WORKLOADS:
+        run_gemm(args)
     else:
         run_decode(args)
 
