@@ -202,6 +202,10 @@ int32_t launch_cfg(const Weight& w, ActQ8K a, int m, float* y, const float* resi
 // the weight is not Q4_K (the caller falls back to the per-row kernels).
 int32_t launch_gemm_mma(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s) {
     if (w.enc != SKAINET_ENC_Q4_K) return 1;
+    if (m >= 128) {
+        const int32_t st = launch_gemm_tc(w, a, m, y, resid, s);
+        if (st != 1) return st;
+    }
     // Up to four activation rows stay with the streaming matvec kernels (faster there). Few rows: weight
     // streaming decides, so small row tiles (many CTAs) and a deep pipeline; many rows: 128 x 32 output tiles.
     if (m <= 4) return 1;

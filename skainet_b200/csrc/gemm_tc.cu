@@ -1,0 +1,361 @@
+// Batched rows on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM) for Q4_K weights
+// and m >= 128 activation rows: the prefill GEMM.
+//
+// The reference's arithmetic for one 256-element super-block (native/src/q4k_matmul.c:143-251) is
+//     y += d_x * ( d_w * S1 - dmin_w * S2 ),   S1 = sum_sb sc[sb] * <codes_sb, xq_sb>,   S2 = sum_sb mn[sb] * sum(xq_sb)
+// with 4-bit codes, 6-bit sc / mn and int8 activation codes xq. Both sums are products of small integers,
+// so they are exact in f16 x f16 -> f32: the A operand carries code*sc (<= 945 < 2048, exact in f16), the
+// B operand the activation codes, and one super-block is 16 MMAs of K = 16 accumulated in TMEM. S2 is one
+// more K = 16 MMA of (mn[sb] twice) x (sums of 16 codes, <= 2032). The CUDA cores only unpack nibbles into
+// the A operand (one LOP3 + one HFMA2 per two elements, using the 0x6400|n trick: f16(1024+n)*s - 1024*s
+// is n*s exactly under the fused rounding) and apply the three fp32 block scales once per super-block.
+//
+// CTA = 128 weight rows (TMEM lanes) x 128 activation rows (TMEM columns), 9 warps:
+//   warps 0-7  two threads per weight row: per 64-element group each writes half of that row's 64 f16 of the
+//              A stage (weights fetched one super-block ahead), thread 0 also issues the bulk copies of the B
+//              stage; after producing super-block kb they fold super-block kb-1 out of TMEM (tcgen05.ld) into
+//              64 fp32 accumulators per thread (each thread of a pair takes half of the columns);
+//   warp 8     one lane issues the MMAs and commits: stage barriers back to the producers, accumulator
+//              barriers to the epilogue; two TMEM accumulator sets so MMAs of kb+1 overlap the fold of kb.
+// Shared-memory operands use the no-swizzle K-major canonical layout (8 rows x 16 B core matrices; leading
+// byte offset = next 8 k-elements, stride byte offset = next 8 rows). The activation side is prepared once
+// per call by act_f16_tiles_kernel in exactly that order, so a B stage is one contiguous 16 KB bulk copy.
+// Every mbarrier wait is bounded; a wait that runs out raises the device flag, and the CTA still reaches
+// the common exit where TMEM is freed.
+#include "common.cuh"
+#include "actquant.cuh"
+#include "tma.cuh"
+#include "matvec_fused.cuh"
+
+#include <cuda_fp16.h>
+#include <mutex>
+
+namespace sk {
+
+namespace {
+
+constexpr int TC_M = 128, TC_N = 128, TC_KS = 64, TC_STAGES = 6;
+constexpr int TC_A_BYTES = TC_M * TC_KS * 2, TC_B_BYTES = TC_N * TC_KS * 2, TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
+constexpr int TC_S2A_BYTES = TC_M * 16 * 2, TC_S2B_BYTES = TC_N * 16 * 2, TC_S2_BYTES = TC_S2A_BYTES + TC_S2B_BYTES;
+constexpr int TC_OFF_S2 = TC_STAGES * TC_STAGE_BYTES;
+constexpr int TC_OFF_DX = TC_OFF_S2 + 2 * TC_S2_BYTES;
+constexpr int TC_OFF_BAR = TC_OFF_DX + 2 * TC_N * 4;
+constexpr int TC_NBARS = 2 * TC_STAGES + 6;      // full, empty per stage; s2_full, acc_full, acc_empty per accumulator set
+constexpr int TC_SMEM = TC_OFF_BAR + TC_NBARS * 8 + 16;
+constexpr uint32_t TC_IDESC = (1u << 4) | ((uint32_t) (TC_N >> 3) << 17) | ((uint32_t) (TC_M >> 4) << 24);   // f16 x f16 -> f32, K-major both
+
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t) ((saddr & 0x3ffffu) >> 4) | ((uint64_t) (lbo_bytes >> 4) << 16) | ((uint64_t) (sbo_bytes >> 4) << 32) | (1ull << 46);
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(skd::smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive1(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(skd::smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- activation side: int8 codes -> f16 in core-matrix order, sums of 16 codes, transposed block scales ----
+//   xh  [m_pad/128][cols/64][16][8][8 rows][8]  f16: one 16 KB B stage (128 rows x 64 k) is contiguous; inside every
+//                                               group of four k the order is (0,2,1,3), matching the order in which
+//                                               the weight nibbles leave a 32-bit word
+//   hs  [m_pad/128][bpr][16][2][8 rows][8]      f16 sums of 16 consecutive codes: 4 KB per (tile, super-block)
+//   dxt [bpr][m_pad]                            fp32 block scales
+__global__ void __launch_bounds__(256)
+act_f16_tiles_kernel(ActQ8K act, int m, int m_pad, int cols, __half* __restrict__ xh, __half* __restrict__ hs, float* __restrict__ dxt) {
+    skd::pdl_launch_dependents();
+    skd::pdl_wait();
+    const int per_row = cols >> 4;
+    const int64_t idx = (int64_t) blockIdx.x * 256 + threadIdx.x;
+    if (idx >= (int64_t) m_pad * per_row) return;
+    const int n = (int) (idx / per_row), seg = (int) (idx % per_row);        // 16 codes: elements 16*seg ..
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (n < m) raw = *reinterpret_cast<const uint4*>(act.q + (size_t) n * cols + (size_t) seg * 16);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    int sum = 0;
+    __half out[16];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int b0 = (int8_t) (w[j] & 0xff), b1 = (int8_t) ((w[j] >> 8) & 0xff), b2 = (int8_t) ((w[j] >> 16) & 0xff), b3 = (int8_t) (w[j] >> 24);
+        sum += b0 + b1 + b2 + b3;
+        out[4 * j] = __int2half_rn(b0); out[4 * j + 1] = __int2half_rn(b2); out[4 * j + 2] = __int2half_rn(b1); out[4 * j + 3] = __int2half_rn(b3);
+    }
+    const int tile = n >> 7, ng = (n & 127) >> 3, r = n & 7;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const int kcg = seg * 2 + c, it = kcg >> 3, kc = kcg & 7;            // 8-element chunk: stage it, chunk kc of the stage
+        *reinterpret_cast<uint4*>(xh + ((((size_t) tile * (cols >> 6) + it) * 16 + ng) * 8 + kc) * 64 + r * 8) = *reinterpret_cast<const uint4*>(out + 8 * c);
+    }
+    const int kb = seg >> 4, j = seg & 15;
+    hs[(((((size_t) tile * (cols >> 8) + kb) * 16 + ng) * 2 + (j >> 3)) * 8 + r) * 8 + (j & 7)] = __int2half_rn(sum);
+    if (j == 0) dxt[(size_t) kb * m_pad + n] = n < m ? act.d[(size_t) n * (cols >> 8) + kb] : 0.0f;
+}
+
+constexpr int TC_WORKERS = 256;      // two threads per weight row: each converts half of a stage and folds half of the columns
+
+__global__ void __launch_bounds__(TC_WORKERS + 32, 1)
+q4k_gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ hdr, int rows, int bpr, const __half* __restrict__ xh,
+                   const __half* __restrict__ hs, const float* __restrict__ dxt, int m, int m_pad, float* __restrict__ y,
+                   const float* __restrict__ resid, int* __restrict__ timeout_flag) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t* full = (uint64_t*) (smem + TC_OFF_BAR);
+    uint64_t* empty = full + TC_STAGES;
+    uint64_t* s2_full = empty + TC_STAGES;
+    uint64_t* acc_full = s2_full + 2;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = (uint32_t*) (acc_empty + 2);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int row0 = blockIdx.x * TC_M, col0 = blockIdx.y * TC_N;
+    constexpr int MMA_WARP = TC_WORKERS / 32;
+    skd::pdl_launch_dependents();
+
+    if (warp == MMA_WARP) {
+        if (lane == 0) {
+            for (int s = 0; s < TC_STAGES; ++s) { skd::mbar_init(full + s, TC_WORKERS + 1); skd::mbar_init(empty + s, 1); }
+            for (int b = 0; b < 2; ++b) {
+                skd::mbar_init(s2_full + b, TC_WORKERS + 1); skd::mbar_init(acc_full + b, 1); skd::mbar_init(acc_empty + b, TC_WORKERS);
+            }
+            skd::mbar_fence_init();
+        }
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(skd::smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;                  // set S at columns 256*S: S1 in 0..127, S2 in 128..255
+
+    if (warp == MMA_WARP) {
+        // ------------------------------------------------ MMA issuer ------------------------------------------------
+        if (lane == 0) {
+            bool ok = true;
+            for (int kb = 0; kb < bpr && ok; ++kb) {
+                const int set = kb & 1;
+                if (kb >= 2) ok = skd::mbar_wait_bounded(acc_empty + set, ((kb >> 1) - 1) & 1, timeout_flag);
+                tc_fence_after();
+                for (int gq = 0; gq < 4 && ok; ++gq) {
+                    const int it = kb * 4 + gq, s = it % TC_STAGES, round = it / TC_STAGES;
+                    ok = skd::mbar_wait_bounded(full + s, round & 1, timeout_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a0 = skd::smem_u32(smem + s * TC_STAGE_BYTES), b0 = a0 + TC_A_BYTES;
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; ++k4)
+                        umma_f16(tmem + set * 256, smem_desc(a0 + k4 * 256, 128, 1024), smem_desc(b0 + k4 * 256, 128, 1024), TC_IDESC,
+                                 (gq | k4) != 0 ? 1u : 0u);
+                    umma_commit(empty + s);            // the stage may be overwritten once these MMAs have read it
+                }
+                if (!ok) break;
+                ok = skd::mbar_wait_bounded(s2_full + set, (kb >> 1) & 1, timeout_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a2 = skd::smem_u32(smem + TC_OFF_S2 + set * TC_S2_BYTES), b2 = a2 + TC_S2A_BYTES;
+                umma_f16(tmem + set * 256 + 128, smem_desc(a2, 128, 256), smem_desc(b2, 128, 256), TC_IDESC, 0u);
+                umma_commit(acc_full + set);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------- producers of A, then epilogue -------------------------------------
+        const int r = tid & 127, half = tid >> 7;       // weight row of the tile; which half of a stage / of the columns
+        const int grow = min(row0 + r, rows - 1);
+        constexpr int NC = TC_N / 2;
+        float yacc[NC];
+#pragma unroll
+        for (int i = 0; i < NC; ++i) yacc[i] = 0.0f;
+        float d_prev = 0.0f, dmin_prev = 0.0f;
+        bool ok = true;
+
+        auto fold = [&](int kb, float dw, float dminw) {        // super-block kb out of TMEM into yacc
+            const int set = kb & 1;
+            if (!skd::mbar_wait_bounded(acc_full + set, (kb >> 1) & 1, timeout_flag)) { ok = false; return; }
+            tc_fence_after();
+            const float* dx = (const float*) (smem + TC_OFF_DX) + set * TC_N + half * NC;
+            const uint32_t t0 = tmem + ((uint32_t) ((warp & 3) * 32) << 16) + set * 256 + half * NC;
+#pragma unroll
+            for (int c = 0; c < NC; c += 16) {
+                float s1[16], s2[16];
+                tmem_ld16(t0 + c, s1);
+                tmem_ld16(t0 + 128 + c, s2);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) yacc[c + i] = fmaf(dx[c + i], fmaf(-dminw, s2[i], dw * s1[i]), yacc[c + i]);
+            }
+            tc_fence_before();
+            mbar_arrive1(acc_empty + set);
+        };
+
+        // this thread's 16 bytes of each 32-byte group of the row's super-block, and the header; one block ahead
+        uint4 q[4], qn[4], hd, hdn;
+        {
+            const size_t blk = (size_t) grow * bpr;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) qn[i] = skd::ld_stream(qs + blk * 128 + i * 32 + half * 16);
+            hdn = skd::ld_stream(hdr + blk * 16);
+        }
+        skd::pdl_wait();                               // the activation tiles are the predecessor's output
+
+        for (int kb = 0; kb < bpr && ok; ++kb) {
+            const int set = kb & 1;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) q[i] = qn[i];
+            hd = hdn;
+            if (kb + 1 < bpr) {
+                const size_t blk = (size_t) grow * bpr + kb + 1;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) qn[i] = skd::ld_stream(qs + blk * 128 + i * 32 + half * 16);
+                hdn = skd::ld_stream(hdr + blk * 16);
+            }
+            const float dw = __half2float(__ushort_as_half((unsigned short) (hd.x & 0xffff)));
+            const float dminw = __half2float(__ushort_as_half((unsigned short) (hd.x >> 16)));
+            uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
+            skd::k4_unpack(hd.y, hd.z, hd.w, sc_lo, sc_hi, mn_lo, mn_hi);
+
+#pragma unroll
+            for (int gq = 0; gq < 4; ++gq) {
+                const int it = kb * 4 + gq, s = it % TC_STAGES, round = it / TC_STAGES;
+                if (round > 0 && !skd::mbar_wait_bounded(empty + s, (round - 1) & 1, timeout_flag)) { ok = false; break; }
+                uint8_t* as = smem + s * TC_STAGE_BYTES;
+                if (tid == 0) {                        // B stage: one contiguous 16 KB piece of xh
+                    skd::mbar_expect_tx(full + s, TC_B_BYTES);
+                    skd::bulk_g2s(as + TC_A_BYTES, xh + ((size_t) blockIdx.y * (bpr * 4) + it) * (TC_B_BYTES / 2), TC_B_BYTES, full + s);
+                }
+                // A stage: k 0..31 = low nibbles x sc[2gq], k 32..63 = high nibbles x sc[2gq+1]; this thread's
+                // four words are bytes 16*half.. of the group: chunks 2*half, 2*half+1 of each nibble half
+                const uint32_t scw = gq < 2 ? sc_lo : sc_hi;
+                const __half s_lo = __int2half_rn((int) ((scw >> (16 * (gq & 1))) & 0xff)), s_hi = __int2half_rn((int) ((scw >> (16 * (gq & 1) + 8)) & 0xff));
+                const __half2 ml = __half2half2(s_lo), mh = __half2half2(s_hi);
+                const __half2 nl = __hmul2(ml, __float2half2_rn(-1024.0f)), nh = __hmul2(mh, __float2half2_rn(-1024.0f));
+                const uint32_t wv[4] = {q[gq].x, q[gq].y, q[gq].z, q[gq].w};
+                uint8_t* arow = as + (r >> 3) * 1024 + (r & 7) * 16;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t lo4[4], hi4[4];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t w = wv[2 * c + h];
+                        const uint32_t x02 = (w & 0x000f000fu) | 0x64006400u, x13 = ((w >> 8) & 0x000f000fu) | 0x64006400u;
+                        const uint32_t y02 = ((w >> 4) & 0x000f000fu) | 0x64006400u, y13 = ((w >> 12) & 0x000f000fu) | 0x64006400u;
+                        __half2 v;
+                        v = __hfma2(*reinterpret_cast<const __half2*>(&x02), ml, nl); lo4[2 * h] = *reinterpret_cast<uint32_t*>(&v);
+                        v = __hfma2(*reinterpret_cast<const __half2*>(&x13), ml, nl); lo4[2 * h + 1] = *reinterpret_cast<uint32_t*>(&v);
+                        v = __hfma2(*reinterpret_cast<const __half2*>(&y02), mh, nh); hi4[2 * h] = *reinterpret_cast<uint32_t*>(&v);
+                        v = __hfma2(*reinterpret_cast<const __half2*>(&y13), mh, nh); hi4[2 * h + 1] = *reinterpret_cast<uint32_t*>(&v);
+                    }
+                    *reinterpret_cast<uint4*>(arow + (2 * half + c) * 128) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
+                    *reinterpret_cast<uint4*>(arow + (4 + 2 * half + c) * 128) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
+                }
+                fence_async_smem();
+                mbar_arrive1(full + s);
+            }
+            if (!ok) break;
+            // S2 operands of this super-block: mins (each twice) against the sums of 16 codes; block scales
+            {
+                uint8_t* s2 = smem + TC_OFF_S2 + set * TC_S2_BYTES;
+                if (tid == 0) {
+                    if (kb >= 2 && !skd::mbar_wait_bounded(acc_empty + set, ((kb >> 1) - 1) & 1, timeout_flag)) { ok = false; break; }
+                    skd::mbar_expect_tx(s2_full + set, TC_S2B_BYTES + TC_N * 4);
+                    skd::bulk_g2s(s2 + TC_S2A_BYTES, hs + ((size_t) blockIdx.y * bpr + kb) * (TC_S2B_BYTES / 2), TC_S2B_BYTES, s2_full + set);
+                    skd::bulk_g2s(smem + TC_OFF_DX + set * TC_N * 4, dxt + (size_t) kb * m_pad + col0, TC_N * 4, s2_full + set);
+                }
+                const uint32_t mnw = half ? mn_hi : mn_lo;       // half h writes the chunk of sub-blocks 4h..4h+3
+                uint32_t mm[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const __half2 vv = __half2half2(__int2half_rn((int) ((mnw >> (8 * i)) & 0xff)));
+                    mm[i] = *reinterpret_cast<const uint32_t*>(&vv);
+                }
+                *reinterpret_cast<uint4*>(s2 + (r >> 3) * 256 + half * 128 + (r & 7) * 16) = make_uint4(mm[0], mm[1], mm[2], mm[3]);
+                fence_async_smem();
+                mbar_arrive1(s2_full + set);
+            }
+            if (kb > 0) fold(kb - 1, d_prev, dmin_prev);
+            d_prev = dw; dmin_prev = dminw;
+        }
+        if (ok && bpr > 0) fold(bpr - 1, d_prev, dmin_prev);
+        if (ok && row0 + r < rows) {
+#pragma unroll
+            for (int c = 0; c < NC; ++c)
+                if (col0 + half * NC + c < m) {
+                    const size_t o = (size_t) (col0 + half * NC + c) * rows + row0 + r;
+                    y[o] = resid ? resid[o] + yacc[c] : yacc[c];
+                }
+        }
+        if (!ok) {                                      // give copies in flight time to land before the CTA leaves
+            for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == MMA_WARP) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+
+struct TcScratch { void* p = nullptr; size_t bytes = 0; };
+TcScratch g_tc_scratch[64];
+std::mutex g_tc_mu;
+
+}  // namespace
+
+// y[m][w.rows] (= resid +) for m >= 128 quantized activation rows. Returns 1 when not taken (the caller
+// falls back to the mma.sync tile kernel): other encodings, few rows, or scratch that would have to grow
+// while the stream is being captured.
+int32_t launch_gemm_tc(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s) {
+    static const bool off = []() { const char* e = getenv("SKAINET_GEMM"); return e && strcmp(e, "mma") == 0; }();
+    if (off || w.enc != SKAINET_ENC_Q4_K || m < 128 || w.bpr < 1) return 1;
+    int dev = 0;
+    SK_CUDA(cudaGetDevice(&dev));
+    const int m_pad = (m + TC_N - 1) / TC_N * TC_N;
+    const size_t xh_bytes = (size_t) m_pad * w.cols * 2, hs_bytes = (size_t) m_pad * (w.cols / 16) * 2, dx_bytes = (size_t) w.bpr * m_pad * 4;
+    const size_t need = xh_bytes + hs_bytes + dx_bytes + 3 * 256;
+    void* base = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_tc_mu);
+        TcScratch& sc = g_tc_scratch[dev & 63];
+        if (sc.bytes < need) {
+            cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+            if (cudaStreamIsCapturing(s, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) { cudaGetLastError(); return 1; }
+            SK_CUDA(cudaStreamSynchronize(s));
+            if (sc.p) SK_CUDA(cudaFree(sc.p));
+            sc.p = nullptr; sc.bytes = 0;
+            SK_CUDA(cudaMalloc(&sc.p, need));
+            sc.bytes = need;
+        }
+        base = sc.p;
+    }
+    auto up = [](size_t v) { return (v + 255) & ~(size_t) 255; };
+    __half* xh = (__half*) base;
+    __half* hs = (__half*) ((uint8_t*) base + up(xh_bytes));
+    float* dxt = (float*) ((uint8_t*) base + up(xh_bytes) + up(hs_bytes));
+    static bool attr_done = false;
+    if (!attr_done) { SK_CUDA(cudaFuncSetAttribute(q4k_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM)); attr_done = true; }
+    const int64_t n16 = (int64_t) m_pad * (w.cols / 16);
+    SK_CUDA(launch_pdl(act_f16_tiles_kernel, dim3((unsigned) ((n16 + 255) / 256)), dim3(256), 0, s, a, m, m_pad, w.cols, xh, hs, dxt));
+    dim3 grid((w.rows + TC_M - 1) / TC_M, m_pad / TC_N);
+    SK_CUDA(launch_pdl(q4k_gemm_tc_kernel, grid, dim3(TC_WORKERS + 32), (size_t) TC_SMEM, s, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr,
+                       (const __half*) xh, (const __half*) hs, (const float*) dxt, m, m_pad, y, resid, device_timeout_flag()));
+    return SKAINET_CUDA_OK;
+}
+
+}  // namespace sk

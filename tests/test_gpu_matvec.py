@@ -75,7 +75,7 @@ def test_host_twins_match_reference_c_outputs(gpu, oracle, tag):
 
 @pytest.mark.parametrize("enc,n,k", [("Q4_K", 64, 256), ("Q4_K", 129, 4096), ("Q4_K", 33, 11008), ("Q4_K", 1, 512),
                                      ("Q8_0", 64, 32), ("Q8_0", 130, 4096), ("Q8_0", 9, 11008), ("Q8_0", 1, 64)])
-@pytest.mark.parametrize("m", [1, 3, 8, 13, 40])
+@pytest.mark.parametrize("m", [1, 3, 8, 13, 40, 130])
 def test_resident_matvec_matches_oracle(gpu, oracle, enc, n, k, m):
     rng = np.random.default_rng(n * 131 + k + m)
     wf = (0.02 * rng.standard_normal((n, k))).astype(np.float32)
