@@ -168,3 +168,23 @@ def test_fused_norm_quant_matvec_residual(gpu, oracle, enc, n, k):
     from skainet_b200 import _lib
     assert _lib.lib().skainet_cuda_device_status() == 0
     w.free()
+
+
+def test_tcgen05_rows_tile_kernel_is_exact_and_repeatable(gpu, oracle):
+    """m >= 128 rows take the tcgen05 kernel: several row and column tiles, ragged on both sides. The integer sums
+    are exact in f16 x f16 -> f32, so the result equals the reference's to fp32 rounding, and ten runs are
+    bit-identical (a race between the roles of the kernel shows up as a run that differs)."""
+    n, k, m = 300, 2048, 290
+    rng = np.random.default_rng(77)
+    wf = (0.02 * rng.standard_normal((n, k))).astype(np.float32)
+    packed = oracle.quantize_q4k(wf)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = gpu.Weight.upload(packed, "Q4_K", n, k)
+    ref = oracle.matmul("Q4_K", x, packed, k, n, "rm", use_ref=oracle.ref() is not None)
+    first = gpu.matmul_host(w, x)
+    rel_err_ok(first, ref, 1e-5)
+    for _ in range(9):
+        np.testing.assert_array_equal(gpu.matmul_host(w, x), first)
+    from skainet_b200 import _lib
+    assert _lib.lib().skainet_cuda_device_status() == 0
+    w.free()
