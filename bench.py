@@ -18,6 +18,8 @@ Prints ONE JSON line (rank 0). Workloads (all inputs synthetic and seeded):
   q8_0_matvec — BASELINE config 1: Q8_0 W[4096,4096], same protocol.
   attn_decode — BASELINE config 3: GQA decode attention, 32 query / 8 KV heads, head_dim 128, f16 cache of
       --context keys (default 4096) for --batch sequences; metric = K/V bytes read per second.
+  generate_7b — BASELINE config 4 as one request: 512 random prompt tokens through the real prefill, then 128 greedy
+      tokens; metric = generated tokens per second of request time, with the two phases reported apart.
   q4k_gemm — BASELINE config 2 at M = --batch rows (default 512) through the tensor-core tile kernels (tcgen05 from 128 rows);
       metric = 2*M*rows*cols operations per second, roofline against the measured cuBLAS bf16 burst.
 
@@ -55,6 +57,8 @@ DECODE_WORKLOADS = {"decode_70b": ("70b", 4096), "decode_7b": ("7b", 512)}
 ATTN_WORKLOADS = {"attn_decode": (32, 8, 128)}
 # batched rows through the tensor-core tile kernel: the Q4_K sweep shapes with --batch activation rows (default 512)
 GEMM_WORKLOADS = {"q4k_gemm": [(11008, 4096), (4096, 11008)]}
+# whole requests: (model, prompt tokens, generated tokens)
+REQUEST_WORKLOADS = {"generate_7b": ("7b", 512, 128)}
 BLOCK = {"Q4_K": (144, 256), "Q8_0": (34, 32)}
 
 
@@ -242,6 +246,8 @@ def run_reference(args) -> None:
             r = cpu_attn_rate(args.workload, args.context, max(1, args.batch)); unit = "GB/s"; metric = "attn_decode_hbm_gbs"
         elif args.workload in GEMM_WORKLOADS:
             r = cpu_gemm_rate(args.workload, args.batch if args.batch > 1 else 512, budget); unit = "TFLOP/s"; metric = "q4k_gemm_tflops"
+        elif args.workload in REQUEST_WORKLOADS:
+            r = cpu_request_rate(args.workload, budget); unit = "tokens/s"; metric = "request_generated_tokens_per_s"
         else:
             model, ctx = DECODE_WORKLOADS[args.workload]
             r = cpu_decode_rate(model, ctx, budget); unit = "tokens/s"; metric = "decode_tokens_per_s"
@@ -269,7 +275,14 @@ def dtype_of(workload: str) -> str:
 
 
 def workload_config(args, world: int, extra: dict | None = None) -> dict:
-    if args.workload in GEMM_WORKLOADS:
+    if args.workload in REQUEST_WORKLOADS:
+        model, n_prompt, n_gen = REQUEST_WORKLOADS[args.workload]
+        cfg = model_config(model)
+        c = {"workload": args.workload, "layers": cfg.n_layers, "d_model": cfg.d_model, "ffn": cfg.ffn_dim, "heads": cfg.n_heads,
+             "kv_heads": cfg.n_kv_heads, "vocab": cfg.vocab, "linear": "Q4_K", "tables": "Q8_0", "batch": 1, "prompt_tokens": n_prompt,
+             "generated_tokens": n_gen, "prompt": "uniform random token ids, seeded", "weights": "N(0,0.02) packed on device, seeded",
+             "l2": "weights per pass far larger than L2"}
+    elif args.workload in GEMM_WORKLOADS:
         c = {"workload": args.workload, "encoding": "Q4_K", "shapes_out_in": GEMM_WORKLOADS[args.workload],
              "m": args.batch if args.batch > 1 else 512, "activation": "fp32 N(0,1), quantized to int8 per 256 on the device inside the timed region",
              "weights": "N(0,0.02) packed on device, seeded", "l2": "rotating distinct weights larger than 2x L2 per sweep"}
@@ -460,6 +473,86 @@ def cpu_gemm_rate(workload: str, m: int, seconds: float) -> dict:
     return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": 4 if use_ref else 1, "kind": "reference" if use_ref else "port",
             "sample": f"{calls} single-row calls of the reference's row-major Q4_K kernel (it has no batched form); the rate per row "
                       f"does not depend on m = {m}", "seconds": dt}
+
+
+def cpu_request_rate(workload: str, budget_s: float) -> dict:
+    """The reference has no batched kernel, so a prompt token costs it one decode step: the request takes
+    (prompt + generated) steps at the per-token rate of its composed decode step."""
+    model, n_prompt, n_gen = REQUEST_WORKLOADS[workload]
+    r = cpu_decode_rate(model, n_prompt, budget_s)
+    return {"value": r["value"] * n_gen / (n_prompt + n_gen), "unit": "tokens/s", "cores": r["cores"], "kind": r["kind"],
+            "sample": f"generated tokens / ((prompt + generated) x per-token time); per-token time from: {r['sample']}", "seconds": r["seconds"]}
+
+
+def run_request(args) -> None:
+    """BASELINE config 4 end to end: a 512-token prompt through the real prefill (batched-rows kernels, causal
+    attention over the cache it fills), then 128 greedy tokens on the device. A step is one whole request;
+    value = generated tokens / request time. The host-facing variant (`e2e`) sends the prompt from host memory
+    and takes every generated token back through skainet_cuda_llama_decode."""
+    import torch
+    from skainet_b200 import device
+    from skainet_b200.llama import Llama
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local); device.set_device(local)
+    model, n_prompt, n_gen = REQUEST_WORKLOADS[args.workload]
+    cfg = model_config(model, max_seq=n_prompt + n_gen + 64, max_batch=1)
+    m = Llama(cfg)
+    m.synth(seed=100, std=0.02)
+    m.finalize()
+    prompt = (np.random.default_rng(11).integers(0, cfg.vocab, n_prompt)).astype(np.int32)
+    mstream = torch.cuda.ExternalStream(m.stream)
+
+    def request():
+        m.reset()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record(mstream)
+        nxt = m.prefill(prompt, seq=0)
+        e[1].record(mstream)
+        toks = m.generate(np.array([nxt], np.int32), n_gen - 1)
+        e[2].record(mstream)
+        torch.cuda.synchronize()
+        return e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2]), [nxt] + [int(t) for t in toks[:, 0]]
+
+    warm = max(3, args.warmup)
+    for _ in range(warm):
+        request()
+    sampler = ClockSampler(local); sampler.start()
+    steps = max(1, min(args.steps, 16))
+    pre, dec, toks = [], [], None
+    for _ in range(steps):
+        a, b, toks = request()
+        pre.append(a); dec.append(b)
+    clocks = sampler.stop()
+    pre_ms, dec_ms = float(np.mean(pre)), float(np.mean(dec))
+    # host-facing: prompt from host memory (it already is), every token back through the per-step call
+    tin = torch.zeros(1, dtype=torch.int32).pin_memory(); tout = torch.zeros(1, dtype=torch.int32).pin_memory()
+    m.reset()
+    t0 = time.perf_counter()
+    tin[0] = m.prefill(prompt, seq=0)
+    for _ in range(n_gen - 1):
+        m.decode_ptr(1, tin.data_ptr(), tout.data_ptr()); tin.copy_(tout)
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    bytes_step, launches_step = m.step_cost(1)
+    peak, peak_kind = load_peaks()
+    dec_gbs = bytes_step * (n_gen - 1) / (dec_ms * 1e-3) / 1e9
+    ms = pre_ms + dec_ms
+    line = {"metric": "request_generated_tokens_per_s", "value": n_gen / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+            "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": dtype_of("decode_7b"), "data": "synthetic", "config": workload_config(args, 1),
+            "phases": {"prefill_ms": pre_ms, "prefill_tokens_per_s": n_prompt / (pre_ms * 1e-3), "decode_ms": dec_ms,
+                       "decode_tokens_per_s": (n_gen - 1) / (dec_ms * 1e-3)},
+            "roofline": {"bound": "hbm", "achieved": dec_gbs, "peak": peak, "unit": "GB/s", "frac": dec_gbs / peak,
+                         "traffic": None, "peak_kind": peak_kind, "kernel": "q4k_matvec_ring_kernel",
+                         "note": "decode phase: bytes a step must read x steps / decode time (the prefill phase is tensor-bound: see the q4k_gemm workload)"},
+            "e2e": {"value": n_gen / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * n_prompt + 4 * (n_gen - 1),
+                    "d2h_bytes_per_step": 4 * n_gen},
+            "gpu_launches": launches_step * (n_gen - 1) * steps, "clocks": clocks, "tokens_head": toks[:4]}
+    if not args.skip_cpu:
+        cpu = cpu_request_rate(args.workload, 20.0)
+        line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line), flush=True)
+    m.free()
 
 
 def run_gemm(args) -> None:
@@ -709,7 +802,7 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="decode_70b", choices=sorted(MATVEC_WORKLOADS) + sorted(DECODE_WORKLOADS) + sorted(ATTN_WORKLOADS) + sorted(GEMM_WORKLOADS))
+    ap.add_argument("--workload", default="decode_70b", choices=sorted(MATVEC_WORKLOADS) + sorted(DECODE_WORKLOADS) + sorted(ATTN_WORKLOADS) + sorted(GEMM_WORKLOADS) + sorted(REQUEST_WORKLOADS))
     ap.add_argument("--context", type=int, default=4096, help="keys per sequence (attn_decode workload)")
     ap.add_argument("--batch", type=int, default=1, help="sequences decoded together (decode workloads)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -724,6 +817,8 @@ def main() -> None:
         run_attn(args)
     elif args.workload in GEMM_WORKLOADS:
         run_gemm(args)
+    elif args.workload in REQUEST_WORKLOADS:
+        run_request(args)
     else:
         run_decode(args)
 
