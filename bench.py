@@ -5,22 +5,22 @@
 
 Prints ONE JSON line (rank 0). Workloads (all inputs synthetic and seeded):
 
-  decode_70b (default) — BASELINE config 5: Llama-style 80 layers, d 8192, FFN 28672, 64 q / 8 kv
+  decode_70b (default) — benchmark config 5: Llama-style 80 layers, d 8192, FFN 28672, 64 q / 8 kv
       heads, vocab 128256, all Q4_K, random-init N(0,0.02) packed on the device; greedy decode at
       batch 1 behind a 4096-token context, tensor-parallel over the N GPUs (strong scaling: the same
       model and batch at every N). metric = decode tokens/s. A step is one decode step (one token per
       sequence). The context's K/V are seeded noise, not a real prefill (the reference has no batched
       GEMM, so a 4096-row prompt is out of reach for its side). --batch B decodes B sequences.
-  decode_7b — BASELINE config 4: 32 layers, d 4096, FFN 11008, 32 heads, vocab 32000; Q4_K linears,
+  decode_7b — benchmark config 4: 32 layers, d 4096, FFN 11008, 32 heads, vocab 32000; Q4_K linears,
       Q8_0 embedding/output; batch 1 behind a 512-token context.
-  q4k_matvec — BASELINE config 2 at M=1: W[11008,4096] and W[4096,11008]; metric = algorithmic HBM
+  q4k_matvec — benchmark config 2 at M=1: W[11008,4096] and W[4096,11008]; metric = algorithmic HBM
       GB/s over a sweep of distinct weights larger than 2x L2.
-  q8_0_matvec — BASELINE config 1: Q8_0 W[4096,4096], same protocol.
-  attn_decode — BASELINE config 3: GQA decode attention, 32 query / 8 KV heads, head_dim 128, f16 cache of
+  q8_0_matvec — benchmark config 1: Q8_0 W[4096,4096], same protocol.
+  attn_decode — benchmark config 3: GQA decode attention, 32 query / 8 KV heads, head_dim 128, f16 cache of
       --context keys (default 4096) for --batch sequences; metric = K/V bytes read per second.
-  generate_7b — BASELINE config 4 as one request: 512 random prompt tokens through the real prefill, then 128 greedy
+  generate_7b — benchmark config 4 as one request: 512 random prompt tokens through the real prefill, then 128 greedy
       tokens; metric = generated tokens per second of request time, with the two phases reported apart.
-  q4k_gemm — BASELINE config 2 at M = --batch rows (default 512) through the tensor-core tile kernels (tcgen05 from 128 rows);
+  q4k_gemm — benchmark config 2 at M = --batch rows (default 512) through the tensor-core tile kernels (tcgen05 from 128 rows);
       metric = 2*M*rows*cols operations per second, roofline against the measured cuBLAS bf16 burst.
 
 `value` is timed on the device with everything resident in HBM (decode: one CUDA-graph replay per
@@ -485,7 +485,7 @@ def cpu_request_rate(workload: str, budget_s: float) -> dict:
 
 
 def run_request(args) -> None:
-    """BASELINE config 4 end to end: a 512-token prompt through the real prefill (batched-rows kernels, causal
+    """benchmark config 4 end to end: a 512-token prompt through the real prefill (batched-rows kernels, causal
     attention over the cache it fills), then 128 greedy tokens on the device. A step is one whole request;
     value = generated tokens / request time. The host-facing variant (`e2e`) sends the prompt from host memory
     and takes every generated token back through skainet_cuda_llama_decode."""

@@ -34,7 +34,7 @@ typedef struct {
     int32_t rope_mode;        /* 0 = pairs (2i, 2i+1), 1 = pairs (i, i + head_dim/2) */
     int32_t max_seq;          /* KV cache capacity in tokens per sequence */
     int32_t max_batch;        /* sequences decoded together */
-    int32_t linear_enc;       /* SKAINET_ENC_* of q/k/v/o/gate/up/down (Q4_K in the BASELINE configs) */
+    int32_t linear_enc;       /* SKAINET_ENC_* of q/k/v/o/gate/up/down (Q4_K in the benchmark configs) */
     int32_t table_enc;        /* SKAINET_ENC_* of the embedding table and the output head */
     int32_t tp_rank, tp_world;/* tensor parallel position; world 1 = single GPU */
 } skainet_llama_config;

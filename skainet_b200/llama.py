@@ -40,12 +40,12 @@ class LlamaConfig:
 
     @classmethod
     def llama7b(cls, **kw) -> "LlamaConfig":
-        """BASELINE config 4: 32 layers, d 4096, FFN 11008, 32 heads, vocab 32000; Q4_K linears, Q8_0 embed/output."""
+        """Llama-7B shape: 32 layers, d 4096, FFN 11008, 32 heads, vocab 32000; Q4_K linears, Q8_0 embed/output."""
         return cls(32, 4096, 32, 32, 128, 11008, 32000, **kw)
 
     @classmethod
     def llama70b(cls, **kw) -> "LlamaConfig":
-        """BASELINE config 5: 80 layers, d 8192, FFN 28672, 64 q / 8 kv heads, vocab 128256, all Q4_K."""
+        """Llama-70B-class shape: 80 layers, d 8192, FFN 28672, 64 q / 8 kv heads, vocab 128256, all Q4_K."""
         kw.setdefault("table_enc", "Q4_K")
         return cls(80, 8192, 64, 8, 128, 28672, 128256, **kw)
 

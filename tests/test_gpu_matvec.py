@@ -116,7 +116,7 @@ def test_zero_activation_blocks(gpu, oracle):
 
 
 def test_linearity_at_full_size_q4k(gpu):
-    """Size-independent property at the BASELINE shape (11008 x 4096, F32 mode is linear in x):
+    """Size-independent property at the full benchmark shape (11008 x 4096, F32 mode is linear in x):
     W(a + b) == W a + W b within fp32 rounding, on a device-generated weight."""
     w = gpu.Weight.synth("Q4_K", 11008, 4096, seed=3, std=0.02)
     rng = np.random.default_rng(10)

@@ -116,7 +116,7 @@ def test_rope_swiglu_argmax_embed_resident(gpu, oracle):
 @pytest.mark.parametrize("B,H,Hkv,D,L", [(1, 32, 8, 128, 512), (2, 32, 8, 128, 777), (3, 8, 8, 128, 100), (2, 16, 2, 64, 300),
                                          (1, 64, 8, 128, 4096), (2, 4, 2, 128, 1)])
 def test_decode_attention_f16_cache_matches_oracle(gpu, oracle, B, H, Hkv, D, L):
-    """BASELINE config 3 in miniature: q fp32, K/V binary16 in a cache longer than the visible length,
+    """The decode-attention benchmark shape in miniature: q fp32, K/V binary16 in a cache longer than the visible length,
     per-batch lengths; the oracle is the reference SDPA on the exact f16->f32 values."""
     rng = np.random.default_rng(B * 1000 + L)
     stride = L + 13
