@@ -654,12 +654,175 @@ int32_t launch_sdpa_f32(const float* q, const float* k, const float* v, float* o
                                 right_context, lengths, nullptr, mask, mb, mh, mq, mk, 0, s);
 }
 
+// =================================================================================================
+// Prefill attention on the tensor cores: the same fragment scheme as attn_decode_mma_kernel with the roles of
+// the MMA rows changed: rows 0..7 are eight CONSECUTIVE QUERY POSITIONS of one head (f16 high parts; rows
+// 8..15 the low parts), so a K/V tile read once serves eight queries. Each row has its own causal (and
+// window) limit; one CTA sees the whole key range of its queries, so the result is final (no split records).
+// grid (ceil(seq_q/8), heads, batch), eight warps taking 16-key tiles round-robin, two tiles in flight per warp.
+// q / out are token-major [batch, seq_q, heads, D]; query qi of batch b sits at q_abs_base[b] + qi.
+// =================================================================================================
+template <int D>
+__global__ void __launch_bounds__(AM_WARPS * 32)
+attn_prefill_mma_kernel(const float* __restrict__ q, const __half* __restrict__ kc, const __half* __restrict__ vc, float* __restrict__ out,
+                        int heads, int kv_heads, int seq_q, int64_t cache_stride, const int32_t* __restrict__ q_abs_base,
+                        float scale, int window) {
+    constexpr int S4 = D / 32, KS = D / 16, U = D / 64, NT = D / 8;
+    __shared__ float sm_m[AM_WARPS][8], sm_l[AM_WARPS][8], sm_c[AM_WARPS][8];
+    __shared__ uint32_t sm_q[KS][4][32];
+    __shared__ float sm_acc[AM_WARPS][8][D + 4];
+    skd::pdl_launch_dependents();
+    skd::pdl_wait();
+
+    const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int kvh = h / (heads / kv_heads);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int base = __ldg(q_abs_base + b);
+    const int nq = min(8, seq_q - qt * 8);                        // live query rows of this tile
+    // row g: keys [first_g, end_g); the CTA walks [begin, stop)
+    const int qi = qt * 8 + g;
+    const int end_g = g < nq ? base + qi + 1 : 0;
+    const int first_g = window > 0 ? max(0, end_g - window) : 0;
+    const int stop = base + qt * 8 + nq;
+    const int begin = window > 0 ? max(0, base + qt * 8 + 1 - window) : 0;
+
+    const __half* kb = kc + ((int64_t) b * kv_heads + kvh) * cache_stride * D;
+    const __half* vb = vc + ((int64_t) b * kv_heads + kvh) * cache_stride * D;
+    const uint4 zero4 = make_uint4(0, 0, 0, 0);
+    uint4 krA[2][S4], vrA[4][U], krB[2][S4], vrB[4][U];
+    auto load_tile = [&](uint4 (&kr)[2][S4], uint4 (&vr)[4][U], int k0) {
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const int key = k0 + 8 * nt + g;
+#pragma unroll
+            for (int s = 0; s < S4; ++s) kr[nt][s] = key < stop ? skd::ld_ro(kb + (int64_t) key * D + (t + 4 * s) * 8) : zero4;
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            const int key = k0 + 2 * t + (kk & 1) + 8 * (kk >> 1);
+#pragma unroll
+            for (int u = 0; u < U; ++u) vr[kk][u] = key < stop ? skd::ld_ro(vb + (int64_t) key * D + (g + 8 * u) * 8) : zero4;
+        }
+    };
+    constexpr int STEP = AM_WARPS * 16;
+    int k0 = (begin & ~15) + warp * 16;
+    if (k0 < stop) load_tile(krA, vrA, k0);
+    if (k0 + STEP < stop) load_tile(krB, vrB, k0 + STEP);
+
+    for (int ks = warp; ks < KS; ks += AM_WARPS) {
+        float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (g < nq) f = __ldg((const float4*) (q + (((int64_t) b * seq_q + qi) * heads + h) * D + (t + 4 * (ks >> 1)) * 8 + 4 * (ks & 1)));
+        uint32_t h0, l0, h1, l1;
+        split_pack(f.x, f.y, h0, l0);
+        split_pack(f.z, f.w, h1, l1);
+        sm_q[ks][0][lane] = h0; sm_q[ks][1][lane] = l0; sm_q[ks][2][lane] = h1; sm_q[ks][3][lane] = l1;
+    }
+    __syncthreads();
+    uint32_t qa[KS][4];
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) qa[ks][j] = sm_q[ks][j][lane];
+
+    float m = MASKED, l = 0.0f;
+    float o[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) { o[i][0] = 0.f; o[i][1] = 0.f; o[i][2] = 0.f; o[i][3] = 0.f; }
+
+    auto tile = [&](const uint4 (&kr)[2][S4], const uint4 (&vr)[4][U], int k0) {
+        float sc[4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int s = 0; s < S4; ++s) {
+                mma_f16(c, qa[2 * s], kr[nt][s].x, kr[nt][s].y);
+                mma_f16(c, qa[2 * s + 1], kr[nt][s].z, kr[nt][s].w);
+            }
+            const int key = k0 + 8 * nt + 2 * t;
+            sc[2 * nt] = (key >= first_g && key < end_g) ? (c[0] + c[2]) * scale : MASKED;
+            sc[2 * nt + 1] = (key + 1 >= first_g && key + 1 < end_g) ? (c[1] + c[3]) * scale : MASKED;
+        }
+        float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float mnew = fmaxf(m, mx);
+        const float corr = fast_exp(m - mnew);
+        const bool rescale = m != mnew && l != 0.0f;
+        m = mnew;
+        float p[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p[i] = sc[i] > 0.5f * MASKED ? fast_exp(sc[i] - mnew) : 0.0f;
+        l = l * corr + (p[0] + p[1]) + (p[2] + p[3]);
+        if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+            for (int i = 0; i < NT; ++i) { o[i][0] *= corr; o[i][1] *= corr; o[i][2] *= corr; o[i][3] *= corr; }
+        }
+        uint32_t pa[4];
+        split_pack(p[0], p[1], pa[0], pa[1]);
+        split_pack(p[2], p[3], pa[2], pa[3]);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t v0[4] = {vr[0][u].x, vr[0][u].y, vr[0][u].z, vr[0][u].w}, v1[4] = {vr[1][u].x, vr[1][u].y, vr[1][u].z, vr[1][u].w};
+            const uint32_t v8[4] = {vr[2][u].x, vr[2][u].y, vr[2][u].z, vr[2][u].w}, v9[4] = {vr[3][u].x, vr[3][u].y, vr[3][u].z, vr[3][u].w};
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                mma_f16(o[u * 8 + 2 * r], pa, __byte_perm(v0[r], v1[r], 0x5410), __byte_perm(v8[r], v9[r], 0x5410));
+                mma_f16(o[u * 8 + 2 * r + 1], pa, __byte_perm(v0[r], v1[r], 0x7632), __byte_perm(v8[r], v9[r], 0x7632));
+            }
+        }
+    };
+    while (k0 < stop) {
+        tile(krA, vrA, k0);
+        if (k0 + 2 * STEP < stop) load_tile(krA, vrA, k0 + 2 * STEP);
+        k0 += STEP;
+        if (k0 >= stop) break;
+        tile(krB, vrB, k0);
+        if (k0 + 2 * STEP < stop) load_tile(krB, vrB, k0 + 2 * STEP);
+        k0 += STEP;
+    }
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (t == 0) { sm_m[warp][g] = m; sm_l[warp][g] = l; }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            sm_acc[warp][g][8 * (2 * t + 8 * u) + i] = o[u * 8 + i][0] + o[u * 8 + i][2];
+            sm_acc[warp][g][8 * (2 * t + 1 + 8 * u) + i] = o[u * 8 + i][1] + o[u * 8 + i][3];
+        }
+    __syncthreads();
+    if (threadIdx.x < 8 * AM_WARPS) {
+        const int w = threadIdx.x >> 3, hg = threadIdx.x & 7;
+        float mxx = MASKED;
+#pragma unroll
+        for (int w2 = 0; w2 < AM_WARPS; ++w2) mxx = fmaxf(mxx, sm_m[w2][hg]);
+        sm_c[w][hg] = fast_exp(sm_m[w][hg] - mxx);
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nq * D; idx += AM_WARPS * 32) {
+        const int hg = idx / D, dd = idx % D;
+        float at = 0.0f, lt = 0.0f;
+#pragma unroll
+        for (int w = 0; w < AM_WARPS; ++w) { at += sm_c[w][hg] * sm_acc[w][hg][dd]; lt += sm_c[w][hg] * sm_l[w][hg]; }
+        out[(((int64_t) b * seq_q + qt * 8 + hg) * heads + h) * D + dd] = lt > 0.0f ? at / lt : 0.0f;
+    }
+}
+
 // Causal attention of a block of new queries over an f16 cache (prefill): query qi of batch b sits at
 // absolute position q_abs_base[b] + qi and sees keys [0, that position]. q/out are token-major
 // [batch, seq_q, heads, D], the layout the projections produce.
 int32_t launch_sdpa_cache(const float* q, const __half* k, const __half* v, float* out, int batch, int heads,
                           int kv_heads, int seq_q, int seq_kv, int64_t cache_stride, int d, float scale, int window,
                           const int32_t* q_abs_base, cudaStream_t s) {
+    // SKAINET_ATTN=simt keeps the CUDA-core row kernel (A/B measurements)
+    static const bool simt = []() { const char* e = getenv("SKAINET_ATTN"); return e && strcmp(e, "simt") == 0; }();
+    if (!simt && (d == 128 || d == 64) && batch > 0 && seq_q > 0 && heads % kv_heads == 0 && batch <= 65535 && heads <= 65535) {
+        dim3 grid((seq_q + 7) / 8, heads, batch);
+        if (d == 128) SK_CUDA(launch_pdl(attn_prefill_mma_kernel<128>, grid, dim3(AM_WARPS * 32), 0, s, q, k, v, out, heads, kv_heads, seq_q, cache_stride, q_abs_base, scale, window));
+        else SK_CUDA(launch_pdl(attn_prefill_mma_kernel<64>, grid, dim3(AM_WARPS * 32), 0, s, q, k, v, out, heads, kv_heads, seq_q, cache_stride, q_abs_base, scale, window));
+        return SKAINET_CUDA_OK;
+    }
     return launch_sdpa_t<__half>(q, k, v, out, batch, heads, kv_heads, seq_q, seq_kv, cache_stride, d, scale, 1, window,
                                  0, nullptr, q_abs_base, nullptr, 0, 0, 0, 0, 1, s);
 }
