@@ -10,6 +10,9 @@
 // store round instead of NCCL's multi-step protocol: what matters for a 32 KB sum issued 160 times per token.
 #include "comm.cuh"
 #include "tma.cuh"
+#include "actquant.cuh"
+
+#include <cooperative_groups.h>
 
 #include <dlfcn.h>
 #include <cstring>
@@ -76,12 +79,16 @@ constexpr int P2P_SPIN_LIMIT = 1 << 24;             // ~1 s of polling, then the
 // Per-rank region, identical layout on every rank:
 //   inbox [2][world][P2P_MAX_ELEMS] float | flags [world][P2P_MAX_CTAS] int | seq [P2P_MAX_CTAS] int (local only)
 struct P2PView {
-    float* inbox[P2P_MAX_WORLD];    // base of each rank's region as mapped into this process
+    float* inbox[P2P_MAX_WORLD];    // base of each rank's channel as mapped into this process
     int rank, world;
 };
-static size_t p2p_region_bytes(int world) {
+static size_t p2p_channel_bytes(int world) {
     return (size_t) 2 * world * P2P_MAX_ELEMS * 4 + (size_t) world * P2P_MAX_CTAS * 4 + P2P_MAX_CTAS * 4;
 }
+// Two channels with the layout above: channel 0 for the plain all-reduce (slot = 1024 floats), channel 1 for the
+// fused all-reduce + RMSNorm + quantize (slot = 2048 floats). Inside a channel a slot always covers the same
+// floats, which is what lets the two inbox copies alternate safely; mixing slot sizes in one channel would not.
+static size_t p2p_region_bytes(int world) { return 2 * ((p2p_channel_bytes(world) + 255) & ~(size_t) 255); }
 __device__ __forceinline__ int* p2p_flags(float* base, int world) { return (int*) (base + (size_t) 2 * world * P2P_MAX_ELEMS); }
 
 __global__ void __launch_bounds__(256)
@@ -133,11 +140,98 @@ allreduce_oneshot_kernel(P2PView v, float* __restrict__ buf, int n, int* __restr
     if (threadIdx.x == 0) *seq_slot = seq;
 }
 
+// All-reduce of rows of x over the group fused with what always follows it in the decoder: RMSNorm with weights
+// gamma and the int8-per-256 activation quantizer. One thread-block cluster per row, one CTA per 2048 floats
+// (256 threads x 8): exchange and sum as above (the sum is also written back to x, the residual stream), then the
+// CTAs of the cluster add up their sums of squares through distributed shared memory and each normalises and
+// quantizes its own 2048 values (one warp = one 256-block, as in prep_kernel).
+constexpr int P2P_FUSED_CTA_ELEMS = 2048;
+__global__ void __launch_bounds__(256)
+allreduce_norm_quant_kernel(P2PView v, float* __restrict__ x, int n, const float* __restrict__ gamma, float eps, ActQ8K act,
+                            int* __restrict__ timeout_flag) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ int s_seq;
+    __shared__ float s_red[8];
+    __shared__ float s_part;                           // this CTA's sum of squares, read by the whole cluster
+    skd::pdl_launch_dependents();
+    const int cs = gridDim.x, cx = blockIdx.x, row = blockIdx.y;
+    const int cta = row * cs + cx, world = v.world, rank = v.rank;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* mine = v.inbox[rank];
+    int* my_flags = p2p_flags(mine, world);
+    int* seq_slot = my_flags + world * P2P_MAX_CTAS + cta;
+    const int col = cx * P2P_FUSED_CTA_ELEMS + threadIdx.x * 8;           // this thread's 8 floats of the row
+    const int64_t i = (int64_t) cta * P2P_FUSED_CTA_ELEMS + threadIdx.x * 8;   // ... and of the inbox
+    float* xr = x + (size_t) row * n + col;
+    skd::pdl_wait();
+    if (threadIdx.x == 0) s_seq = *seq_slot + 1;
+    __syncthreads();
+    const int seq = s_seq, par = seq & 1;
+    const float4 own0 = *reinterpret_cast<const float4*>(xr), own1 = *reinterpret_cast<const float4*>(xr + 4);
+    for (int p = 0; p < world; ++p)
+        if (p != rank) {
+            float* dst = v.inbox[p] + ((size_t) par * world + rank) * P2P_MAX_ELEMS + i;
+            *reinterpret_cast<float4*>(dst) = own0; *reinterpret_cast<float4*>(dst + 4) = own1;
+        }
+    __syncthreads();
+    if (threadIdx.x < world && (int) threadIdx.x != rank) {
+        __threadfence_system();
+        int* peer_flag = p2p_flags(v.inbox[threadIdx.x], world) + rank * P2P_MAX_CTAS + cta;
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(peer_flag), "r"(seq) : "memory");
+        const int* f = my_flags + threadIdx.x * P2P_MAX_CTAS + cta;
+        int got = 0, spins = 0;
+        do {
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(got) : "l"(f) : "memory");
+        } while (got < seq && ++spins < P2P_SPIN_LIMIT);
+        if (got < seq && timeout_flag) atomicExch(timeout_flag, 2);
+    }
+    __syncthreads();
+    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int p = 0; p < world; ++p) {                  // rank order: every rank gets the same bits
+        float4 u0 = own0, u1 = own1;
+        if (p != rank) {
+            const float* src = mine + ((size_t) par * world + p) * P2P_MAX_ELEMS + i;
+            u0 = __ldcg(reinterpret_cast<const float4*>(src)); u1 = __ldcg(reinterpret_cast<const float4*>(src + 4));
+        }
+        a[0] += u0.x; a[1] += u0.y; a[2] += u0.z; a[3] += u0.w; a[4] += u1.x; a[5] += u1.y; a[6] += u1.z; a[7] += u1.w;
+    }
+    *reinterpret_cast<float4*>(xr) = make_float4(a[0], a[1], a[2], a[3]);
+    *reinterpret_cast<float4*>(xr + 4) = make_float4(a[4], a[5], a[6], a[7]);
+    if (threadIdx.x == 0) *seq_slot = seq;
+    // sum of squares of the row: warp, CTA, cluster (fixed orders)
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ss += a[k] * a[k];
+    ss = skd::warp_sum(ss);
+    if (lane == 0) s_red[warp] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) t += s_red[k];
+        s_part = t;
+    }
+    cluster.sync();
+    float total = 0.0f;
+    for (int r = 0; r < cs; ++r) total += *cluster.map_shared_rank(&s_part, r);
+    cluster.sync();                                    // nobody leaves while its shared memory may still be read
+    const float nscale = 1.0f / sqrtf(total * (1.0f / (float) n) + eps);
+    const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + col)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + col + 4));
+    const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) a[k] = (a[k] * nscale) * g[k];
+    const int blk = col >> 8;
+    skd::quant_q8k_regs(a, act.q + (size_t) row * n + (size_t) blk * 256, act.d + (size_t) row * (n >> 8) + blk,
+                        act.bsums + (size_t) row * (n >> 5) + (size_t) blk * 8, lane);
+}
+
 struct Comm {
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1;
     bool p2p = false;
-    P2PView view = {};
+    P2PView view = {};              // channel 0: plain all-reduce
+    P2PView view_fused = {};        // channel 1: all-reduce + RMSNorm + quantize
     void* region = nullptr;          // this rank's region (cudaMalloc)
     void* peers[P2P_MAX_WORLD] = {}; // opened IPC mappings (null for self)
 };
@@ -185,6 +279,10 @@ static void p2p_setup(Comm* c) {
     }
     cudaGetLastError();
     c->view.rank = c->rank; c->view.world = c->world;
+    c->view_fused = c->view;
+    const size_t ch = (p2p_channel_bytes(c->world) + 255) & ~(size_t) 255;
+    for (int p = 0; p < c->world; ++p)
+        if (c->view.inbox[p]) c->view_fused.inbox[p] = (float*) ((uint8_t*) c->view.inbox[p] + ch);
     c->p2p = sum == c->world;
 }
 
@@ -228,6 +326,25 @@ int32_t comm_all_reduce_sum(Comm* c, float* buf, int64_t n, cudaStream_t s) {
     }
     const ncclResult_t r = g_nccl.AllReduce(buf, buf, (size_t) n, ncclFloat32, ncclSum, c->comm, s);
     return r == 0 ? SKAINET_CUDA_OK : nccl_fail(r, "ncclAllReduce");
+}
+
+// In place: x[rows][n] <- sum over the group; act <- quantize(rmsnorm(x, gamma)). Returns 1 when the fused kernel
+// does not apply (no peer mapping, shapes outside its slots): the caller then runs the two steps separately.
+int32_t comm_all_reduce_norm_quant(Comm* c, float* x, int rows, int n, const float* gamma, float eps, ActQ8K act, cudaStream_t s) {
+    static const bool off = []() { const char* e = getenv("SKAINET_TP_FUSE"); return e && strcmp(e, "0") == 0; }();
+    if (off || !c || !c->p2p || n % P2P_FUSED_CTA_ELEMS != 0) return 1;
+    const int cs = n / P2P_FUSED_CTA_ELEMS;
+    if (cs > 8 || rows * cs > P2P_MAX_CTAS || (int64_t) rows * n > P2P_MAX_ELEMS || ((uintptr_t) x & 15) != 0) return 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cs, rows); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = s;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = cs; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
+    attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs; cfg.numAttrs = 2;
+    SK_CUDA(cudaLaunchKernelEx(&cfg, allreduce_norm_quant_kernel, c->view_fused, x, n, gamma, eps, act, device_timeout_flag()));
+    return SKAINET_CUDA_OK;
 }
 
 int32_t comm_all_gather(Comm* c, const void* send, void* recv, int64_t nbytes, cudaStream_t s) {

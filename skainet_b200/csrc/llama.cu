@@ -326,9 +326,21 @@ static int32_t body(Model& m, int rows, bool prefill, int seq, int kv_bound, cud
     const bool lin_split = c.linear_enc == SKAINET_ENC_Q8_0;
     const float scale = 1.0f / sqrtf((float) D);
     const bool tp = c.tp_world > 1, rank0 = c.tp_rank == 0;
+    // Under TP the group sum of a row-parallel projection is fused with the RMSNorm + quantizer that follows it
+    // when the peer-memory kernel applies; `normed` says the next layer's input is already prepared.
+    auto sum_then_norm = [&](const float* gamma) -> int32_t {
+        if (tp && !lin_split) {
+            const int32_t st = comm_all_reduce_norm_quant(m.comm, m.x, rows, c.d_model, gamma, c.rms_eps, act_q8k_layout(m.act, rows, c.d_model), s);
+            if (st != 1) return st;
+        }
+        SK_TRY(tp_sum(m, m.x, (int64_t) rows * c.d_model, s));
+        return prep<PK_NORM>(m, m.x, gamma, rows, c.d_model, lin_split, s);
+    };
+    bool normed = false;
     for (int l = 0; l < c.n_layers; ++l) {
         Layer& L = m.layers[l];
-        SK_TRY(prep<PK_NORM>(m, m.x, L.g_attn, rows, c.d_model, lin_split, s));
+        if (!normed) SK_TRY(prep<PK_NORM>(m, m.x, L.g_attn, rows, c.d_model, lin_split, s));
+        normed = false;
         SK_TRY(linear(m, *L.wqkv, rows, m.qkv, nullptr, s));
         SK_CUDA(launch_pdl(rope_append_kernel, dim3(rows, H + 2 * HK), dim3(D / 2), 0, s, m.qkv, H, HK, D, (const float*) m.cos_t,
                            (const float*) m.sin_t, (const int32_t*) m.pos, (const int32_t*) (prefill ? m.row_seq : nullptr), prefill ? 1 : 0,
@@ -350,12 +362,12 @@ static int32_t body(Model& m, int rows, bool prefill, int seq, int kv_bound, cud
         if (!fused_attn) SK_TRY(prep<PK_QUANT>(m, m.attn, nullptr, rows, H * D, lin_split, s));
         // row-parallel projections under TP: rank 0 carries the residual, then the group sums
         if (tp && !rank0) SK_TRY(linear(m, *L.wo, rows, m.x, nullptr, s)); else SK_TRY(linear(m, *L.wo, rows, nullptr, m.x, s));
-        SK_TRY(tp_sum(m, m.x, (int64_t) rows * c.d_model, s));
-        SK_TRY(prep<PK_NORM>(m, m.x, L.g_ffn, rows, c.d_model, lin_split, s));
+        SK_TRY(sum_then_norm(L.g_ffn));
         SK_TRY(linear(m, *L.wgu, rows, m.gu, nullptr, s));
         SK_TRY(prep<PK_SWIGLU>(m, m.gu, nullptr, rows, m.ffn_l, lin_split, s));
         if (tp && !rank0) SK_TRY(linear(m, *L.wdown, rows, m.x, nullptr, s)); else SK_TRY(linear(m, *L.wdown, rows, nullptr, m.x, s));
-        SK_TRY(tp_sum(m, m.x, (int64_t) rows * c.d_model, s));
+        if (tp && l + 1 < c.n_layers) { SK_TRY(sum_then_norm(m.layers[l + 1].g_attn)); normed = true; }
+        else SK_TRY(tp_sum(m, m.x, (int64_t) rows * c.d_model, s));
     }
     return SKAINET_CUDA_OK;
 }
