@@ -14,10 +14,10 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def run_world(world: int) -> dict:
+def run_world(world: int, d_model: int) -> dict:
     work = tempfile.mkdtemp(prefix=f"tp{world}_")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), str(r), str(world), work], env=env,
+    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), str(r), str(world), work, str(d_model)], env=env,
                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
     outs = []
     for p in procs:
@@ -33,10 +33,13 @@ def run_world(world: int) -> dict:
     return dict(np.load(os.path.join(work, "out.npz")))
 
 
-def test_tp2_matches_single_gpu(gpu):
+# d_model 1024: group sums by the plain one-shot all-reduce, norm separately; 4096: the fused all-reduce + RMSNorm +
+# quantize kernel (two CTAs per row in one cluster) takes the sums inside the layer stack
+@pytest.mark.parametrize("d_model", [1024, 4096])
+def test_tp2_matches_single_gpu(gpu, d_model):
     if gpu.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    one, two = run_world(1), run_world(2)
+    one, two = run_world(1, d_model), run_world(2, d_model)
     # same seeded tensors, sharded: logits agree to fp32 summation order (K-shards quantize their slice
     # of the activation exactly as the unsharded kernel does), tokens identical unless a near tie
     rel_err_ok(two["logits0"], one["logits0"], 2e-3)

@@ -1,6 +1,6 @@
 """One tensor-parallel rank of the decoder (run as a child process by tests/test_gpu_tp.py).
 
-    python tests/tp_worker.py RANK WORLD WORKDIR
+    python tests/tp_worker.py RANK WORLD WORKDIR [D_MODEL]
 
 Builds this rank's shard of a seeded small model, joins the TP group (rank 0 writes the NCCL unique id
 to WORKDIR/id.bin), prefills a prompt, generates greedily, and rank 0 writes tokens + logits to WORKDIR/out.npz.
@@ -20,7 +20,8 @@ def main():
     from skainet_b200 import device
     from skainet_b200.llama import Llama, LlamaConfig
     device.set_device(rank if device.device_count() > rank else 0)
-    cfg = LlamaConfig(2, 1024, 8, 4, 64, 2048, 1000, max_seq=64, max_batch=2, tp_rank=rank, tp_world=world)
+    d_model = int(sys.argv[4]) if len(sys.argv) > 4 else 1024
+    cfg = LlamaConfig(2, d_model, 8, 4, 64, 2048, 1000, max_seq=64, max_batch=2, tp_rank=rank, tp_world=world)
     m = Llama(cfg)
     m.synth(seed=77, std=0.05)
     m.finalize()
