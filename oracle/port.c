@@ -250,6 +250,84 @@ API void oracle_q4k_matmul(const float* in, const uint8_t* w, int32_t input_dim,
     free(q8); free(di);
 }
 
+/* Q6_K matvec, row-major. native/src/q6k_matmul.c:53-67 (activation quantizer = the Q4_K one), :83-128 (centered
+ * codes in element order), :155-177 (weighted dot over sixteen 16-element scale groups, gs = half*8 + is + 2k),
+ * :187-215 (block term d * d_in * (float) wdot), :252-268 (row loop). */
+API void oracle_q6k_matmul(const float* in, const uint8_t* w, int32_t input_dim, int32_t output_dim, float* out) {
+    if (output_dim <= 0 || input_dim <= 0) return;
+    const int32_t nb = input_dim / 256;
+    int8_t* q8 = (int8_t*) malloc((size_t) input_dim);
+    float* di = (float*) malloc(sizeof(float) * (size_t) nb);
+    for (int32_t b = 0; b < nb; ++b) di[b] = oracle_q8_quantize_block(in + (size_t) b * 256, q8 + (size_t) b * 256);
+    for (int32_t o = 0; o < output_dim; ++o) {
+        float acc = 0.0f;
+        for (int32_t b = 0; b < nb; ++b) {
+            const uint8_t* blk = w + ((size_t) o * nb + b) * 210;
+            const int8_t* sc = (const int8_t*)(blk + 192);
+            const float d = half_to_float((uint16_t)(blk[208] | (blk[209] << 8)));
+            int8_t codes[256];
+            for (int half = 0; half < 2; ++half) {
+                const uint8_t* ql = blk + half * 64; const uint8_t* qh = blk + 128 + half * 32;
+                int8_t* c = codes + half * 128;
+                for (int l = 0; l < 32; ++l) {
+                    c[l]      = (int8_t)((int)((ql[l] & 0x0F) | (((qh[l] >> 0) & 3) << 4)) - 32);
+                    c[l + 32] = (int8_t)((int)((ql[l + 32] & 0x0F) | (((qh[l] >> 2) & 3) << 4)) - 32);
+                    c[l + 64] = (int8_t)((int)((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32);
+                    c[l + 96] = (int8_t)((int)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32);
+                }
+            }
+            int64_t wdot = 0;
+            const int8_t* a = q8 + (size_t) b * 256;
+            for (int half = 0; half < 2; ++half)
+                for (int k = 0; k < 4; ++k)
+                    for (int is = 0; is < 2; ++is) {
+                        const int start = half * 128 + 32 * k + is * 16, gs = half * 8 + is + 2 * k;
+                        int32_t dot = 0;
+                        for (int j = 0; j < 16; ++j) dot += (int) a[start + j] * (int) codes[start + j];
+                        wdot += (int64_t) sc[gs] * dot;
+                    }
+            acc += d * di[b] * (float) wdot;
+        }
+        out[o] = acc;
+    }
+    free(q8); free(di);
+}
+
+/* Q5_K matvec, row-major, fp32 activations. native/src/q5k_matmul.c:93-215 (portable body): per 64-element group
+ * the low- and high-nibble sub-blocks accumulate code_sum = sum v*code and input_sum = sum v, then
+ * acc += code_sum * (d*sc) - input_sum * (dmin*mn), low then high; :242-254 (row loop). */
+API void oracle_q5k_matmul(const float* in, const uint8_t* w, int32_t input_dim, int32_t output_dim, float* out) {
+    if (output_dim <= 0) return;
+    if (input_dim <= 0) { for (int32_t o = 0; o < output_dim; ++o) out[o] = 0.0f; return; }
+    const int32_t nb = input_dim / 256;
+    for (int32_t o = 0; o < output_dim; ++o) {
+        float acc_row = 0.0f;
+        for (int32_t b = 0; b < nb; ++b) {
+            const uint8_t* blk = w + ((size_t) o * nb + b) * 176;
+            const float d = half_to_float((uint16_t)(blk[0] | (blk[1] << 8)));
+            const float dmin = half_to_float((uint16_t)(blk[2] | (blk[3] << 8)));
+            int sc[8], mn[8]; k4_scales(blk + 4, sc, mn);
+            const uint8_t* qh = blk + 16; const uint8_t* qs = blk + 48;
+            const float* x = in + (size_t) b * 256;
+            float acc = 0.0f;
+            for (int g = 0; g < 4; ++g) {
+                float cs_lo = 0.0f, is_lo = 0.0f, cs_hi = 0.0f, is_hi = 0.0f;
+                for (int i = 0; i < 32; ++i) {
+                    const uint8_t by = qs[32 * g + i], h = qh[i];
+                    const float c_lo = (float)((by & 0x0F) | (((h >> (2 * g)) & 1) << 4));
+                    const float c_hi = (float)((by >> 4) | (((h >> (2 * g + 1)) & 1) << 4));
+                    const float v_lo = x[64 * g + i], v_hi = x[64 * g + 32 + i];
+                    cs_lo += v_lo * c_lo; is_lo += v_lo; cs_hi += v_hi * c_hi; is_hi += v_hi;
+                }
+                acc += cs_lo * (d * (float) sc[2 * g]) - is_lo * (dmin * (float) mn[2 * g]);
+                acc += cs_hi * (d * (float) sc[2 * g + 1]) - is_hi * (dmin * (float) mn[2 * g + 1]);
+            }
+            acc_row += acc;
+        }
+        out[o] = acc_row;
+    }
+}
+
 /* native/src/q8_0_matmul.c:68-118 (block term: fp32 activations, per-block sum then * d),
  * :134-165 (row loops), :168-187 (run; input_dim<=0 zeroes the output). */
 API void oracle_q8_0_matmul(const float* in, const uint8_t* w, int32_t input_dim, int32_t output_dim,

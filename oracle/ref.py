@@ -295,15 +295,39 @@ def matmul(enc: str, x: np.ndarray, w: np.ndarray, input_dim: int, output_dim: i
     lib = ref() if use_ref else None
     if use_ref and lib is None:
         raise RuntimeError("oracle/_ref is not built")
+    if enc in ("Q5_K", "Q6_K") and order != "rm":
+        raise ValueError("the Q5_K / Q6_K restatements take the row-major order only")
     for r in range(x2.shape[0]):
         if lib is not None:
-            name = {"Q8_0": "skainet_q8_0_matmul", "Q4_K": "skainet_q4k_matmul"}[enc] + ("_rm" if order == "rm" else "")
+            name = {"Q8_0": "skainet_q8_0_matmul", "Q4_K": "skainet_q4k_matmul", "Q5_K": "skainet_q5k_matmul",
+                    "Q6_K": "skainet_q6k_matmul"}[enc] + ("_rm" if order == "rm" else "")
             getattr(lib, name)(_fp(x2[r]), 0, _bp(w), 0, input_dim, output_dim, _fp(out[r]), 0)
+        elif enc in ("Q5_K", "Q6_K"):
+            fn = {"Q5_K": "oracle_q5k_matmul", "Q6_K": "oracle_q6k_matmul"}[enc]
+            getattr(port(), fn)(_fp(x2[r]), _bp(w), C.c_int32(input_dim), C.c_int32(output_dim), _fp(out[r]))
         else:
             fn = {"Q8_0": "oracle_q8_0_matmul", "Q4_K": "oracle_q4k_matmul"}[enc]
             getattr(port(), fn)(_fp(x2[r]), _bp(w), C.c_int32(input_dim), C.c_int32(output_dim), _fp(out[r]),
                                 C.c_int32(0 if order == "rm" else 1))
     return out.reshape(x.shape[:-1] + (output_dim,)) if x.ndim > 1 else out[0]
+
+
+def random_kquant_blocks(enc: str, rows: int, cols: int, seed: int = 0) -> np.ndarray:
+    """Valid random Q5_K / Q6_K super-blocks [rows * cols/256] in canonical GGUF order: random code bits, small scales,
+    f16 d (and dmin) of a magnitude that keeps outputs O(1). Not a quantizer: the matvec tests only need well-formed bytes."""
+    rng = np.random.default_rng(seed)
+    nb = rows * (cols // 256)
+    if enc == "Q6_K":
+        blk = rng.integers(0, 256, (nb, 210), dtype=np.uint8)
+        blk[:, 192:208] = rng.integers(-48, 48, (nb, 16)).astype(np.int8).view(np.uint8)
+        blk[:, 208:210] = np.abs(0.0008 * rng.standard_normal(nb)).astype(np.float16).view(np.uint8).reshape(nb, 2)
+        return blk.reshape(-1)
+    if enc == "Q5_K":
+        blk = rng.integers(0, 256, (nb, 176), dtype=np.uint8)
+        blk[:, 0:2] = np.abs(0.0006 * rng.standard_normal(nb)).astype(np.float16).view(np.uint8).reshape(nb, 2)
+        blk[:, 2:4] = np.abs(0.004 * rng.standard_normal(nb)).astype(np.float16).view(np.uint8).reshape(nb, 2)
+        return blk.reshape(-1)
+    raise ValueError(enc)
 
 
 def q8_quantize(x: np.ndarray):

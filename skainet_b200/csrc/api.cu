@@ -392,7 +392,7 @@ int32_t skainet_cuda_matmul_dev(skainet_weight_t h, const float* x_dev, int32_t 
     const size_t need = act_scratch_bytes(w->enc, act_mode, m, w->cols);
     if (need) SK_TRY(scratch_get(s, SCRATCH_ACT, need, &scratch));
     SK_TRY(launch_act_quant(w->enc, act_mode, x_dev, m, w->cols, scratch, s));
-    if (m == 1 && act_mode == SKAINET_ACT_NATIVE && matvec_env_mode() == 0) {
+    if (m == 1 && act_mode == SKAINET_ACT_NATIVE && matvec_env_mode() == 0 && (w->enc == SKAINET_ENC_Q4_K || w->enc == SKAINET_ENC_Q8_0)) {
         MatvecIn in;
         if (w->enc == SKAINET_ENC_Q8_0) in.split = act_split_layout(scratch, 1, w->cols); else in.q8 = act_q8k_layout(scratch, 1, w->cols);
         const int32_t st = launch_matvec_fused(*w, in, PREP_QUANTIZED, y_dev, nullptr, s);

@@ -289,8 +289,12 @@ static void launch_q8_m(const Weight& w, ActSplit act, float* y, cudaStream_t s)
 int32_t launch_matvec(const Weight& w, const float* x, const void* act_scratch, int m, float* y, int act_mode,
                       cudaStream_t s) {
     if (m == 0 || w.rows == 0) return SKAINET_CUDA_OK;
+    if (w.enc == SKAINET_ENC_Q6_K || w.enc == SKAINET_ENC_Q5_K) {
+        if (x == nullptr) { set_error("matmul: Q5_K / Q6_K take the fp32 activation pointer"); return SKAINET_CUDA_ERR_INVALID; }
+        return launch_matvec_kq(w, x, act_q8k_layout(const_cast<void*>(act_scratch), m, w.cols), m, y, act_mode, s);
+    }
     if (w.enc != SKAINET_ENC_Q4_K && w.enc != SKAINET_ENC_Q8_0) {
-        set_error("matmul: encoding %d has no matvec kernel yet", w.enc);
+        set_error("matmul: encoding %d has no matvec kernel", w.enc);
         return SKAINET_CUDA_ERR_INVALID;
     }
     const int grid = (w.rows + MV_WARPS - 1) / MV_WARPS;

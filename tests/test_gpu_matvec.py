@@ -188,3 +188,19 @@ def test_tcgen05_rows_tile_kernel_is_exact_and_repeatable(gpu, oracle):
     from skainet_b200 import _lib
     assert _lib.lib().skainet_cuda_device_status() == 0
     w.free()
+
+
+@pytest.mark.parametrize("enc", ["Q6_K", "Q5_K"])
+@pytest.mark.parametrize("n,k,m", [(64, 256, 1), (129, 4096, 1), (33, 2048, 5)])
+def test_k_quant_next_formats_matvec(gpu, oracle, enc, n, k, m):
+    """Q6_K / Q5_K over resident planes against the reference's C kernels (native mode: Q6_K quantizes the
+    activation to int8 per 256 and is integer-exact per block; Q5_K keeps fp32) and, in F32 mode, against the
+    dequantised product in float64."""
+    w_bytes = oracle.random_kquant_blocks(enc, n, k, seed=n + k + m)
+    x = np.random.default_rng(n * 7 + m).standard_normal((m, k)).astype(np.float32)
+    w = gpu.Weight.upload(w_bytes, enc, n, k)
+    ref = oracle.matmul(enc, x, w_bytes, k, n, "rm", use_ref=oracle.ref() is not None)
+    rel_err_ok(gpu.matmul_host(w, x), ref, 1e-5 if enc == "Q6_K" else 1e-4)
+    exact = x.astype(np.float64) @ oracle.dequant(enc, w_bytes).reshape(n, k).astype(np.float64).T
+    rel_err_ok(gpu.matmul_host(w, x, act_mode=1), exact, 1e-4)
+    w.free()

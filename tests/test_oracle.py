@@ -171,3 +171,22 @@ def test_reference_builds_drift_apart_at_the_quantization_cliffs(oracle):
         worst = max(worst, float(np.abs(la - lb).max() / np.sqrt(np.mean(la ** 2))))
     assert worst < 0.2
     assert worst > 1e-3, "no drift seen: the cliff argument would need a longer run"
+
+
+@pytest.mark.parametrize("enc", ["Q6_K", "Q5_K"])
+def test_k_quant_matvec_restatements_match_the_reference_c(oracle, enc):
+    """Q6_K (int8 activations per 256, integer group dots) and Q5_K (fp32 activations) row-major matvec: the
+    restatement against the compiled reference kernels, and both against the dequantised dot product."""
+    if oracle.ref() is None:
+        pytest.skip("oracle/_ref not built here")
+    n, k = 37, 1024
+    w = oracle.random_kquant_blocks(enc, n, k, seed=5)
+    x = np.random.default_rng(6).standard_normal((3, k)).astype(np.float32)
+    a = oracle.matmul(enc, x, w, k, n, "rm", use_ref=False)
+    b = oracle.matmul(enc, x, w, k, n, "rm", use_ref=True)
+    scale = float(np.abs(b).max())
+    assert np.abs(a - b).max() <= 2e-6 * scale
+    exact = x.astype(np.float64) @ oracle.dequant(enc, w).reshape(n, k).astype(np.float64).T
+    # Q6_K pays the int8 activation rounding (about 1 % rms of the output scale), Q5_K only fp32 order
+    tol = 0.03 if enc == "Q6_K" else 1e-5
+    assert np.abs(a - exact).max() <= tol * scale
