@@ -59,23 +59,42 @@ q4k_gemm_mma_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ 
     const int cols = bpr * 256;
     skd::pdl_launch_dependents();
 
+    // Each thread copies the same chunks of every stage: its sources advance by one super-block per stage, so the
+    // row / chunk arithmetic (divisions by 9 and 17) is done once, not per copy.
+    constexpr int WSLOTS = (RT * 9 + NW * 32 - 1) / (NW * 32), XSLOTS = (MT * 17 + NW * 32 - 1) / (NW * 32);
+    const uint8_t* wsrc[WSLOTS]; int wdst[WSLOTS], wstep[WSLOTS];
+    const uint8_t* xsrc[XSLOTS]; int xdst[XSLOTS], xstep[XSLOTS];
+#pragma unroll
+    for (int i = 0; i < WSLOTS; ++i) {
+        const int c = threadIdx.x + i * NW * 32;
+        const int r = c / 9, ch = c % 9;
+        const size_t blk0 = (size_t) min(row0 + r, rows - 1) * bpr;
+        wdst[i] = c < RT * 9 ? r * GW_STRIDE + ch * 16 : -1;
+        wsrc[i] = ch < 8 ? qs + blk0 * 128 + ch * 16 : hdr + blk0 * 16;
+        wstep[i] = ch < 8 ? 128 : 16;
+    }
+#pragma unroll
+    for (int i = 0; i < XSLOTS; ++i) {
+        const int c = threadIdx.x + i * NW * 32;
+        const int r = c / 17, ch = c % 17;
+        const size_t arow = (size_t) min(col0 + r, m - 1);
+        xdst[i] = c < MT * 17 ? r * GX_STRIDE + ch * 16 : -1;
+        xsrc[i] = ch < 16 ? (const uint8_t*) (act.q + arow * cols + ch * 16) : (const uint8_t*) (act.bsums + arow * bpr * 8);
+        xstep[i] = ch < 16 ? 256 : 16;
+    }
+    const float* dsrc = act.d + (size_t) min(col0 + (int) threadIdx.x, m - 1) * bpr;
     auto issue_w = [&](int kb) {
         uint8_t* st = smem + (size_t) (kb % NS) * S_BYTES;
-        for (int c = threadIdx.x; c < RT * 9; c += NW * 32) {
-            const int r = c / 9, ch = c % 9;
-            const size_t blk = (size_t) min(row0 + r, rows - 1) * bpr + kb;
-            cp_async16(st + r * GW_STRIDE + ch * 16, ch < 8 ? qs + blk * 128 + ch * 16 : hdr + blk * 16);
-        }
+#pragma unroll
+        for (int i = 0; i < WSLOTS; ++i)
+            if (wdst[i] >= 0) cp_async16(st + wdst[i], wsrc[i] + (size_t) kb * wstep[i]);
     };
     auto issue_x = [&](int kb) {
         uint8_t* st = smem + (size_t) (kb % NS) * S_BYTES + W_BYTES;
-        for (int c = threadIdx.x; c < MT * 17; c += NW * 32) {
-            const int r = c / 17, ch = c % 17;
-            const size_t arow = (size_t) min(col0 + r, m - 1);
-            cp_async16(st + r * GX_STRIDE + ch * 16,
-                       ch < 16 ? (const void*) (act.q + arow * cols + (size_t) kb * 256 + ch * 16) : (const void*) (act.bsums + (arow * bpr + kb) * 8));
-        }
-        if (threadIdx.x < MT) cp_async4(st + X_BYTES + threadIdx.x * 4, act.d + (size_t) min(col0 + (int) threadIdx.x, m - 1) * bpr + kb);
+#pragma unroll
+        for (int i = 0; i < XSLOTS; ++i)
+            if (xdst[i] >= 0) cp_async16(st + xdst[i], xsrc[i] + (size_t) kb * xstep[i]);
+        if (threadIdx.x < MT) cp_async4(st + X_BYTES + threadIdx.x * 4, dsrc + kb);
     };
 
     // The weights depend on no predecessor: their first stages are in flight before the wait.
@@ -209,6 +228,7 @@ int32_t launch_gemm_mma(const Weight& w, ActQ8K a, int m, float* y, const float*
     // Up to four activation rows stay with the streaming matvec kernels (faster there). Few rows: weight
     // streaming decides, so small row tiles (many CTAs) and a deep pipeline; many rows: 128 x 32 output tiles.
     if (m <= 4) return 1;
+    // (row tiles of 32 or 16 for weights with few rows were measured slower: more activation re-fetch per weight byte)
     if (m <= 8) return launch_cfg<4, 1, 8>(w, a, m, y, resid, s);
     if (m <= 16) return launch_cfg<4, 2, 6>(w, a, m, y, resid, s);
     return launch_cfg<8, 4, 4>(w, a, m, y, resid, s);
