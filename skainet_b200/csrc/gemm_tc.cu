@@ -63,6 +63,18 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a, uint64_t b
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(skd::smem_u32(bar)) : "memory");
 }
+// 8-byte weight load as volatile asm: the compiler keeps it where it is written (ahead of the barrier waits of the
+// current super-block), so the next super-block's bytes really are in flight one iteration early.
+__device__ __forceinline__ uint2 ld_nc_v2(const void* p) {
+    uint2 r;
+    asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));    // L1-allocating: the four threads of a row share sectors
+    return r;
+}
+__device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -282,8 +294,8 @@ q4k_gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ h
         {
             const size_t blk = (size_t) grow * bpr;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) qn[i] = __ldg(reinterpret_cast<const uint2*>(qs + blk * 128 + i * 32 + part * 8));
-            hdn = skd::ld_ro(hdr + blk * 16);
+            for (int i = 0; i < 4; ++i) qn[i] = ld_nc_v2(qs + blk * 128 + i * 32 + part * 8);
+            hdn = ld_nc_v4(hdr + blk * 16);
         }
         int s = 0, round = 0;
         for (int kb = 0; kb < bpr && ok; ++kb) {
@@ -294,8 +306,8 @@ q4k_gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ h
             if (kb + 1 < bpr) {
                 const size_t blk = (size_t) grow * bpr + kb + 1;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) qn[i] = __ldg(reinterpret_cast<const uint2*>(qs + blk * 128 + i * 32 + part * 8));
-                hdn = skd::ld_ro(hdr + blk * 16);
+                for (int i = 0; i < 4; ++i) qn[i] = ld_nc_v2(qs + blk * 128 + i * 32 + part * 8);
+                hdn = ld_nc_v4(hdr + blk * 16);
             }
             const float dw = __half2float(__ushort_as_half((unsigned short) (hd.x & 0xffff)));
             const float dminw = __half2float(__ushort_as_half((unsigned short) (hd.x >> 16)));
