@@ -84,6 +84,12 @@ SKAINET_CUDA_API int32_t skainet_cuda_device_info(int64_t* out4);
  * counterpart: its kernels cannot time out. */
 SKAINET_CUDA_API int32_t skainet_cuda_device_status(void);
 
+/* Exercises that failure path without any fault: launches a kernel whose only wait is on a barrier nothing completes.
+ * outcome = 2 when the kernel gave up after its poll limit and still ran to its end (the expected result; the next
+ * skainet_cuda_device_status() then returns SKAINET_CUDA_ERR_TIMEOUT once), 1 if the wait unexpectedly succeeded,
+ * 0 if the kernel did not finish. Takes a second or so. The reference has no counterpart. */
+SKAINET_CUDA_API int32_t skainet_cuda_selftest_bounded_wait(int32_t* outcome);
+
 /* ---- 1. drop-in twins (HOST pointers) -------------------------------------------------------- */
 
 /* Availability probe, out[i] = 2*in[i] computed on the GPU.

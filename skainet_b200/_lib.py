@@ -38,6 +38,7 @@ SIGNATURES = {
     "skainet_cuda_set_device": [i32],
     "skainet_cuda_device_info": [i64p],
     "skainet_cuda_device_status": [],
+    "skainet_cuda_selftest_bounded_wait": [i32p],
     "skainet_cuda_smoke_double": [f32p, f32p, i32],
     "skainet_cuda_q4k_matmul": _MATVEC,
     "skainet_cuda_q4k_matmul_rm": _MATVEC,

@@ -223,6 +223,21 @@ int32_t skainet_cuda_device_status(void) {
     return SKAINET_CUDA_OK;
 }
 
+int32_t skainet_cuda_selftest_bounded_wait(int32_t* outcome) {
+    SK_REQUIRE(outcome != nullptr, "selftest_bounded_wait: null output");
+    SK_TRY(ensure_device());
+    SK_REQUIRE(device_timeout_flag() != nullptr, "selftest_bounded_wait: the device flag is unavailable");
+    int* d = nullptr;
+    SK_CUDA(cudaMalloc((void**) &d, sizeof(int)));
+    cudaMemset(d, 0, sizeof(int));
+    int32_t st = launch_bounded_wait_selftest(d, (cudaStream_t) 0);
+    int v = 0;
+    if (st == SKAINET_CUDA_OK && cudaMemcpy(&v, d, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) st = cuda_fail(cudaGetLastError(), "cudaMemcpy", __FILE__, __LINE__);
+    cudaFree(d);
+    *outcome = v;
+    return st;
+}
+
 // ---- resident API ---------------------------------------------------------------------------------------------
 int32_t skainet_cuda_malloc(void** dev_ptr, int64_t nbytes) {
     SK_REQUIRE(dev_ptr != nullptr && nbytes >= 0, "malloc: bad arguments");

@@ -79,6 +79,7 @@ enum { SCRATCH_ACT = 0, SCRATCH_ATTN = 1, SCRATCH_TWIN_A = 2, SCRATCH_TWIN_B = 3
        SCRATCH_TWIN_D = 5, SCRATCH_TWIN_E = 6, SCRATCH_TWIN_F = 7, SCRATCH_FUSED = 8, SCRATCH_FUSED2 = 9, SCRATCH_SLOTS = 10 };
 
 int sm_count();
+int32_t launch_bounded_wait_selftest(int* reached_end, cudaStream_t s);   // probe.cu
 int* device_timeout_flag();   // device int set by a kernel whose bounded wait ran out (nullptr if unavailable)
 
 // ---- launchers implemented in the kernel files ------------------------------------------------------

@@ -30,4 +30,23 @@ int32_t launch_probe_read(const Weight& w, uint32_t* sink, cudaStream_t s) {
     return SKAINET_CUDA_OK;
 }
 
+// Self-test of the failure path every kernel here shares: one thread waits on a shared-memory barrier that
+// nothing ever completes. The wait is bounded, so the kernel gives up after its poll limit, raises the device
+// flag and returns normally: no trap, no fault, the context stays usable.
+__global__ void bounded_wait_selftest_kernel(int* __restrict__ timeout_flag, int* __restrict__ reached_end) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) { skd::mbar_init(&bar, 1); skd::mbar_fence_init(); }
+    __syncthreads();
+    bool ok = true;
+    if (threadIdx.x == 0) ok = skd::mbar_wait_bounded(&bar, 0, timeout_flag);
+    __syncthreads();
+    if (threadIdx.x == 0) *reached_end = ok ? 1 : 2;
+}
+
+int32_t launch_bounded_wait_selftest(int* reached_end, cudaStream_t s) {
+    bounded_wait_selftest_kernel<<<1, 32, 0, s>>>(device_timeout_flag(), reached_end);
+    SK_CUDA(cudaGetLastError());
+    return SKAINET_CUDA_OK;
+}
+
 }  // namespace sk

@@ -139,3 +139,18 @@ def test_decode_attention_f16_cache_matches_oracle(gpu, oracle, B, H, Hkv, D, L)
     n = int(lens[0]); lo = max(0, n - 5)
     ref = oracle.sdpa(q[0:1], k[0:1, :, lo:n].astype(np.float32), v[0:1, :, lo:n].astype(np.float32), scale, causal=True)
     rel_err_ok(got[0], ref[0, :, 0, :])
+
+
+def test_bounded_wait_gives_up_reports_and_leaves_the_context_usable(gpu, cuda_lib):
+    """Failure detection without a fault: a kernel waits on a barrier nothing completes; the wait is bounded, the
+    kernel reaches its end, the device flag is raised exactly once, and the next kernel computes correctly."""
+    import ctypes as C
+    outcome = C.c_int32(0)
+    assert cuda_lib.skainet_cuda_selftest_bounded_wait(C.byref(outcome)) == 0
+    assert outcome.value == 2
+    assert cuda_lib.skainet_cuda_device_status() == -6          # SKAINET_CUDA_ERR_TIMEOUT, and the condition is cleared
+    assert cuda_lib.skainet_cuda_device_status() == 0
+    x = np.array([1.0, -2.5, 3.25], np.float32); y = np.zeros(3, np.float32)
+    from skainet_b200 import _lib
+    assert cuda_lib.skainet_cuda_smoke_double(x.ctypes.data_as(_lib.f32p), y.ctypes.data_as(_lib.f32p), 3) == 0
+    np.testing.assert_array_equal(y, 2 * x)
