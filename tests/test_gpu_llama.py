@@ -195,3 +195,31 @@ def test_runtime_argument_errors(gpu):
     with pytest.raises(ValueError, match="max_seq"):
         m.prefill(list(range(17)))
     m.free()
+
+
+def test_prefill_and_decode_are_bit_repeatable(gpu):
+    """Three runs of the same request (a 300-token prompt through the tcgen05 / mma.sync tile kernels and the
+    tensor-core prefill attention, then 48 greedy tokens through the ring matvecs and split-K attention) give identical
+    logits bit for bit and identical tokens: every reduction in the path has a fixed order, and a race between the
+    warp roles of a kernel would show up as a run that differs."""
+    from skainet_b200.llama import Llama, LlamaConfig
+    from skainet_b200 import _lib
+    cfg = LlamaConfig(3, 2048, 16, 4, 128, 5632, 4000, max_seq=512)
+    m = Llama(cfg)
+    m.synth(seed=21, std=0.03)
+    m.finalize()
+    prompt = list(np.random.default_rng(8).integers(0, cfg.vocab, size=300))
+    runs = []
+    for _ in range(3):
+        m.reset()
+        f = m.prefill(prompt)
+        lg = m.logits(1).copy()
+        toks = [f] + list(m.generate([f], 48)[:, 0])
+        runs.append((lg, toks, m.logits(1).copy()))
+    for lg, toks, lg2 in runs[1:]:
+        np.testing.assert_array_equal(lg, runs[0][0])
+        assert toks == runs[0][1]
+        np.testing.assert_array_equal(lg2, runs[0][2])
+    assert np.isfinite(runs[0][0]).all()
+    assert _lib.lib().skainet_cuda_device_status() == 0
+    m.free()
