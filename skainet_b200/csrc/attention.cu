@@ -258,7 +258,7 @@ template <int D>
 __global__ void __launch_bounds__(AM_WARPS * 32)
 attn_decode_mma_kernel(const float* __restrict__ q, int64_t q_row_stride, const __half* __restrict__ kc, const __half* __restrict__ vc,
                        float* __restrict__ part, int heads, int kv_heads, int G, int64_t cache_stride,
-                       const int32_t* __restrict__ kv_len, float scale, int window, int chunk, int splits) {
+                       const int32_t* __restrict__ kv_len, float scale, int window, int chunk, int splits, float* __restrict__ out_direct) {
     constexpr int S4 = D / 32;     // chunks of a K row per lane
     constexpr int KS = D / 16;     // k-steps of the score contraction
     constexpr int U = D / 64;      // chunks of a V row per lane
@@ -405,6 +405,13 @@ attn_decode_mma_kernel(const float* __restrict__ q, int64_t q_row_stride, const 
         float at = 0.0f;
 #pragma unroll
         for (int w = 0; w < AM_WARPS; ++w) at += sm_c[w][hg] * sm_acc[w][hg][dd];
+        if (out_direct) {            // a single key split: this is the final result, no records and no merge launch
+            float lt = 0.0f;
+#pragma unroll
+            for (int w = 0; w < AM_WARPS; ++w) lt += sm_c[w][hg] * sm_l[w][hg];
+            out_direct[((int64_t) b * heads + kvh * G + hg) * D + dd] = lt > 0.0f ? at / lt : 0.0f;
+            continue;
+        }
         float* rec = part + (((int64_t) b * heads + kvh * G + hg) * splits + split) * (D + 2);
         rec[2 + dd] = at;
         if (dd == 0) {
@@ -489,9 +496,10 @@ static void launch_decode_dg(const float* q, const __half* k, const __half* v, f
         if (splits > 1 && !always_partials) launch_pdl(attn_merge_kernel<D>, dim3(batch * heads), dim3(D * MG), 0, s, (const float*) part, out, splits);
         return;
     }
+    const bool direct = splits == 1 && !always_partials;
     launch_pdl(attn_decode_mma_kernel<D>, grid, dim3(AM_WARPS * 32), 0, s, q, q_row_stride, k, v, part, heads, kv_heads, G, cache_stride, kv_len,
-               scale, window, chunk, splits);
-    if (!always_partials) launch_pdl(attn_merge_kernel<D>, dim3(batch * heads), dim3(D * MG), 0, s, (const float*) part, out, splits);
+               scale, window, chunk, splits, direct ? out : (float*) nullptr);
+    if (!always_partials && !direct) launch_pdl(attn_merge_kernel<D>, dim3(batch * heads), dim3(D * MG), 0, s, (const float*) part, out, splits);
 }
 
 static int32_t attn_decode_impl(const float* q, int64_t q_row_stride, const __half* k, const __half* v, float* out, int batch, int heads,
