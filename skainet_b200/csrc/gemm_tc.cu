@@ -12,16 +12,17 @@
 //
 // CTA = 128 weight rows (TMEM lanes) x 128 activation rows (TMEM columns), 18 warps:
 //   warps 0-15 four threads per weight row: per 64-element group each writes a quarter of that row's 64 f16 of
-//              the A stage (weights fetched one super-block ahead); after producing super-block kb they fold super-block kb-1 out of TMEM (tcgen05.ld) into
-//              32 fp32 accumulators per thread (each of the four takes a quarter of the columns);
+//              the A stage (weights fetched one super-block ahead); after producing super-block kb they fold
+//              super-block kb-1 out of TMEM (tcgen05.ld) into 32 fp32 accumulators per thread (each of the four
+//              takes a quarter of the columns);
 //   warp 17    one lane posts the bulk copies of the B stages and of the S2 / scale pieces as soon as their slots
 //              free up, independently of the other warps;
 //   warp 16    one lane issues the MMAs and commits: stage barriers back to the producers, accumulator
 //              barriers to the epilogue; two TMEM accumulator sets so MMAs of kb+1 overlap the fold of kb.
 // The stage operands use the K-major 128-byte-swizzle canonical layout (a 64-element group is exactly one
 // 128-byte row; 16-byte chunks XOR the row index), the small S2 operands the no-swizzle one (8 rows x 16 B
-// core matrices). The activation side is prepared once
-// per call by act_f16_tiles_kernel in exactly that order, so a B stage is one contiguous 16 KB bulk copy.
+// core matrices). A stage holds two such groups (128 k). The activation side is prepared once per call by
+// act_f16_tiles_kernel in exactly that order, so a B stage is one contiguous 32 KB bulk copy.
 // Every mbarrier wait is bounded; a wait that runs out raises the device flag, and the CTA still reaches
 // the common exit where TMEM is freed.
 #include "common.cuh"
