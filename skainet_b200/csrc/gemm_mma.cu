@@ -215,6 +215,143 @@ int32_t launch_cfg(const Weight& w, ActQ8K a, int m, float* y, const float* resi
     return SKAINET_CUDA_OK;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Q8_0 weights x two-term int8 activations (hi*128 + lo per 32 values, ActSplit): mma.sync m16n8k32 s8 x s8.
+// One Q8_0 block (32 codes) is one MMA against `hi` and one against `lo`; the block contributes
+// d_w * d_x * float(128*dot_hi + dot_lo), the same 15-bit arithmetic as the matvec (reference:
+// native/src/q8_0_matmul.c:68-118 keeps fp32 activations; deviation of the split is ~4e-5 relative).
+// Stage = 256 columns (8 blocks): weights [16*NW rows][272 B] = 256 codes + 8 f16 scales; activations
+// hi [MT][272 B] and lo [MT][272 B], each 256 codes + four of the row's eight fp32 block scales in the pad.
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_s8s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int NW, int NT, int NS, int EPI>
+__global__ void __launch_bounds__(NW * 32)
+q8_0_gemm_mma_kernel(const int8_t* __restrict__ codes, const __half* __restrict__ scales, int rows, int cols, ActSplit act, int m,
+                     float* __restrict__ y, const float* __restrict__ resid) {
+    constexpr int RT = NW * 16, MT = NT * 8, ST = 272;
+    constexpr int W_BYTES = RT * ST, X_BYTES = MT * ST, S_BYTES = W_BYTES + 2 * X_BYTES;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int row0 = blockIdx.x * RT, col0 = blockIdx.y * MT;
+    const int nst = cols >> 8, b32 = cols >> 5;
+    skd::pdl_launch_dependents();
+
+    // fixed copy slots per thread (see the Q4_K kernel): weights 17 chunks per row, activations 34 per row
+    constexpr int WSLOTS = (RT * 17 + NW * 32 - 1) / (NW * 32), XSLOTS = (MT * 34 + NW * 32 - 1) / (NW * 32);
+    const uint8_t* wsrc[WSLOTS]; int wdst[WSLOTS], wstep[WSLOTS];
+    const uint8_t* xsrc[XSLOTS]; int xdst[XSLOTS], xstep[XSLOTS];
+#pragma unroll
+    for (int i = 0; i < WSLOTS; ++i) {
+        const int c = threadIdx.x + i * NW * 32;
+        const int r = c / 17, ch = c % 17;
+        const size_t grow = (size_t) min(row0 + r, rows - 1);
+        wdst[i] = c < RT * 17 ? r * ST + ch * 16 : -1;
+        wsrc[i] = ch < 16 ? (const uint8_t*) (codes + grow * cols + ch * 16) : (const uint8_t*) (scales + grow * b32);
+        wstep[i] = ch < 16 ? 256 : 16;
+    }
+#pragma unroll
+    for (int i = 0; i < XSLOTS; ++i) {
+        const int c = threadIdx.x + i * NW * 32;
+        const int r = c / 34, ch = c % 34;
+        const size_t arow = (size_t) min(col0 + r, m - 1);
+        // ch 0..15 hi codes, 16 = scales 0..3 (hi pad), 17..32 lo codes, 33 = scales 4..7 (lo pad)
+        const bool lo_half = ch >= 17;
+        const int cc = lo_half ? ch - 17 : ch;
+        xdst[i] = c < MT * 34 ? (lo_half ? X_BYTES : 0) + r * ST + cc * 16 : -1;
+        if (cc < 16) { xsrc[i] = (const uint8_t*) ((lo_half ? act.lo : act.hi) + arow * cols + cc * 16); xstep[i] = 256; }
+        else { xsrc[i] = (const uint8_t*) (act.d + arow * b32 + (lo_half ? 4 : 0)); xstep[i] = 32; }
+    }
+    auto issue_w = [&](int kb) {
+        uint8_t* st = smem + (size_t) (kb % NS) * S_BYTES;
+#pragma unroll
+        for (int i = 0; i < WSLOTS; ++i)
+            if (wdst[i] >= 0) cp_async16(st + wdst[i], wsrc[i] + (size_t) kb * wstep[i]);
+    };
+    auto issue_x = [&](int kb) {
+        uint8_t* st = smem + (size_t) (kb % NS) * S_BYTES + W_BYTES;
+#pragma unroll
+        for (int i = 0; i < XSLOTS; ++i)
+            if (xdst[i] >= 0) cp_async16(st + xdst[i], xsrc[i] + (size_t) kb * xstep[i]);
+    };
+    for (int s = 0; s < NS - 1 && s < nst; ++s) issue_w(s);
+    skd::pdl_wait();
+    for (int s = 0; s < NS - 1; ++s) {
+        if (s < nst) issue_x(s);
+        cp_async_commit();
+    }
+
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) { acc[nt][0] = 0.f; acc[nt][1] = 0.f; acc[nt][2] = 0.f; acc[nt][3] = 0.f; }
+    const int lm_row = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), lm_byte = 16 * (lane >> 4);
+
+    for (int kb = 0; kb < nst; ++kb) {
+        cp_async_wait<NS - 2>();
+        __syncthreads();
+        if (kb + NS - 1 < nst) { issue_w(kb + NS - 1); issue_x(kb + NS - 1); }
+        cp_async_commit();
+        const uint8_t* ws = smem + (size_t) (kb % NS) * S_BYTES;
+        const uint8_t* xh = ws + W_BYTES;
+        const uint8_t* xl = xh + X_BYTES;
+#pragma unroll
+        for (int blk = 0; blk < 8; ++blk) {
+            uint32_t a[4];
+            ldmatrix_x4(a, ws + lm_row * ST + 32 * blk + lm_byte);
+            const float dw0 = __half2float(*reinterpret_cast<const __half*>(ws + (warp * 16 + g) * ST + 256 + 2 * blk));
+            const float dw1 = __half2float(*reinterpret_cast<const __half*>(ws + (warp * 16 + g + 8) * ST + 256 + 2 * blk));
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint8_t* rh = xh + (nt * 8 + g) * ST + 32 * blk + 4 * t;
+                const uint8_t* rl = xl + (nt * 8 + g) * ST + 32 * blk + 4 * t;
+                int ch[4] = {0, 0, 0, 0}, cl[4] = {0, 0, 0, 0};
+                mma_s8s8(ch, a, *(const uint32_t*) rh, *(const uint32_t*) (rh + 16));
+                mma_s8s8(cl, a, *(const uint32_t*) rl, *(const uint32_t*) (rl + 16));
+                // block scale of activation rows 2t, 2t+1: four in the hi pad, four in the lo pad
+                const uint8_t* pad = (blk < 4 ? xh : xl) + 256 + 4 * (blk & 3);
+                const float dx0 = *reinterpret_cast<const float*>(pad + (nt * 8 + 2 * t) * ST);
+                const float dx1 = *reinterpret_cast<const float*>(pad + (nt * 8 + 2 * t + 1) * ST);
+                acc[nt][0] += (dw0 * dx0) * (float) (ch[0] * 128 + cl[0]);
+                acc[nt][1] += (dw0 * dx1) * (float) (ch[1] * 128 + cl[1]);
+                acc[nt][2] += (dw1 * dx0) * (float) (ch[2] * 128 + cl[2]);
+                acc[nt][3] += (dw1 * dx1) * (float) (ch[3] * 128 + cl[3]);
+            }
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int row = row0 + warp * 16 + g + 8 * (j >> 1), col = col0 + nt * 8 + 2 * t + (j & 1);
+            if (row < rows && col < m) {
+                const size_t o = (size_t) col * rows + row;
+                y[o] = EPI == EPI_ADD ? resid[o] + acc[nt][j] : acc[nt][j];
+            }
+        }
+}
+
+template <int NW, int NT, int NS>
+int32_t launch_cfg_q8(const Weight& w, ActSplit a, int m, float* y, const float* resid, cudaStream_t s) {
+    constexpr int RT = NW * 16, MT = NT * 8;
+    constexpr size_t smem = (size_t) NS * (RT * 272 + 2 * MT * 272);
+    static bool done[2] = {false, false};
+    dim3 grid((w.rows + RT - 1) / RT, (m + MT - 1) / MT);
+    if (resid) {
+        if (!done[1]) { SK_CUDA(cudaFuncSetAttribute(q8_0_gemm_mma_kernel<NW, NT, NS, EPI_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem)); done[1] = true; }
+        SK_CUDA(launch_pdl(q8_0_gemm_mma_kernel<NW, NT, NS, EPI_ADD>, grid, dim3(NW * 32), smem, s, (const int8_t*) w.qs, (const __half*) w.hdr, w.rows, w.cols,
+                           a, m, y, resid));
+    } else {
+        if (!done[0]) { SK_CUDA(cudaFuncSetAttribute(q8_0_gemm_mma_kernel<NW, NT, NS, EPI_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem)); done[0] = true; }
+        SK_CUDA(launch_pdl(q8_0_gemm_mma_kernel<NW, NT, NS, EPI_STORE>, grid, dim3(NW * 32), smem, s, (const int8_t*) w.qs, (const __half*) w.hdr, w.rows, w.cols,
+                           a, m, y, resid));
+    }
+    return SKAINET_CUDA_OK;
+}
+
 }  // namespace
 
 // y[m][w.rows] (= resid +) act . W^T for m >= 2 activation rows already quantized (ActQ8K). Returns 1 when
@@ -232,6 +369,14 @@ int32_t launch_gemm_mma(const Weight& w, ActQ8K a, int m, float* y, const float*
     if (m <= 8) return launch_cfg<4, 1, 8>(w, a, m, y, resid, s);
     if (m <= 16) return launch_cfg<4, 2, 6>(w, a, m, y, resid, s);
     return launch_cfg<8, 4, 4>(w, a, m, y, resid, s);
+}
+
+// The same for Q8_0 weights and the two-term activation split; needs whole 256-column stages. 1 = not taken.
+int32_t launch_gemm_mma_q8(const Weight& w, ActSplit a, int m, float* y, const float* resid, cudaStream_t s) {
+    if (w.enc != SKAINET_ENC_Q8_0 || w.cols % 256 != 0 || m < 2) return 1;     // from two rows up: the per-pass Q8_0 matvec is slower
+    if (m <= 8) return launch_cfg_q8<4, 1, 4>(w, a, m, y, resid, s);
+    if (m <= 16) return launch_cfg_q8<4, 2, 4>(w, a, m, y, resid, s);
+    return launch_cfg_q8<8, 4, 3>(w, a, m, y, resid, s);
 }
 
 }  // namespace sk

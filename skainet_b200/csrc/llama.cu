@@ -287,7 +287,9 @@ static int32_t linear(Model& m, const Weight& w, int rows, float* y, float* resi
         if (st != 1) return st;
     }
     if (rows >= 2 && matvec_env_mode() == 0) {
-        const int32_t st = launch_gemm_mma(w, act_q8k_layout(m.act, rows, w.cols), rows, resid_inplace ? resid_inplace : y, resid_inplace, s);
+        const int32_t st = w.enc == SKAINET_ENC_Q8_0
+            ? launch_gemm_mma_q8(w, act_split_layout(m.act, rows, w.cols), rows, resid_inplace ? resid_inplace : y, resid_inplace, s)
+            : launch_gemm_mma(w, act_q8k_layout(m.act, rows, w.cols), rows, resid_inplace ? resid_inplace : y, resid_inplace, s);
         if (st != 1) return st;
     }
     float* out = resid_inplace ? m.tmp : y;

@@ -313,7 +313,9 @@ int32_t launch_matvec(const Weight& w, const float* x, const void* act_scratch, 
     // SKAINET_MATVEC=direct|stream selects the earlier kernel generations (kept for A/B measurements).
     static const bool force_direct = matvec_env_mode() == 1;
     if (m >= 2 && matvec_env_mode() == 0) {       // several activation rows: tensor-core tile kernel
-        const int32_t st = launch_gemm_mma(w, act_q8k_layout(const_cast<void*>(act_scratch), m, w.cols), m, y, nullptr, s);
+        const int32_t st = w.enc == SKAINET_ENC_Q8_0
+            ? launch_gemm_mma_q8(w, act_split_layout(const_cast<void*>(act_scratch), m, w.cols), m, y, nullptr, s)
+            : launch_gemm_mma(w, act_q8k_layout(const_cast<void*>(act_scratch), m, w.cols), m, y, nullptr, s);
         if (st != 1) return st;
     }
     for (int m0 = 0; m0 < m;) {
