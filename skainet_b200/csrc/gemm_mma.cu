@@ -362,9 +362,10 @@ int32_t launch_gemm_mma(const Weight& w, ActQ8K a, int m, float* y, const float*
         const int32_t st = launch_gemm_tc(w, a, m, y, resid, s);
         if (st != 1) return st;
     }
-    // Up to four activation rows stay with the streaming matvec kernels (faster there). Few rows: weight
-    // streaming decides, so small row tiles (many CTAs) and a deep pipeline; many rows: 128 x 32 output tiles.
-    if (m <= 4) return 1;
+    // One or two activation rows stay with the streaming matvec kernels (faster there; from three rows the tile
+    // kernel wins: 13.6 vs 15.7 us on 11008x4096). Few rows: weight streaming decides, so 64-row tiles and a deep
+    // pipeline; many rows: 128 x 32 output tiles.
+    if (m <= 2) return 1;
     // (row tiles of 32 or 16 for weights with few rows were measured slower: more activation re-fetch per weight byte)
     if (m <= 8) return launch_cfg<4, 1, 8>(w, a, m, y, resid, s);
     if (m <= 16) return launch_cfg<4, 2, 6>(w, a, m, y, resid, s);
