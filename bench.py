@@ -721,6 +721,7 @@ def run_decode(args) -> None:
         torch.cuda.synchronize()
 
     warm = max(3, args.warmup)
+    barrier()                                             # ranks start their first step together (peer waits are bounded)
     m.generate(first, warm)
     bytes_step, launches_step = m.step_cost(batch)
     sampler = ClockSampler(local)

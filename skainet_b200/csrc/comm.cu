@@ -74,7 +74,7 @@ constexpr int P2P_MAX_WORLD = 8;
 constexpr int P2P_CTA_ELEMS = 1024;                 // floats per CTA (256 threads x float4)
 constexpr int P2P_MAX_CTAS = 64;
 constexpr int P2P_MAX_ELEMS = P2P_CTA_ELEMS * P2P_MAX_CTAS;
-constexpr int P2P_SPIN_LIMIT = 1 << 24;             // ~1 s of polling, then the kernel gives up and reports
+constexpr int P2P_SPIN_LIMIT = 1 << 25;             // several seconds of polling (ranks may enter their first step apart), then the kernel gives up and reports
 
 // Per-rank region, identical layout on every rank:
 //   inbox [2][world][P2P_MAX_ELEMS] float | flags [world][P2P_MAX_CTAS] int | seq [P2P_MAX_CTAS] int (local only)
