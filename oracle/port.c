@@ -448,6 +448,23 @@ API void oracle_rope(float* x, int32_t heads, int32_t d, int32_t pos, float thet
     }
 }
 
+/* The same rotation applied to a cache-shaped block x[heads][len][d]: the row at index t of every head is
+ * rotated for position pos0 + t (what a decoder has applied to each key before it was cached). */
+API void oracle_rope_seq(float* x, int32_t heads, int32_t len, int32_t d, int32_t pos0, float theta, int32_t mode) {
+    for (int32_t t = 0; t < len; ++t) for (int32_t i = 0; i < d / 2; ++i) {
+        const double a = (double) (pos0 + t) * pow((double) theta, -2.0 * (double) i / (double) d);
+        const float c = (float) cos(a), s = (float) sin(a);
+        for (int32_t h = 0; h < heads; ++h) {
+            float* row = x + ((size_t) h * len + t) * d;
+            float* px = row + (mode == 0 ? 2 * i : i);
+            float* py = row + (mode == 0 ? 2 * i + 1 : i + d / 2);
+            const float a0 = *px, b0 = *py;
+            *px = a0 * c - b0 * s;
+            *py = a0 * s + b0 * c;
+        }
+    }
+}
+
 /* arg max, lowest index on ties:
  * skainet-backends/skainet-backend-cpu/src/commonMain/kotlin/sk/ainet/exec/tensor/ops/DefaultCpuOps.kt:3042-3078 */
 API int32_t oracle_argmax(const float* x, int32_t n) {

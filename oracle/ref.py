@@ -404,6 +404,15 @@ def rope(x: np.ndarray, heads: int, d: int, pos: int, theta: float = 1e4, mode: 
     return out
 
 
+def rope_seq(x: np.ndarray, pos0: int = 0, theta: float = 1e4, mode: int = 0) -> np.ndarray:
+    """x [heads, len, d]: row t of every head rotated for position pos0 + t (keys as a decoder caches them)."""
+    out = np.ascontiguousarray(x, dtype=np.float32).copy()
+    heads, ln, d = out.shape
+    port().oracle_rope_seq(_fp(out.reshape(-1)), C.c_int32(heads), C.c_int32(ln), C.c_int32(d), C.c_int32(pos0),
+                           C.c_float(theta), C.c_int32(mode))
+    return out
+
+
 def round_f16(x: np.ndarray) -> np.ndarray:
     """fp32 -> binary16 (round to nearest even) -> fp32: what an f16 KV cache holds."""
     return np.ascontiguousarray(x, dtype=np.float32).astype(np.float16).astype(np.float32)

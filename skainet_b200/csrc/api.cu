@@ -65,23 +65,58 @@ int32_t ensure_device() {
     return SKAINET_CUDA_OK;
 }
 
-int sm_count() {
-    const int c = t_device < 64 ? g_sm_count[t_device] : 0;
-    return c > 0 ? c : 148;
+// The CUDA device current on the calling thread (what every launch of this thread targets).
+static int current_device() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess) { cudaGetLastError(); d = 0; }
+    return d;
 }
 
-// One int per device, set by kernels whose bounded waits give up.
+int sm_count() {
+    const int dev = current_device();
+    if (dev < 0 || dev >= 64) return 148;
+    if (g_sm_count[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) g_sm_count[dev] = n;
+        else cudaGetLastError();
+    }
+    return g_sm_count[dev] > 0 ? g_sm_count[dev] : 148;
+}
+
+// Makes `device` current on this thread and records it as the thread's device, so that later calls of the
+// thread (flag, SM count, scratch) all refer to the device its kernels really run on.
+int32_t set_thread_device(int device) {
+    SK_TRY(ensure_device());
+    if (device != t_device || current_device() != device) {
+        SK_CUDA(cudaSetDevice(device));
+        t_device = device;
+    }
+    return SKAINET_CUDA_OK;
+}
+
+// One int per device, set by kernels whose bounded waits give up (1 = a wait on an asynchronous copy or
+// tensor-core barrier, 2 = a wait on a tensor-parallel peer). Keyed on the device that is current when it is
+// asked for, and allocated with that device current, so a kernel never receives a flag that lives on another GPU.
 static int* g_timeout_flag[64] = {nullptr};
 int* device_timeout_flag() {
-    if (t_device >= 64) return nullptr;
+    const int dev = current_device();
+    if (dev < 0 || dev >= 64) return nullptr;
     std::lock_guard<std::mutex> lk(g_mu);
-    if (!g_timeout_flag[t_device]) {
+    if (!g_timeout_flag[dev]) {
         int* p = nullptr;
         if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
         cudaMemset(p, 0, sizeof(int));
-        g_timeout_flag[t_device] = p;
+        g_timeout_flag[dev] = p;
     }
-    return g_timeout_flag[t_device];
+    return g_timeout_flag[dev];
+}
+
+// Turns a raised flag value into the status and message the entry points return.
+int32_t timeout_status(int value) {
+    if (value == 0) return SKAINET_CUDA_OK;
+    if (value == 2) set_error("a kernel's bounded wait on a tensor-parallel peer ran out (a rank is late or gone); the step's outputs are not valid");
+    else set_error("a kernel's bounded wait on an asynchronous copy or tensor-core barrier ran out; its outputs are not valid");
+    return SKAINET_CUDA_ERR_TIMEOUT;
 }
 
 // ---- weight registry ---------------------------------------------------------------------------------------
@@ -168,6 +203,24 @@ int32_t scratch_get(cudaStream_t stream, int slot, size_t nbytes, void** out) {
     return SKAINET_CUDA_OK;
 }
 
+size_t scratch_capacity(cudaStream_t stream, int slot) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_scratch.find({dev, stream});
+    return it == g_scratch.end() || it->second.empty() ? 0 : it->second[slot].n;
+}
+
+void scratch_release(cudaStream_t stream) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_scratch.find({dev, stream});
+    if (it == g_scratch.end()) return;
+    for (auto& b : it->second) if (b.p) cudaFree(b.p);
+    g_scratch.erase(it);
+}
+
 // Host twins share the default stream's staging buffers: one twin call at a time per process.
 static std::mutex g_twin_mu;
 #define SK_TWIN_LOCK() std::lock_guard<std::mutex> _twin_lk(::sk::g_twin_mu)
@@ -215,12 +268,8 @@ int32_t skainet_cuda_device_status(void) {
     if (!flag) return SKAINET_CUDA_OK;
     int v = 0;
     SK_CUDA(cudaMemcpy(&v, flag, sizeof(int), cudaMemcpyDeviceToHost));
-    if (v != 0) {
-        cudaMemset(flag, 0, sizeof(int));
-        set_error("a kernel's bounded wait on an asynchronous copy ran out; its outputs are not valid");
-        return SKAINET_CUDA_ERR_TIMEOUT;
-    }
-    return SKAINET_CUDA_OK;
+    if (v != 0) cudaMemset(flag, 0, sizeof(int));
+    return timeout_status(v);
 }
 
 int32_t skainet_cuda_selftest_bounded_wait(int32_t* outcome) {
@@ -275,7 +324,11 @@ int32_t skainet_cuda_stream_create(skainet_stream_t* out) {
     return SKAINET_CUDA_OK;
 }
 int32_t skainet_cuda_stream_destroy(skainet_stream_t stream) {
-    if (stream) SK_CUDA(cudaStreamDestroy(as_stream(stream)));
+    if (stream) {
+        SK_CUDA(cudaStreamSynchronize(as_stream(stream)));
+        scratch_release(as_stream(stream));          // the stream's scratch goes with it
+        SK_CUDA(cudaStreamDestroy(as_stream(stream)));
+    }
     return SKAINET_CUDA_OK;
 }
 int32_t skainet_cuda_stream_sync(skainet_stream_t stream) {
@@ -403,16 +456,17 @@ int32_t skainet_cuda_matmul_dev(skainet_weight_t h, const float* x_dev, int32_t 
     SK_TRY(ensure_device());
     cudaStream_t s = as_stream(stream);
     if (w->cols == 0) { SK_CUDA(cudaMemsetAsync(y_dev, 0, sizeof(float) * (size_t) m * w->rows, s)); return SKAINET_CUDA_OK; }
+    // One activation row in the native mode: a single launch that quantizes the row in its own prologue while
+    // its first weight tiles are already in flight (one-tile kernel, or the ring kernel for large weights).
+    if (m == 1 && act_mode == SKAINET_ACT_NATIVE && (w->enc == SKAINET_ENC_Q4_K || w->enc == SKAINET_ENC_Q8_0)) {
+        MatvecIn in; in.x = x_dev;
+        const int32_t st = launch_matvec_fused(*w, in, PREP_F32, y_dev, nullptr, s);
+        if (st != 1) return st;
+    }
     void* scratch = nullptr;
     const size_t need = act_scratch_bytes(w->enc, act_mode, m, w->cols);
     if (need) SK_TRY(scratch_get(s, SCRATCH_ACT, need, &scratch));
     SK_TRY(launch_act_quant(w->enc, act_mode, x_dev, m, w->cols, scratch, s));
-    if (m == 1 && act_mode == SKAINET_ACT_NATIVE && matvec_env_mode() == 0 && (w->enc == SKAINET_ENC_Q4_K || w->enc == SKAINET_ENC_Q8_0)) {
-        MatvecIn in;
-        if (w->enc == SKAINET_ENC_Q8_0) in.split = act_split_layout(scratch, 1, w->cols); else in.q8 = act_q8k_layout(scratch, 1, w->cols);
-        const int32_t st = launch_matvec_fused(*w, in, PREP_QUANTIZED, y_dev, nullptr, s);
-        if (st != 1) return st;
-    }
     return launch_matvec(*w, x_dev, scratch, m, y_dev, act_mode, s);
 }
 

@@ -23,146 +23,8 @@ namespace sk {
 constexpr float MASKED = -1.0e30f;
 
 // =================================================================================================
-// Decode attention, split-K.
+// Decode attention, split-K: merge of the partial records.
 // =================================================================================================
-constexpr int AD_THREADS = 128;          // 4 warps = 8 half-warp workers
-constexpr int AD_WORKERS = AD_THREADS / 16;
-constexpr int AD_TK = 4;                 // keys per worker per step (loads in flight: 2*AD_TK x 16 B per lane)
-
-__device__ __forceinline__ float half16_sum(float v) {
-    v += __shfl_xor_sync(0xffffffffu, v, 8);
-    v += __shfl_xor_sync(0xffffffffu, v, 4);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    return v;
-}
-__device__ __forceinline__ void unpack8(const uint4& r, float (&f)[8]) {
-    const __half2* h = reinterpret_cast<const __half2*>(&r);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { const float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
-}
-
-// partial record per (batch, head, split): [m, l, acc[D]]
-template <int D, int G>
-__global__ void __launch_bounds__(AD_THREADS)
-attn_decode_kernel(const float* __restrict__ q, const __half* __restrict__ kc, const __half* __restrict__ vc,
-                   float* __restrict__ out, float* __restrict__ part, int heads, int kv_heads, int64_t cache_stride,
-                   const int32_t* __restrict__ kv_len, float scale, int window, int chunk, int splits,
-                   int64_t q_row_stride, int always_partials) {
-    static_assert(D == 128 || D == 64, "head_dim");
-    skd::pdl_launch_dependents();
-    skd::pdl_wait();
-    constexpr int LPK = D / 8;            // lanes per key (16 B = 8 halves per lane)
-    constexpr int KPW = 32 / LPK;         // keys per warp-load
-    constexpr int NW = AD_THREADS / LPK;  // workers in the CTA
-    __shared__ float sm_m[NW][G], sm_l[NW][G];
-    __shared__ float sm_acc[NW][G][D];
-
-    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-    const int worker = threadIdx.x / LPK, wl = threadIdx.x % LPK;
-    const int len = kv_len[b];
-    int first = 0, end = len;
-    if (window > 0 && len - window > first) first = len - window;
-    const int begin = max(first, split * chunk), stop = min(end, (split + 1) * chunk);
-
-    float qr[G][8];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        const float* qp = q + (int64_t) b * q_row_stride + (int64_t) (kvh * G + g) * D + wl * 8;
-        const float4 a = __ldg((const float4*) qp), c = __ldg((const float4*) qp + 1);
-        qr[g][0] = a.x; qr[g][1] = a.y; qr[g][2] = a.z; qr[g][3] = a.w;
-        qr[g][4] = c.x; qr[g][5] = c.y; qr[g][6] = c.z; qr[g][7] = c.w;
-    }
-    float m[G], l[G], acc[G][8];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        m[g] = MASKED; l[g] = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[g][i] = 0.0f;
-    }
-    const __half* kb = kc + ((int64_t) b * kv_heads + kvh) * cache_stride * D + wl * 8;
-    const __half* vb = vc + ((int64_t) b * kv_heads + kvh) * cache_stride * D + wl * 8;
-
-    // Workers of one warp walk in lock-step (shuffles are warp-wide), so the loop bound is per warp.
-    const int warp_first_worker = (threadIdx.x >> 5) * KPW;
-    for (int k0 = begin + warp_first_worker * AD_TK; k0 < stop; k0 += NW * AD_TK) {
-        const int kmine = k0 + (worker - warp_first_worker) * AD_TK;
-        uint4 kr[AD_TK], vr[AD_TK];
-#pragma unroll
-        for (int t = 0; t < AD_TK; ++t) {
-            const int key = kmine + t;
-            if (key < stop) {
-                kr[t] = skd::ld_stream(kb + (int64_t) key * D);
-                vr[t] = skd::ld_stream(vb + (int64_t) key * D);
-            } else { kr[t] = make_uint4(0, 0, 0, 0); vr[t] = make_uint4(0, 0, 0, 0); }
-        }
-        float s[AD_TK][G];
-#pragma unroll
-        for (int t = 0; t < AD_TK; ++t) {
-            float kf[8]; unpack8(kr[t], kf);
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                float p = 0.0f;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) p += qr[g][i] * kf[i];
-                if (LPK == 16) p = half16_sum(p);
-                else { p += __shfl_xor_sync(~0u, p, 4); p += __shfl_xor_sync(~0u, p, 2); p += __shfl_xor_sync(~0u, p, 1); }
-                s[t][g] = (kmine + t < stop) ? p * scale : MASKED;
-            }
-        }
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            float mx = m[g];
-#pragma unroll
-            for (int t = 0; t < AD_TK; ++t) mx = fmaxf(mx, s[t][g]);
-            const float corr = expf(m[g] - mx);
-            m[g] = mx;
-            l[g] *= corr;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[g][i] *= corr;
-#pragma unroll
-            for (int t = 0; t < AD_TK; ++t) s[t][g] = (kmine + t < stop) ? expf(s[t][g] - mx) : 0.0f;
-        }
-#pragma unroll
-        for (int t = 0; t < AD_TK; ++t) {
-            float vf[8]; unpack8(vr[t], vf);
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                l[g] += s[t][g];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) acc[g][i] += s[t][g] * vf[i];
-            }
-        }
-    }
-    // merge the CTA's workers (fixed order)
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        if (wl == 0) { sm_m[worker][g] = m[g]; sm_l[worker][g] = l[g]; }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) sm_acc[worker][g][wl * 8 + i] = acc[g][i];
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < G * D; idx += AD_THREADS) {
-        const int g = idx / D, dd = idx % D;
-        float mx = MASKED;
-        for (int w = 0; w < NW; ++w) mx = fmaxf(mx, sm_m[w][g]);
-        float lt = 0.0f, at = 0.0f;
-        for (int w = 0; w < NW; ++w) {
-            const float c = expf(sm_m[w][g] - mx);
-            lt += c * sm_l[w][g];
-            at += c * sm_acc[w][g][dd];
-        }
-        const int head = kvh * G + g;
-        if (splits == 1 && !always_partials) {
-            out[((int64_t) b * heads + head) * D + dd] = lt > 0.0f ? at / lt : 0.0f;
-        } else {
-            float* rec = part + (((int64_t) b * heads + head) * splits + split) * (D + 2);
-            rec[2 + dd] = at;
-            if (dd == 0) { rec[0] = mx; rec[1] = lt; }
-        }
-    }
-}
-
 // Merge of split-K partial records {max, sum, acc[D]}: thread (group, element) folds the splits
 // group, group+MG, .. in chunks of eight whose loads are all issued before the first use (one memory
 // round trip per chunk), then the MG groups are folded in a fixed order through shared memory. Returns
@@ -423,10 +285,8 @@ attn_decode_mma_kernel(const float* __restrict__ q, int64_t q_row_stride, const 
     }
 }
 
-static int attn_min_keys() {
-    static const int min_keys = []() { const char* e = getenv("SKAINET_ATTN_MIN_KEYS"); return e ? std::max(16, atoi(e)) : 128; }();
-    return min_keys;
-}
+// Fewest keys a split is given: one 16-key tile per warp of the split-K kernel.
+static int attn_min_keys() { return 128; }
 static int decode_splits(int batch, int kv_heads, int max_kv_len) {
     // One wave: the split-K kernel holds one CTA of eight warps per SM (register-bound), and a second wave
     // would double its time. Each split gets at least min_keys keys (one 16-key tile per warp at 128).
@@ -488,14 +348,6 @@ static void launch_decode_dg(const float* q, const __half* k, const __half* v, f
                              int heads, int kv_heads, int64_t cache_stride, const int32_t* kv_len, float scale,
                              int window, int chunk, int splits, int64_t q_row_stride, int always_partials, cudaStream_t s) {
     dim3 grid(splits, kv_heads, batch);
-    // SKAINET_ATTN=simt selects the CUDA-core kernel (kept for A/B measurements)
-    static const bool simt = []() { const char* e = getenv("SKAINET_ATTN"); return e && strcmp(e, "simt") == 0; }();
-    if (simt) {
-        launch_pdl(attn_decode_kernel<D, G>, grid, dim3(AD_THREADS), 0, s, q, k, v, out, part, heads, kv_heads, cache_stride, kv_len,
-                   scale, window, chunk, splits, q_row_stride, always_partials);
-        if (splits > 1 && !always_partials) launch_pdl(attn_merge_kernel<D>, dim3(batch * heads), dim3(D * MG), 0, s, (const float*) part, out, splits);
-        return;
-    }
     const bool direct = splits == 1 && !always_partials;
     launch_pdl(attn_decode_mma_kernel<D>, grid, dim3(AM_WARPS * 32), 0, s, q, q_row_stride, k, v, part, heads, kv_heads, G, cache_stride, kv_len,
                scale, window, chunk, splits, direct ? out : (float*) nullptr);
@@ -823,9 +675,7 @@ attn_prefill_mma_kernel(const float* __restrict__ q, const __half* __restrict__ 
 int32_t launch_sdpa_cache(const float* q, const __half* k, const __half* v, float* out, int batch, int heads,
                           int kv_heads, int seq_q, int seq_kv, int64_t cache_stride, int d, float scale, int window,
                           const int32_t* q_abs_base, cudaStream_t s) {
-    // SKAINET_ATTN=simt keeps the CUDA-core row kernel (A/B measurements)
-    static const bool simt = []() { const char* e = getenv("SKAINET_ATTN"); return e && strcmp(e, "simt") == 0; }();
-    if (!simt && (d == 128 || d == 64) && batch > 0 && seq_q > 0 && heads % kv_heads == 0 && batch <= 65535 && heads <= 65535) {
+    if ((d == 128 || d == 64) && batch > 0 && seq_q > 0 && heads % kv_heads == 0 && batch <= 65535 && heads <= 65535) {
         dim3 grid((seq_q + 7) / 8, heads, batch);
         if (d == 128) SK_CUDA(launch_pdl(attn_prefill_mma_kernel<128>, grid, dim3(AM_WARPS * 32), 0, s, q, k, v, out, heads, kv_heads, seq_q, cache_stride, q_abs_base, scale, window));
         else SK_CUDA(launch_pdl(attn_prefill_mma_kernel<64>, grid, dim3(AM_WARPS * 32), 0, s, q, k, v, out, heads, kv_heads, seq_q, cache_stride, q_abs_base, scale, window));

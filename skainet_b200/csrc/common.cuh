@@ -75,12 +75,17 @@ Weight* weight_from_handle(skainet_weight_t h);   // nullptr (+ error set) when 
 // Device scratch reused across calls on one stream (quantized activations, split-K partials).
 // Grown on demand outside stream capture; never shrinks.
 int32_t scratch_get(cudaStream_t stream, int slot, size_t nbytes, void** out);
+size_t scratch_capacity(cudaStream_t stream, int slot);   // bytes the slot holds now (0 if never used)
+void scratch_release(cudaStream_t stream);                // frees every slot of a stream about to be destroyed
 enum { SCRATCH_ACT = 0, SCRATCH_ATTN = 1, SCRATCH_TWIN_A = 2, SCRATCH_TWIN_B = 3, SCRATCH_TWIN_C = 4,
-       SCRATCH_TWIN_D = 5, SCRATCH_TWIN_E = 6, SCRATCH_TWIN_F = 7, SCRATCH_FUSED = 8, SCRATCH_FUSED2 = 9, SCRATCH_SLOTS = 10 };
+       SCRATCH_TWIN_D = 5, SCRATCH_TWIN_E = 6, SCRATCH_TWIN_F = 7, SCRATCH_FUSED = 8, SCRATCH_FUSED2 = 9, SCRATCH_GEMM = 10,
+       SCRATCH_FFN = 11, SCRATCH_SLOTS = 12 };
 
 int sm_count();
 int32_t launch_bounded_wait_selftest(int* reached_end, cudaStream_t s);   // probe.cu
-int* device_timeout_flag();   // device int set by a kernel whose bounded wait ran out (nullptr if unavailable)
+int* device_timeout_flag();   // current device's int, set by a kernel whose bounded wait ran out (nullptr if unavailable)
+int32_t timeout_status(int flag_value);       // OK for 0, else ERR_TIMEOUT with a message naming the kind of wait
+int32_t set_thread_device(int device);        // cudaSetDevice + the thread's device bookkeeping
 
 // ---- launchers implemented in the kernel files ------------------------------------------------------
 // repack.cu
@@ -99,7 +104,6 @@ int32_t launch_sdpa_cache(const float* q, const __half* k, const __half* v, floa
                           const int32_t* q_abs_base, cudaStream_t s);
 int32_t launch_embed(const Weight& w, const int32_t* ids, int n, float* out, cudaStream_t s);
 // matvec.cu
-int matvec_env_mode();
 size_t act_scratch_bytes(int enc, int act_mode, int m, int cols);
 int32_t launch_act_quant(int enc, int act_mode, const float* x, int m, int cols, void* scratch, cudaStream_t s);
 struct ActQ8K;

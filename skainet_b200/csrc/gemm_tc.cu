@@ -42,7 +42,8 @@ constexpr int TC_A_BYTES = TC_M * TC_KS * 2, TC_B_BYTES = TC_N * TC_KS * 2, TC_S
 constexpr int TC_S2A_BYTES = TC_M * 16 * 2, TC_S2B_BYTES = TC_N * 16 * 2, TC_S2_BYTES = TC_S2A_BYTES + TC_S2B_BYTES;
 constexpr int TC_OFF_S2 = TC_STAGES * TC_STAGE_BYTES;
 constexpr int TC_OFF_DX = TC_OFF_S2 + 2 * TC_S2_BYTES;
-constexpr int TC_OFF_BAR = TC_OFF_DX + 4 * TC_N * 4;
+constexpr int TC_DX_SLOTS = 2;                   // block-scale slots: one per accumulator set
+constexpr int TC_OFF_BAR = TC_OFF_DX + TC_DX_SLOTS * TC_N * 4;
 constexpr int TC_NBARS = 2 * TC_STAGES + 6;      // full, empty per stage; s2_full, acc_full, acc_empty per accumulator set
 constexpr int TC_SMEM = TC_OFF_BAR + TC_NBARS * 8 + 16;
 constexpr uint32_t TC_IDESC = (1u << 4) | ((uint32_t) (TC_N >> 3) << 17) | ((uint32_t) (TC_M >> 4) << 24);   // f16 x f16 -> f32, K-major both
@@ -243,10 +244,8 @@ q4k_gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ h
                 fence_async_smem();                    // order the copies below after the generic-proxy reads just observed
                 skd::mbar_expect_tx(s2_full + set, TC_S2B_BYTES + TC_N * 4);
                 skd::bulk_g2s(s2 + TC_S2A_BYTES, hs + ((size_t) tile_n * bpr + kb) * (TC_S2B_BYTES / 2), TC_S2B_BYTES, s2_full + set);
-                // The block scales rotate over four slots although two would follow from the barrier protocol: with two,
-                // a slot was seen overwritten before a late warp of the epilogue had read it (about one run in three on
-                // the 129 x 4096, m = 130 test); with four, no run differs.
-                skd::bulk_g2s(smem + TC_OFF_DX + (kb & 3) * TC_N * 4, dxt + (size_t) kb * m_pad + col0, TC_N * 4, s2_full + set);
+                // the slot of super-block kb-2: every epilogue warp arrived on acc_empty after reading it
+                skd::bulk_g2s(smem + TC_OFF_DX + (kb % TC_DX_SLOTS) * TC_N * 4, dxt + (size_t) kb * m_pad + col0, TC_N * 4, s2_full + set);
             }
         }
         __syncwarp();
@@ -268,7 +267,7 @@ q4k_gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ h
             // the block scales below were written by a bulk copy: observe the barrier that tracked it (long complete)
             if (!__all_sync(0xffffffffu, wait_backoff(s2_full + set, (kb >> 1) & 1, timeout_flag))) { ok = false; return; }
             tc_fence_after();
-            const float* dx = (const float*) (smem + TC_OFF_DX) + (kb & 3) * TC_N + part * NC;
+            const float* dx = (const float*) (smem + TC_OFF_DX) + (kb % TC_DX_SLOTS) * TC_N + part * NC;
             const uint32_t t0 = tmem + ((uint32_t) ((warp & 3) * 32) << 16) + set * 256 + part * NC;
 #pragma unroll
             for (int c = 0; c < NC; c += 16) {
@@ -395,44 +394,31 @@ q4k_gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ h
     }
 }
 
-struct TcScratch { void* p = nullptr; size_t bytes = 0; };
-TcScratch g_tc_scratch[64];
-std::mutex g_tc_mu;
-
 }  // namespace
 
 // y[m][w.rows] (= resid +) for m >= 128 quantized activation rows. Returns 1 when not taken (the caller
 // falls back to the mma.sync tile kernel): other encodings, few rows, or scratch that would have to grow
 // while the stream is being captured.
 int32_t launch_gemm_tc(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s) {
-    static const bool off = []() { const char* e = getenv("SKAINET_GEMM"); return e && strcmp(e, "mma") == 0; }();
-    if (off || w.enc != SKAINET_ENC_Q4_K || m < 128 || w.bpr < 1) return 1;
-    int dev = 0;
-    SK_CUDA(cudaGetDevice(&dev));
+    if (w.enc != SKAINET_ENC_Q4_K || m < 128 || w.bpr < 1) return 1;
     const int m_pad = (m + TC_N - 1) / TC_N * TC_N;
     const size_t xh_bytes = (size_t) m_pad * w.cols * 2, hs_bytes = (size_t) m_pad * (w.cols / 16) * 2, dx_bytes = (size_t) w.bpr * m_pad * 4;
     const size_t need = xh_bytes + hs_bytes + dx_bytes + 3 * 256;
-    void* base = nullptr;
-    {
-        std::lock_guard<std::mutex> lock(g_tc_mu);
-        TcScratch& sc = g_tc_scratch[dev & 63];
-        if (sc.bytes < need) {
-            cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
-            if (cudaStreamIsCapturing(s, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) { cudaGetLastError(); return 1; }
-            SK_CUDA(cudaStreamSynchronize(s));
-            if (sc.p) SK_CUDA(cudaFree(sc.p));
-            sc.p = nullptr; sc.bytes = 0;
-            SK_CUDA(cudaMalloc(&sc.p, need));
-            sc.bytes = need;
-        }
-        base = sc.p;
+    // the operand tiles live in the calling stream's own scratch (calls on different streams do not share them)
+    if (scratch_capacity(s, SCRATCH_GEMM) < need) {
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(s, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) { cudaGetLastError(); return 1; }
     }
+    void* base = nullptr;
+    SK_TRY(scratch_get(s, SCRATCH_GEMM, need, &base));
     auto up = [](size_t v) { return (v + 255) & ~(size_t) 255; };
     __half* xh = (__half*) base;
     __half* hs = (__half*) ((uint8_t*) base + up(xh_bytes));
     float* dxt = (float*) ((uint8_t*) base + up(xh_bytes) + up(hs_bytes));
-    static bool attr_done = false;
-    if (!attr_done) { SK_CUDA(cudaFuncSetAttribute(q4k_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM)); attr_done = true; }
+    static std::once_flag attr_once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(attr_once, []() { attr_err = cudaFuncSetAttribute(q4k_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM); });
+    SK_CUDA(attr_err);
     const int64_t n16 = (int64_t) m_pad * (w.cols / 16);
     SK_CUDA(launch_pdl(act_f16_tiles_kernel, dim3((unsigned) ((n16 + 255) / 256)), dim3(256), 0, s, a, m, m_pad, w.cols, xh, hs, dxt));
     dim3 grid((w.rows + TC_M - 1) / TC_M, m_pad / TC_N);

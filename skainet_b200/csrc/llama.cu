@@ -182,10 +182,12 @@ __global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__
     for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) x[i] += y[i];
 }
 
-// Seeded f16 noise into the cache (fake_prefill).
-__global__ void fill_cache_kernel(__half* kc, __half* vc, int64_t n, uint64_t seed) {
+// Seeded f16 noise into the cache (fake_prefill). The value of an element depends only on the seed and on its
+// place in the unsharded cache (global kv head, position, dim), so every tensor-parallel size decodes the same context.
+__global__ void fill_cache_kernel(__half* kc, __half* vc, int64_t n, int64_t per_head, int head0, uint64_t seed) {
     for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) {
-        uint64_t z = (seed + (uint64_t) i) * 0x9E3779B97F4A7C15ull;
+        const int64_t gi = i + (int64_t) head0 * per_head;      // index in the full [kv_heads][max_seq][head_dim] cache of the sequence
+        uint64_t z = (seed + (uint64_t) gi) * 0x9E3779B97F4A7C15ull;
         z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull; z ^= z >> 27;
         kc[i] = __float2half_rn(((float) (z & 0xFFFF) / 32768.0f - 1.0f) * 1.7f);
         vc[i] = __float2half_rn(((float) ((z >> 16) & 0xFFFF) / 32768.0f - 1.0f) * 1.7f);
@@ -221,7 +223,10 @@ struct Model {
     std::map<std::pair<int, int>, cudaGraphExec_t> graphs;   // (batch, bucket) -> step graph
     bool finalized = false;
     Comm* comm = nullptr;
+    bool comm_broken = false;      // a peer wait ran out: the group's inboxes are out of step, the model refuses further steps
     int device = 0;
+    int* d_flag = nullptr;         // the device's bounded-wait flag (owned by the library, not by the model)
+    int* h_flag = nullptr;         // pinned host copy read after every synchronising call
     uint64_t magic = 0;
 };
 
@@ -280,13 +285,13 @@ static int bucket_of(const Model& m, int len) {
 
 // y[rows][w.rows] (= resid +) W . act   for activation rows already quantized into m.act.
 static int32_t linear(Model& m, const Weight& w, int rows, float* y, float* resid_inplace, cudaStream_t s) {
-    if (rows == 1 && matvec_env_mode() == 0) {
+    if (rows == 1) {
         MatvecIn in;
         if (w.enc == SKAINET_ENC_Q8_0) in.split = act_split_layout(m.act, 1, w.cols); else in.q8 = act_q8k_layout(m.act, 1, w.cols);
         const int32_t st = launch_matvec_fused(w, in, PREP_QUANTIZED, resid_inplace ? resid_inplace : y, resid_inplace, s);
         if (st != 1) return st;
     }
-    if (rows >= 2 && matvec_env_mode() == 0) {
+    if (rows >= 2) {
         const int32_t st = w.enc == SKAINET_ENC_Q8_0
             ? launch_gemm_mma_q8(w, act_split_layout(m.act, rows, w.cols), rows, resid_inplace ? resid_inplace : y, resid_inplace, s)
             : launch_gemm_mma(w, act_q8k_layout(m.act, rows, w.cols), rows, resid_inplace ? resid_inplace : y, resid_inplace, s);
@@ -299,6 +304,21 @@ static int32_t linear(Model& m, const Weight& w, int rows, float* y, float* resi
         SK_CUDA(launch_pdl(add_rows_kernel, dim3((unsigned) std::min<int64_t>((n + 255) / 256, 1184)), dim3(256), 0, s, resid_inplace, (const float*) out, n));
     }
     return SKAINET_CUDA_OK;
+}
+
+template <int MODE>
+static int32_t prep(Model& m, const float* in, const float* gamma, int rows, int n, bool split, cudaStream_t s);
+
+// y[rows][w.rows] = W . quantize(rmsnorm(x, gamma)). One activation row takes a single launch: the matvec
+// kernel normalises and quantizes the row in its own prologue while its first weight tiles are in flight.
+static int32_t linear_normed(Model& m, const Weight& w, const float* x, const float* gamma, int rows, float* y, cudaStream_t s) {
+    if (rows == 1) {
+        MatvecIn in; in.x = x; in.gamma = gamma; in.eps = m.cfg.rms_eps;
+        const int32_t st = launch_matvec_fused(w, in, PREP_NORM_F32, y, nullptr, s);
+        if (st != 1) return st;
+    }
+    SK_TRY(prep<PK_NORM>(m, x, gamma, rows, w.cols, w.enc == SKAINET_ENC_Q8_0, s));
+    return linear(m, w, rows, y, nullptr, s);
 }
 
 template <int MODE>
@@ -330,20 +350,22 @@ static int32_t body(Model& m, int rows, bool prefill, int seq, int kv_bound, cud
     const bool tp = c.tp_world > 1, rank0 = c.tp_rank == 0;
     // Under TP the group sum of a row-parallel projection is fused with the RMSNorm + quantizer that follows it
     // when the peer-memory kernel applies; `normed` says the next layer's input is already prepared.
-    auto sum_then_norm = [&](const float* gamma) -> int32_t {
+    // Returns with `prepared` saying whether the quantized normalised row is already in m.act.
+    auto sum_then_norm = [&](const float* gamma, bool* prepared) -> int32_t {
+        *prepared = false;
         if (tp && !lin_split) {
             const int32_t st = comm_all_reduce_norm_quant(m.comm, m.x, rows, c.d_model, gamma, c.rms_eps, act_q8k_layout(m.act, rows, c.d_model), s);
+            if (st == SKAINET_CUDA_OK) *prepared = true;
             if (st != 1) return st;
         }
-        SK_TRY(tp_sum(m, m.x, (int64_t) rows * c.d_model, s));
-        return prep<PK_NORM>(m, m.x, gamma, rows, c.d_model, lin_split, s);
+        return tp_sum(m, m.x, (int64_t) rows * c.d_model, s);
     };
     bool normed = false;
     for (int l = 0; l < c.n_layers; ++l) {
         Layer& L = m.layers[l];
-        if (!normed) SK_TRY(prep<PK_NORM>(m, m.x, L.g_attn, rows, c.d_model, lin_split, s));
+        if (normed) SK_TRY(linear(m, *L.wqkv, rows, m.qkv, nullptr, s));       // the group sum already left the quantized row
+        else SK_TRY(linear_normed(m, *L.wqkv, m.x, L.g_attn, rows, m.qkv, s));
         normed = false;
-        SK_TRY(linear(m, *L.wqkv, rows, m.qkv, nullptr, s));
         SK_CUDA(launch_pdl(rope_append_kernel, dim3(rows, H + 2 * HK), dim3(D / 2), 0, s, m.qkv, H, HK, D, (const float*) m.cos_t,
                            (const float*) m.sin_t, (const int32_t*) m.pos, (const int32_t*) (prefill ? m.row_seq : nullptr), prefill ? 1 : 0,
                            L.kc, L.vc, (int64_t) c.max_seq, c.rope_mode));
@@ -364,11 +386,13 @@ static int32_t body(Model& m, int rows, bool prefill, int seq, int kv_bound, cud
         if (!fused_attn) SK_TRY(prep<PK_QUANT>(m, m.attn, nullptr, rows, H * D, lin_split, s));
         // row-parallel projections under TP: rank 0 carries the residual, then the group sums
         if (tp && !rank0) SK_TRY(linear(m, *L.wo, rows, m.x, nullptr, s)); else SK_TRY(linear(m, *L.wo, rows, nullptr, m.x, s));
-        SK_TRY(sum_then_norm(L.g_ffn));
-        SK_TRY(linear(m, *L.wgu, rows, m.gu, nullptr, s));
+        bool ffn_ready = false;
+        SK_TRY(sum_then_norm(L.g_ffn, &ffn_ready));
+        if (ffn_ready) SK_TRY(linear(m, *L.wgu, rows, m.gu, nullptr, s));
+        else SK_TRY(linear_normed(m, *L.wgu, m.x, L.g_ffn, rows, m.gu, s));
         SK_TRY(prep<PK_SWIGLU>(m, m.gu, nullptr, rows, m.ffn_l, lin_split, s));
         if (tp && !rank0) SK_TRY(linear(m, *L.wdown, rows, m.x, nullptr, s)); else SK_TRY(linear(m, *L.wdown, rows, nullptr, m.x, s));
-        if (tp && l + 1 < c.n_layers) { SK_TRY(sum_then_norm(m.layers[l + 1].g_attn)); normed = true; }
+        if (tp && l + 1 < c.n_layers) SK_TRY(sum_then_norm(m.layers[l + 1].g_attn, &normed));
         else SK_TRY(tp_sum(m, m.x, (int64_t) rows * c.d_model, s));
     }
     return SKAINET_CUDA_OK;
@@ -432,18 +456,17 @@ __global__ void pack_pairs_kernel(const float* vals, const int32_t* idxs, float2
 // Enqueues one greedy decode step for sequences 0..batch-1 on s.
 static int32_t enqueue_step(Model& m, int batch, int kv_bound, cudaStream_t s) {
     const auto& c = m.cfg;
-    begin_step_kernel<<<1, 256, 0, s>>>(m.pos, m.kv_len, batch);
+    begin_step_kernel<<<(batch + 255) / 256, 256, 0, s>>>(m.pos, m.kv_len, batch);
     SK_TRY(launch_embed(*m.embed, m.cur_token, batch, m.x, s));
     SK_TRY(body(m, batch, false, 0, kv_bound, s));
-    SK_TRY(prep<PK_NORM>(m, m.x, m.g_out, batch, c.d_model, c.table_enc == SKAINET_ENC_Q8_0, s));
-    SK_TRY(linear(m, *m.head, batch, m.logits, nullptr, s));
+    SK_TRY(linear_normed(m, *m.head, m.x, m.g_out, batch, m.logits, s));
     if (c.tp_world > 1) {
         float* vals = m.tmp; int32_t* idxs = (int32_t*) (m.tmp + batch);
         float2* mine = (float2*) (m.tmp + 2 * batch); float2* all = mine + batch;
         SK_CUDA(launch_pdl(argmax_pairs_kernel, dim3(batch), dim3(1024), 0, s, (const float*) m.logits, m.vocab_l, c.tp_rank * m.vocab_l, vals, idxs));
-        SK_CUDA(launch_pdl(pack_pairs_kernel, dim3(1), dim3(256), 0, s, (const float*) vals, (const int32_t*) idxs, mine, batch));
+        SK_CUDA(launch_pdl(pack_pairs_kernel, dim3((batch + 255) / 256), dim3(256), 0, s, (const float*) vals, (const int32_t*) idxs, mine, batch));
         SK_TRY(comm_all_gather(m.comm, mine, all, (int64_t) batch * 8, s));
-        SK_CUDA(launch_pdl(finish_step_kernel, dim3(1), dim3(256), 0, s, (const float2*) all, c.tp_world, batch, m.cur_token, m.pos, m.log, (const int32_t*) m.log_cursor));
+        SK_CUDA(launch_pdl(finish_step_kernel, dim3((batch + 255) / 256), dim3(256), 0, s, (const float2*) all, c.tp_world, batch, m.cur_token, m.pos, m.log, (const int32_t*) m.log_cursor));
     } else {
         SK_CUDA(launch_pdl(argmax_advance_kernel, dim3(batch), dim3(1024), 0, s, (const float*) m.logits, c.vocab, m.cur_token, m.pos, m.log, m.log_cursor, batch));
     }
@@ -489,10 +512,24 @@ static int32_t run_steps(Model& m, int batch, int n_steps) {
     return SKAINET_CUDA_OK;
 }
 
-static int32_t set_device_of(Model& m) {
-    SK_TRY(ensure_device());
-    SK_CUDA(cudaSetDevice(m.device));
+// The model's device becomes the calling thread's device (flag, SM count and scratch follow it).
+static int32_t set_device_of(Model& m) { return set_thread_device(m.device); }
+
+// Copies the bounded-wait flag next to the results a call is about to wait for ...
+static int32_t flag_fetch(Model& m, cudaStream_t s) {
+    if (m.d_flag && m.h_flag) SK_CUDA(cudaMemcpyAsync(m.h_flag, m.d_flag, sizeof(int), cudaMemcpyDeviceToHost, s));
     return SKAINET_CUDA_OK;
+}
+// ... and, after the stream has been synchronised, turns a raised flag into SKAINET_CUDA_ERR_TIMEOUT (clearing it).
+// A peer wait that ran out leaves the group's inboxes out of step, so the model refuses further steps.
+static int32_t flag_check(Model& m) {
+    if (!m.d_flag || !m.h_flag) return SKAINET_CUDA_OK;
+    const int v = *m.h_flag;
+    if (v == 0) return SKAINET_CUDA_OK;
+    *m.h_flag = 0;
+    cudaMemsetAsync(m.d_flag, 0, sizeof(int), m.stream);
+    if (v == 2) m.comm_broken = true;
+    return timeout_status(v);
 }
 
 static void free_model(Model* m) {
@@ -508,7 +545,8 @@ static void free_model(Model* m) {
                     (void*) m->pos, (void*) m->kv_len, (void*) m->log, (void*) m->log_cursor, (void*) m->row_seq})
         if (p) cudaFree(p);
     comm_destroy(m->comm);
-    if (m->stream) cudaStreamDestroy(m->stream);
+    if (m->h_flag) cudaFreeHost(m->h_flag);
+    if (m->stream) { scratch_release(m->stream); cudaStreamDestroy(m->stream); }
     m->magic = 0;
     delete m;
 }
@@ -538,11 +576,13 @@ int32_t skainet_cuda_llama_create(const skainet_llama_config* cfg, skainet_model
     SK_REQUIRE(c.d_model % 256 == 0 && (c.ffn_dim / c.tp_world) % be == 0 && (c.n_heads / c.tp_world * c.head_dim) % be == 0,
                "llama_create: d_model, ffn_dim/tp and heads*head_dim/tp must be multiples of the block size");
     SK_REQUIRE(c.max_seq >= 1 && c.max_batch >= 1, "llama_create: max_seq and max_batch must be positive");
+    SK_REQUIRE(c.max_batch <= 4096, "llama_create: max_batch %d above 4096", c.max_batch);
     SK_TRY(ensure_device());
-    device_timeout_flag();          // allocate the per-device flag now: not allowed later inside stream capture
     Model* m = new Model();
     m->cfg = c;
     cudaGetDevice(&m->device);
+    m->d_flag = device_timeout_flag();          // allocate the per-device flag now: not allowed later inside stream capture
+    if (cudaMallocHost((void**) &m->h_flag, sizeof(int)) == cudaSuccess) *m->h_flag = 0; else { cudaGetLastError(); m->h_flag = nullptr; }
     m->heads_l = c.n_heads / c.tp_world; m->kv_heads_l = c.n_kv_heads / c.tp_world;
     m->ffn_l = c.ffn_dim / c.tp_world; m->vocab_l = c.vocab / c.tp_world;
     m->layers.resize(c.n_layers);
@@ -739,6 +779,7 @@ int32_t skainet_cuda_llama_tp_init(skainet_model_t h, const uint8_t* id128) {
     if (m->cfg.tp_world <= 1) return SKAINET_CUDA_OK;
     SK_TRY(set_device_of(*m));
     if (m->comm) { comm_destroy(m->comm); m->comm = nullptr; }
+    m->comm_broken = false;
     return comm_create(m->cfg.tp_rank, m->cfg.tp_world, id128, &m->comm);
 }
 
@@ -754,6 +795,7 @@ int32_t skainet_cuda_llama_reset(skainet_model_t h) {
 static int32_t require_ready(Model* m, const char* who) {
     SK_REQUIRE(m->finalized, "%s: call llama_finalize first", who);
     SK_REQUIRE(m->cfg.tp_world == 1 || m->comm != nullptr, "%s: tensor-parallel model without a communicator", who);
+    if (m->comm_broken) { set_error("%s: an earlier step gave up waiting for a tensor-parallel peer; rebuild the group (llama_tp_init) before running again", who); return SKAINET_CUDA_ERR_COMM; }
     return set_device_of(*m);
 }
 
@@ -761,8 +803,7 @@ static int32_t require_ready(Model* m, const char* who) {
 static int32_t sample_row(Model& m, const float* xrow, int32_t* token_host) {
     const auto& c = m.cfg;
     cudaStream_t s = m.stream;
-    SK_TRY(prep<PK_NORM>(m, xrow, m.g_out, 1, c.d_model, c.table_enc == SKAINET_ENC_Q8_0, s));
-    SK_TRY(linear(m, *m.head, 1, m.logits, nullptr, s));
+    SK_TRY(linear_normed(m, *m.head, xrow, m.g_out, 1, m.logits, s));
     const float* full = m.logits;
     if (c.tp_world > 1) {
         SK_TRY(comm_all_gather(m.comm, m.logits, m.logits_full, (int64_t) m.vocab_l * 4, s));
@@ -770,8 +811,9 @@ static int32_t sample_row(Model& m, const float* xrow, int32_t* token_host) {
     }
     SK_TRY(launch_argmax(full, 1, c.vocab, m.cur_token, s));
     SK_CUDA(cudaMemcpyAsync(token_host, m.cur_token, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    SK_TRY(flag_fetch(m, s));
     SK_CUDA(cudaStreamSynchronize(s));
-    return SKAINET_CUDA_OK;
+    return flag_check(m);
 }
 
 int32_t skainet_cuda_llama_prefill(skainet_model_t h, int32_t seq, const int32_t* tokens_host, int32_t n, int32_t* next_token_host) {
@@ -792,7 +834,9 @@ int32_t skainet_cuda_llama_prefill(skainet_model_t h, int32_t seq, const int32_t
         SK_TRY(body(*m, rows, true, seq, m->host_pos[seq] + rows, s));
         m->host_pos[seq] += rows;
         SK_CUDA(cudaMemcpyAsync(m->pos + seq, &m->host_pos[seq], sizeof(int32_t), cudaMemcpyHostToDevice, s));
+        SK_TRY(flag_fetch(*m, s));
         SK_CUDA(cudaStreamSynchronize(s));     // host_pos/tokens buffers are reused by the next chunk
+        SK_TRY(flag_check(*m));
         done += rows; last_rows = rows;
     }
     if (next_token_host && n > 0) SK_TRY(sample_row(*m, m->x + (size_t) (last_rows - 1) * m->cfg.d_model, next_token_host));
@@ -808,6 +852,7 @@ int32_t skainet_cuda_llama_fake_prefill(skainet_model_t h, int32_t seq, int32_t 
     const size_t per_seq = (size_t) m->kv_heads_l * m->cfg.max_seq * m->cfg.head_dim;
     for (int l = 0; l < m->cfg.n_layers; ++l)
         fill_cache_kernel<<<592, 256, 0, m->stream>>>(m->layers[l].kc + seq * per_seq, m->layers[l].vc + seq * per_seq, (int64_t) per_seq,
+                                                     (int64_t) m->cfg.max_seq * m->cfg.head_dim, m->cfg.tp_rank * m->kv_heads_l,
                                                      seed + 977ull * l + 31ull * seq);
     SK_CUDA(cudaGetLastError());
     m->host_pos[seq] = n;
@@ -827,8 +872,9 @@ int32_t skainet_cuda_llama_decode(skainet_model_t h, int32_t batch, const int32_
     SK_CUDA(cudaMemsetAsync(m->log_cursor, 0, sizeof(int32_t), s));
     SK_TRY(run_steps(*m, batch, 1));
     SK_CUDA(cudaMemcpyAsync(tokens_out_host, m->cur_token, sizeof(int32_t) * batch, cudaMemcpyDeviceToHost, s));
+    SK_TRY(flag_fetch(*m, s));
     SK_CUDA(cudaStreamSynchronize(s));
-    return SKAINET_CUDA_OK;
+    return flag_check(*m);
 }
 
 int32_t skainet_cuda_llama_generate(skainet_model_t h, int32_t batch, const int32_t* first_tokens_host, int32_t n_steps, int32_t* out_tokens_host) {
@@ -843,8 +889,9 @@ int32_t skainet_cuda_llama_generate(skainet_model_t h, int32_t batch, const int3
     SK_CUDA(cudaMemsetAsync(m->log_cursor, 0, sizeof(int32_t), s));
     SK_TRY(run_steps(*m, batch, n_steps));
     if (n_steps > 0) SK_CUDA(cudaMemcpyAsync(out_tokens_host, m->log, sizeof(int32_t) * (size_t) n_steps * batch, cudaMemcpyDeviceToHost, s));
+    SK_TRY(flag_fetch(*m, s));
     SK_CUDA(cudaStreamSynchronize(s));
-    return SKAINET_CUDA_OK;
+    return flag_check(*m);
 }
 
 int32_t skainet_cuda_llama_logits(skainet_model_t h, int32_t batch, float* logits_host) {

@@ -260,18 +260,6 @@ q8_0_matvec_f32_kernel(const int8_t* __restrict__ codes, const __half* __restric
     if (lane == 0) y[(int64_t) m * rows + row] = acc;
 }
 
-// SKAINET_MATVEC=direct|stream selects the earlier kernel generations (kept for A/B measurements):
-// 0 = default (persistent for single rows), 1 = direct loads, 2 = one-tile streaming kernels.
-int matvec_env_mode() {
-    static const int mode = []() {
-        const char* e = getenv("SKAINET_MATVEC");
-        if (e && strcmp(e, "direct") == 0) return 1;
-        if (e && strcmp(e, "stream") == 0) return 2;
-        return 0;
-    }();
-    return mode;
-}
-
 // ---- dispatch -------------------------------------------------------------------------------------------
 template <int M>
 static void launch_q4k_m(const Weight& w, ActQ8K act, float* y, cudaStream_t s) {
@@ -310,9 +298,7 @@ int32_t launch_matvec(const Weight& w, const float* x, const void* act_scratch, 
         SK_CUDA(cudaGetLastError());
         return SKAINET_CUDA_OK;
     }
-    // SKAINET_MATVEC=direct|stream selects the earlier kernel generations (kept for A/B measurements).
-    static const bool force_direct = matvec_env_mode() == 1;
-    if (m >= 2 && matvec_env_mode() == 0) {       // several activation rows: tensor-core tile kernel
+    if (m >= 2) {       // several activation rows: tensor-core tile kernel
         const int32_t st = w.enc == SKAINET_ENC_Q8_0
             ? launch_gemm_mma_q8(w, act_split_layout(const_cast<void*>(act_scratch), m, w.cols), m, y, nullptr, s)
             : launch_gemm_mma(w, act_q8k_layout(const_cast<void*>(act_scratch), m, w.cols), m, y, nullptr, s);
@@ -322,7 +308,7 @@ int32_t launch_matvec(const Weight& w, const float* x, const void* act_scratch, 
         const int left = m - m0;
         const int mm = left >= 8 ? 8 : (left >= 4 ? 4 : (left >= 2 ? 2 : 1));
         float* yo = y + (int64_t) m0 * w.rows;
-        if (!force_direct) {
+        {   // shapes the tile kernels decline: the streaming kernel, then direct loads
             const int32_t st = launch_matvec_stream(w, act_scratch, m, m0, mm, yo, s);
             if (st == SKAINET_CUDA_OK) { m0 += mm; continue; }
             if (st != 1) return st;

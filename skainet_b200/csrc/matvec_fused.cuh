@@ -23,9 +23,8 @@ struct MatvecIn {
 // outside what the kernel takes (the caller then uses the general kernels).
 int32_t launch_matvec_fused(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s);
 
-// matvec_ring.cu: the persistent ring kernel for large weights (activation already quantized); same
-// return convention.
-int32_t launch_matvec_ring(const Weight& w, const MatvecIn& in, float* y, const float* resid, cudaStream_t s);
+// matvec_ring.cu: the persistent ring kernel for large weights, same activation forms and return convention.
+int32_t launch_matvec_ring(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s);
 // gemm_mma.cu: y[m][w.rows] (= resid +) for m >= 2 quantized activation rows on the tensor cores; 1 = not taken
 int32_t launch_gemm_mma(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s);
 int32_t launch_gemm_mma_q8(const Weight& w, ActSplit a, int m, float* y, const float* resid, cudaStream_t s);

@@ -14,6 +14,7 @@
 #include "actquant.cuh"
 #include "tma.cuh"
 #include "matvec_fused.cuh"
+#include "actprep.cuh"
 
 #include <cstdlib>
 
@@ -21,8 +22,8 @@ namespace sk {
 
 constexpr int RG_MAX_STAGES = 8;
 constexpr size_t RG_SMEM_MAX = 200 * 1024;
-// SKAINET_RING_KB overrides the per-SM ring budget (A/B measurements)
-static size_t ring_budget() { static const size_t v = []() { const char* e = getenv("SKAINET_RING_KB"); return (size_t) (e ? atoi(e) : 190) << 10; }(); return std::min(v, RG_SMEM_MAX); }
+// shared memory per SM given to the rings of its resident CTAs
+static size_t ring_budget() { return (size_t) 190 << 10; }
 
 template <int NC>
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NC * 32) : "memory"); }
@@ -33,18 +34,19 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // ================================================================================================
 // Q4_K. Stage: qs part [NC][16][128] then hdr part [NC][16][16].
 // ================================================================================================
-template <int NC, int EPI>
+template <int NC, int PREP, int EPI>
 __global__ void __launch_bounds__((NC + 1) * 32)
-q4k_matvec_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ hdr, int rows, int bpr, ActQ8K act,
+q4k_matvec_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ hdr, int rows, int bpr, MatvecIn in,
                        int cols, float* __restrict__ y, const float* __restrict__ resid, int nstages, int* __restrict__ timeout_flag) {
     constexpr int S_QS = NC * 16 * 128, S_HDR = NC * 16 * 16, S_BYTES = S_QS + S_HDR;
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: ring | q8 (swizzled) | split sub-block sums | d | barriers
+    // layout: ring | q8 (swizzled) | split sub-block sums | d | reduce scratch | barriers
     uint8_t* s_ring = smem;
     int8_t* s_q8 = (int8_t*) (s_ring + (size_t) nstages * S_BYTES);
     uint8_t* s_bs = (uint8_t*) (s_q8 + cols);                      // 16 bytes per block
     float* s_d = (float*) (s_bs + cols / 16);
-    uint64_t* full = (uint64_t*) ((uint8_t*) s_d + ((bpr * 4 + 15) & ~15));
+    float* s_red = (float*) ((uint8_t*) s_d + ((bpr * 4 + 15) & ~15));
+    uint64_t* full = (uint64_t*) (s_red + 8);
     uint64_t* empty = full + RG_MAX_STAGES;
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -87,21 +89,9 @@ q4k_matvec_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict
     }
 
     // ---------------- consumers ----------------
-    skd::pdl_wait();                                   // the quantized activation is the predecessor's output
-    {
-        const int t = threadIdx.x;                     // 0 .. NC*32-1
-        for (int c = t; c < (cols >> 4); c += NC * 32) {
-            const int blk = c >> 4, ch = c & 15;
-            *reinterpret_cast<uint4*>(s_q8 + (size_t) blk * 256 + (ch ^ (((blk >> 1) & 1) << 1)) * 16) = skd::ld_ro(act.q + (size_t) c * 16);
-        }
-        // sub-block sums as two int8 planes (sum = 128*hi + lo): per block [hi 0..3 | lo 0..3 | hi 4..7 | lo 4..7]
-        for (int c = t; c < (cols >> 5); c += NC * 32) {
-            const int sum = (int) __ldg(act.bsums + c), hi = (sum + 64) >> 7, lo = sum - (hi << 7);
-            int8_t* dst = (int8_t*) s_bs + (size_t) (c >> 3) * 16 + ((c >> 2) & 1) * 8 + (c & 3);
-            dst[0] = (int8_t) hi; dst[4] = (int8_t) lo;
-        }
-        for (int c = t; c < bpr; c += NC * 32) s_d[c] = __ldg(act.d + c);
-    }
+    skd::pdl_wait();                                   // the activation is the predecessor's output
+    // taken as already quantized, or quantized here (optionally RMS-normalised first) while the ring fills
+    q8k_prep_to_smem<PREP, NC, 1>(in, cols, bpr, s_q8, s_bs, s_d, s_red, warp, lane, threadIdx.x);
     consumer_sync<NC>();
 
     const int h = lane & 1, slot = lane >> 1, s1 = (slot >> 1) & 1;
@@ -178,9 +168,9 @@ q4k_matvec_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict
 // ================================================================================================
 constexpr int RG8_COLS = 2048;
 
-template <int NC, int EPI>
+template <int NC, int PREP, int EPI>
 __global__ void __launch_bounds__((NC + 1) * 32)
-q8_0_matvec_ring_kernel(const int8_t* __restrict__ codes, const __half* __restrict__ scales, int rows, int cols, ActSplit act,
+q8_0_matvec_ring_kernel(const int8_t* __restrict__ codes, const __half* __restrict__ scales, int rows, int cols, MatvecIn in,
                         float* __restrict__ y, const float* __restrict__ resid, int nstages, int* __restrict__ timeout_flag) {
     constexpr int S_CODES = NC * RG8_COLS, S_SC = NC * (RG8_COLS / 32) * 2, S_BYTES = S_CODES + S_SC;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -189,7 +179,8 @@ q8_0_matvec_ring_kernel(const int8_t* __restrict__ codes, const __half* __restri
     int8_t* s_hi = (int8_t*) (s_ring + (size_t) nstages * S_BYTES);
     int8_t* s_lo = s_hi + cols;
     float* s_dx = (float*) (s_lo + cols);
-    uint64_t* full = (uint64_t*) ((uint8_t*) s_dx + ((bpr * 4 + 15) & ~15));
+    float* s_red = (float*) ((uint8_t*) s_dx + ((bpr * 4 + 15) & ~15));
+    uint64_t* full = (uint64_t*) (s_red + 8);
     uint64_t* empty = full + RG_MAX_STAGES;
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -227,14 +218,7 @@ q8_0_matvec_ring_kernel(const int8_t* __restrict__ codes, const __half* __restri
     }
 
     skd::pdl_wait();
-    {
-        const int t = threadIdx.x;
-        for (int c = t; c < (cols >> 4); c += NC * 32) {
-            *reinterpret_cast<uint4*>(s_hi + (size_t) c * 16) = skd::ld_ro(act.hi + (size_t) c * 16);
-            *reinterpret_cast<uint4*>(s_lo + (size_t) c * 16) = skd::ld_ro(act.lo + (size_t) c * 16);
-        }
-        for (int c = t; c < bpr; c += NC * 32) s_dx[c] = __ldg(act.d + c);
-    }
+    split_prep_to_smem<PREP, NC, 1>(in, cols, bpr, s_hi, s_lo, s_dx, s_red, warp, lane, threadIdx.x);
     consumer_sync<NC>();
 
     uint4 ah[4], al[4];
@@ -284,7 +268,7 @@ q8_0_matvec_ring_kernel(const int8_t* __restrict__ codes, const __half* __restri
 }
 
 // ================================================================================================
-// dispatch (m = 1, activation already quantized). Returns 1 when the shape is outside what these take.
+// dispatch (m = 1). Returns 1 when the shape is outside what these take.
 // ================================================================================================
 struct RingPlan { int nc, cps, nstages; size_t smem; };
 
@@ -320,33 +304,43 @@ static int32_t set_smem_once(K kernel, bool* done) {
         return SKAINET_CUDA_OK;                                                                               \
     } while (0)
 
-template <int EPI>
-static int32_t launch_q4k_ring(const Weight& w, ActQ8K a, float* y, const float* resid, const RingPlan& plan, int* flag, cudaStream_t s) {
+template <int PREP, int EPI>
+static int32_t launch_q4k_ring(const Weight& w, const MatvecIn& in, float* y, const float* resid, const RingPlan& plan, int* flag, cudaStream_t s) {
     if (plan.nc == 4)
-        SK_RG_LAUNCH((q4k_matvec_ring_kernel<4, EPI>), 4, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr, a, w.cols, y, resid, plan.nstages, flag);
-    SK_RG_LAUNCH((q4k_matvec_ring_kernel<8, EPI>), 8, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr, a, w.cols, y, resid, plan.nstages, flag);
+        SK_RG_LAUNCH((q4k_matvec_ring_kernel<4, PREP, EPI>), 4, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr, in, w.cols, y, resid, plan.nstages, flag);
+    SK_RG_LAUNCH((q4k_matvec_ring_kernel<8, PREP, EPI>), 8, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr, in, w.cols, y, resid, plan.nstages, flag);
 }
-template <int EPI>
-static int32_t launch_q8_ring(const Weight& w, ActSplit a, float* y, const float* resid, const RingPlan& plan, int* flag, cudaStream_t s) {
+template <int PREP, int EPI>
+static int32_t launch_q8_ring(const Weight& w, const MatvecIn& in, float* y, const float* resid, const RingPlan& plan, int* flag, cudaStream_t s) {
     if (plan.nc == 4)
-        SK_RG_LAUNCH((q8_0_matvec_ring_kernel<4, EPI>), 4, (const int8_t*) w.qs, (const __half*) w.hdr, w.rows, w.cols, a, y, resid, plan.nstages, flag);
-    SK_RG_LAUNCH((q8_0_matvec_ring_kernel<8, EPI>), 8, (const int8_t*) w.qs, (const __half*) w.hdr, w.rows, w.cols, a, y, resid, plan.nstages, flag);
+        SK_RG_LAUNCH((q8_0_matvec_ring_kernel<4, PREP, EPI>), 4, (const int8_t*) w.qs, (const __half*) w.hdr, w.rows, w.cols, in, y, resid, plan.nstages, flag);
+    SK_RG_LAUNCH((q8_0_matvec_ring_kernel<8, PREP, EPI>), 8, (const int8_t*) w.qs, (const __half*) w.hdr, w.rows, w.cols, in, y, resid, plan.nstages, flag);
 }
 
-int32_t launch_matvec_ring(const Weight& w, const MatvecIn& in, float* y, const float* resid, cudaStream_t s) {
+#define SK_RG_PE(FN)                                                                                              \
+    switch (prep * 2 + (resid ? EPI_ADD : EPI_STORE)) {                                                           \
+        case PREP_QUANTIZED * 2 + EPI_STORE: return FN<PREP_QUANTIZED, EPI_STORE>(w, in, y, resid, plan, flag, s); \
+        case PREP_QUANTIZED * 2 + EPI_ADD:   return FN<PREP_QUANTIZED, EPI_ADD>(w, in, y, resid, plan, flag, s);   \
+        case PREP_F32 * 2 + EPI_STORE:       return FN<PREP_F32, EPI_STORE>(w, in, y, resid, plan, flag, s);       \
+        case PREP_F32 * 2 + EPI_ADD:         return FN<PREP_F32, EPI_ADD>(w, in, y, resid, plan, flag, s);         \
+        case PREP_NORM_F32 * 2 + EPI_STORE:  return FN<PREP_NORM_F32, EPI_STORE>(w, in, y, resid, plan, flag, s);  \
+        default:                             return FN<PREP_NORM_F32, EPI_ADD>(w, in, y, resid, plan, flag, s);    \
+    }
+
+int32_t launch_matvec_ring(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s) {
     int* flag = device_timeout_flag();
     if (w.rows <= 0) return 1;
     RingPlan plan;
     if (w.enc == SKAINET_ENC_Q4_K) {
-        const size_t fixed = (size_t) w.cols + w.cols / 16 + ((w.bpr * 4 + 15) & ~15) + 2 * RG_MAX_STAGES * 8;
+        const size_t fixed = (size_t) w.cols + w.cols / 16 + ((w.bpr * 4 + 15) & ~15) + 32 + 2 * RG_MAX_STAGES * 8;
         if (!plan_ring(fixed, 16 * 144, &plan)) return 1;
-        return resid ? launch_q4k_ring<EPI_ADD>(w, in.q8, y, resid, plan, flag, s) : launch_q4k_ring<EPI_STORE>(w, in.q8, y, resid, plan, flag, s);
+        SK_RG_PE(launch_q4k_ring)
     }
     if (w.enc == SKAINET_ENC_Q8_0) {
         if (w.cols % 256 != 0) return 1;
-        const size_t fixed = (size_t) 2 * w.cols + ((w.bpr * 4 + 15) & ~15) + 2 * RG_MAX_STAGES * 8;
+        const size_t fixed = (size_t) 2 * w.cols + ((w.bpr * 4 + 15) & ~15) + 32 + 2 * RG_MAX_STAGES * 8;
         if (!plan_ring(fixed, RG8_COLS + RG8_COLS / 16, &plan)) return 1;
-        return resid ? launch_q8_ring<EPI_ADD>(w, in.split, y, resid, plan, flag, s) : launch_q8_ring<EPI_STORE>(w, in.split, y, resid, plan, flag, s);
+        SK_RG_PE(launch_q8_ring)
     }
     return 1;
 }

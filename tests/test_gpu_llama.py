@@ -197,6 +197,30 @@ def test_runtime_argument_errors(gpu):
     m.free()
 
 
+def test_decode_reports_a_bounded_wait_that_ran_out(gpu, cuda_lib):
+    """No fault involved: the self-test kernel waits on a barrier nothing completes, gives up and raises the device
+    flag. The next synchronising runtime call must report SKAINET_CUDA_ERR_TIMEOUT instead of returning tokens as if
+    nothing had happened, clear the condition, and work again afterwards."""
+    import ctypes as C
+    from skainet_b200.llama import Llama, LlamaConfig
+    from skainet_b200._lib import SkainetCudaError, ERR_TIMEOUT
+    m = Llama(LlamaConfig(1, 256, 4, 2, 64, 512, 300, max_seq=32))
+    m.synth(); m.finalize()
+    tin, tout = np.array([5], np.int32), np.zeros(1, np.int32)
+    m.decode(tin, tout)
+    good = int(tout[0])
+    outcome = C.c_int32(0)
+    assert cuda_lib.skainet_cuda_selftest_bounded_wait(C.byref(outcome)) == 0 and outcome.value == 2
+    with pytest.raises(SkainetCudaError) as e:
+        m.decode(tin, tout)
+    assert e.value.status == ERR_TIMEOUT and "bounded wait" in str(e.value)
+    assert cuda_lib.skainet_cuda_device_status() == 0          # the call cleared the condition
+    m.reset()
+    m.decode(tin, tout)
+    assert int(tout[0]) == good
+    m.free()
+
+
 def test_prefill_and_decode_are_bit_repeatable(gpu):
     """Three runs of the same request (a 300-token prompt through the tcgen05 / mma.sync tile kernels and the
     tensor-core prefill attention, then 48 greedy tokens through the ring matvecs and split-K attention) give identical
