@@ -257,7 +257,8 @@ def run_reference(args) -> None:
     line = {"impl": "reference", "metric": metric, "value": v, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": float(np.mean(times)), "higher_is_better": True,
             "scaling": "weak" if args.workload in MATVEC_WORKLOADS else "strong", "vs_baseline": None, "dtype": dtype_of(args.workload),
-            "data": "synthetic", "config": workload_config(args, 1),
+            "data": "synthetic", "config": workload_config(args, 1, {"weights": "random valid packed blocks on the host (the integer kernels' time does not depend on the values)",
+                                                                     "context_fill": "random f16-rounded K/V on the host" }),
             "cpu_baseline": {"value": v, "unit": unit, "cores": r["cores"], "kind": r["kind"], "sample": r["sample"]},
             "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -364,6 +365,31 @@ def matvec_sweep_rate(torch, device, L, weights_flat, stream, steps: int, warmup
         e1.record(stream)
         stream.synchronize()
     return e0.elapsed_time(e1) / steps, 2 * len(weights_flat), graph, (xs, ys)
+
+
+def matvec_configs_summary(torch, device, L, steps: int = 10) -> dict:
+    """Benchmark configs 1 (Q8_0 4096x4096) and 2 (Q4_K 11008x4096 + 4096x11008) at M = 1, measured in the same process as the
+    decode line: algorithmic GB/s of the quantizer + matvec pair over a rotation of distinct weights larger than 2x L2, the
+    fraction of the measured copy bandwidth, and the time a kernel that only reads the same bytes takes."""
+    info = device.device_info()
+    peak, _ = load_peaks()
+    out = {}
+    stream = torch.cuda.Stream()
+    for name, key in (("q8_0_matvec", "config1_q8_0_4096x4096"), ("q4k_matvec", "config2_q4k_11008x4096_4096x11008")):
+        enc, shapes, bb, be = MATVEC_WORKLOADS[name]
+        copies = max(2, int(np.ceil(2.2 * info["l2_bytes"] / min(r * (c // be) * bb for r, c in shapes))))
+        ws = [device.Weight.synth(enc, r, c, seed=50 + 10 * si + ci, std=0.02) for ci in range(copies) for si, (r, c) in enumerate(shapes)]
+        nbytes = sum(algorithmic_bytes(bb, be, w.rows, w.cols) for w in ws)
+        ms, _, graph, keep = matvec_sweep_rate(torch, device, L, ws, stream, steps, 3)
+        floor = read_floor_ms(torch, L, ws, stream, steps)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[key] = {"gbs": gbs, "frac": gbs / peak, "avg_launch_us": ms * 1e3 / len(ws), "read_floor_us": floor * 1e3 / len(ws),
+                    "weights": len(ws), "launches_per_matvec": 2}
+        del graph, keep
+        for w in ws:
+            w.free()
+    out["note"] = "M = 1; each matvec = activation quantizer launch + streaming matvec launch, one CUDA graph per sweep; frac of the measured copy bandwidth"
+    return out
 
 
 def run_matvec(args) -> None:
@@ -691,6 +717,58 @@ def run_attn(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def tp_parity_check(torch, dist, m, cfg, model_name: str, ctx: int, batch: int, rank: int, world: int, n_steps: int = 4) -> dict:
+    """Correctness of the tensor-parallel run against the single-GPU model, inside the bench: rank 0 also builds the
+    unsharded model of the same seed (it fits beside its shard), both decode the same seeded context with the same
+    teacher tokens for a few steps, and the logits are compared. Logits agree to fp32 summation order unless an int8
+    activation code flips somewhere in the stack (one flip moves the outputs by ~3e-3 of their RMS): the bar of the
+    2-GPU parity test (2e-3) is reported as `within_bar`; only a gross error (> 5e-2: a wrong shard) fails the run."""
+    from skainet_b200.llama import Llama
+    ref = None
+    if rank == 0:
+        ref = Llama(model_config(model_name, max_seq=cfg.max_seq, max_batch=batch, tp_rank=0, tp_world=1))
+        ref.synth(seed=100, std=0.02)
+        ref.finalize()
+        for b in range(batch):
+            ref.fake_prefill(ctx, seq=b, seed=7 + b)
+    m.reset()
+    for b in range(batch):
+        m.fake_prefill(ctx, seq=b, seed=7 + b)
+    tok = torch.from_numpy((np.arange(1, batch + 1, dtype=np.int32) * 17 % cfg.vocab).astype(np.int32)).cuda()
+    errs, equal, margins = [], True, []
+    tin, tout = np.zeros(batch, np.int32), np.zeros(batch, np.int32)
+    for _ in range(n_steps):
+        tin[:] = tok.cpu().numpy()
+        m.decode(tin, tout)
+        lg_tp = m.logits(batch)                            # all ranks take part in the gather
+        if rank == 0:
+            rtin, rtout = tin.copy(), np.zeros(batch, np.int32)
+            ref.decode(rtin, rtout)
+            lg = ref.logits(batch)
+            rms = float(np.sqrt(np.mean(lg.astype(np.float64) ** 2)))
+            errs.append(float(np.abs(lg_tp.astype(np.float64) - lg).max() / rms))
+            srt = np.sort(lg, axis=1)
+            margins.append(float(((srt[:, -1] - srt[:, -2]) / rms).min()))
+            equal = equal and bool(np.array_equal(tout, rtout))
+            tok = torch.from_numpy(rtout.copy()).cuda()
+        dist.broadcast(tok, src=0)                         # teacher tokens: the single-GPU model's greedy choice
+    out = None
+    if rank == 0:
+        ref.free()
+        worst = max(errs)
+        out = {"steps": n_steps, "max_rel_logit_err": worst, "tokens_equal": equal, "min_top2_margin": min(margins), "bar": 2e-3,
+               "within_bar": worst <= 2e-3, "reference": "the unsharded model of the same seed on rank 0, same seeded context, teacher-forced"}
+    flag = torch.tensor([1 if (rank != 0 or max(errs) <= 5e-2) else 0], device="cuda", dtype=torch.int32)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if int(flag[0]) != 1:
+        raise SystemExit(f"tensor-parallel logits differ grossly from the single-GPU model: {out}")
+    # back to the state the timed region starts from
+    m.reset()
+    for b in range(batch):
+        m.fake_prefill(ctx, seq=b, seed=7 + b)
+    return out
+
+
 def run_decode(args) -> None:
     import torch
     import torch.distributed as dist
@@ -724,23 +802,34 @@ def run_decode(args) -> None:
     barrier()                                             # ranks start their first step together (peer waits are bounded)
     m.generate(first, warm)
     bytes_step, launches_step = m.step_cost(batch)
+    tp_parity = tp_parity_check(torch, dist, m, cfg, model_name, ctx, batch, rank, world) if world > 1 else None
     sampler = ClockSampler(local)
     barrier()
     if rank == 0:
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(mstream)
-    toks = m.generate(first, args.steps)                 # K graph replays, synchronises at the end
-    e1.record(mstream)
-    barrier()
-    ms = e0.elapsed_time(e1)
-    if not args.skip_cpu:                                # keep the GPUs loaded long enough for the clock sampler;
-        tm = torch.tensor([ms], device="cuda", dtype=torch.float64)   # every rank takes the same number of extra steps
-        if world > 1:
-            dist.all_reduce(tm, op=dist.ReduceOp.MAX)
-        if float(tm[0]) < 1500:
-            m.generate(first, min(1024, int(1500 / max(float(tm[0]) / args.steps, 1e-3))))
+
+    def block():                                          # EXACTLY `steps` decode steps, device-timed on the model's stream
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(mstream)
+        t = m.generate(first, args.steps)                 # K graph replays, synchronises at the end
+        e1.record(mstream)
+        barrier()
+        return e0.elapsed_time(e1), t
+
+    # The block is repeated until about a second has been timed (a single block of 20 steps is 0.1-0.2 s, too short to
+    # be stable); every rank runs the same number of blocks, and the median block is reported.
+    ms0, toks = block()
+    tm = torch.tensor([ms0], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+    room = max(0, (cfg.max_seq - ctx - warm - 200) // max(1, args.steps) - 1)       # decode positions left in the cache
+    extra = int(min(15, room, max(0, np.ceil(1000.0 / max(float(tm[0]), 1e-3)) - 1)))
+    block_ms = [ms0] + [block()[0] for _ in range(extra)]
+    ms = float(np.median(block_ms))
     clocks = sampler.stop() if rank == 0 else None
+    logits_ok = bool(np.isfinite(m.logits(batch)).all())
+    tokens_ok = bool(((toks >= 0) & (toks < cfg.vocab)).all())
 
     # end to end: one C-ABI call per step, token ids from pinned host memory and back
     e2e_steps = 0 if args.skip_e2e else max(1, min(args.steps, 64))
@@ -770,25 +859,45 @@ def run_decode(args) -> None:
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms, mv_ms = float(t[0]), float(t[1]), float(t[2])
+    # a run in which a bounded device wait gave up, or whose outputs are not numbers, must not print a number
+    status = L.lib().skainet_cuda_device_status()
+    ok = torch.tensor([1 if (status == 0 and logits_ok and tokens_ok) else 0], device="cuda", dtype=torch.int32)
+    if world > 1:
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if int(ok[0]) != 1:
+        raise SystemExit(f"rank {rank}: device status {status} ({L.last_error() if status else 'ok'}), logits finite {logits_ok}, tokens in range {tokens_ok}")
+    matvec_summary = matvec_configs_summary(torch, device, L) if (world == 1 and not args.skip_cpu) else None
     if rank == 0:
         peak, peak_kind = load_peaks()
         achieved = mv_bytes / (mv_ms * 1e-3) / 1e9
         step_gbs = bytes_step / (ms / args.steps * 1e-3) / 1e9
+        # the bytes one launch of the dominant kernel must move (its own weight), and the DRAM bytes ncu counted for it
+        launch_bytes = mv_bytes / len(ws)
         line = {
             "metric": "decode_tokens_per_s", "value": batch * args.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": dtype_of(args.workload), "data": "synthetic", "config": workload_config(args, world),
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": mv_bytes / len(ws) * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE,
-                         "traffic_source": "ncu dram bytes per launch of q4k_matvec_ring_kernel captures, scaled by weight bytes",
-                         "peak_kind": peak_kind, "kernel": "q4k_matvec_ring_kernel", "avg_launch_us": mv_ms * 1e3 / len(ws),
-                         "note": "per GPU: the fused matvec path (quantizer + matvec) swept over this rank's own weights, bytes / time",
-                         "step_bytes_per_gpu": bytes_step, "step_gbs_per_gpu": step_gbs, "step_frac": step_gbs / peak},
+            "roofline": {"bound": "hbm", "achieved": step_gbs, "peak": peak, "unit": "GB/s", "frac": step_gbs / peak,
+                         "traffic": launch_bytes * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE,
+                         "traffic_source": "dram read+write bytes of one q4k_matvec_ring_kernel launch from the ncu captures summarised in "
+                                           "profiles/ (1.001 x the weight bytes at 25 MB and at 264 MB), scaled to this run's mean weight size",
+                         "peak_kind": peak_kind, "kernel": "q4k_matvec_ring_kernel",
+                         "note": "per GPU. achieved / frac: bytes one decode step must read (weights once + visible K/V) / measured step time. "
+                                 "kernel_*: the matvec path alone (quantizer + matvec) swept over this rank's own weights in a CUDA graph",
+                         "step_bytes_per_gpu": bytes_step, "kernel_achieved": achieved, "kernel_frac": achieved / peak,
+                         "kernel_avg_launch_us": mv_ms * 1e3 / len(ws)},
+            "timing": {"blocks": len(block_ms), "block_ms_min": float(min(block_ms)), "block_ms_median": ms, "block_ms_max": float(max(block_ms)),
+                       "note": "each block = exactly `steps` steps between barriers, CUDA events on the model's stream; the median block is reported"},
             "e2e": {"value": (batch * e2e_steps / (e2e_ms * 1e-3)) if e2e_steps else None, "unit": "tokens/s",
                     "h2d_bytes_per_step": 4 * batch, "d2h_bytes_per_step": 4 * batch,
                     "note": "one skainet_cuda_llama_decode call per step: pinned host token ids in, arg-max ids out, host sync each step"},
             "gpu_launches": launches_step * args.steps, "clocks": clocks, "tokens_head": [int(x) for x in toks[:4, 0]],
+            "checks": {"device_status": 0, "logits_finite": True, "tokens_in_vocab": True},
         }
+        if tp_parity is not None:
+            line["tp_parity"] = tp_parity
+        if matvec_summary is not None:
+            line["matvec"] = matvec_summary
         if world == 1 and not args.skip_cpu:
             cpu = cpu_decode_rate(model_name, ctx, 20.0)
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}

@@ -68,6 +68,7 @@ extern "C" {
 #define SKAINET_ACT_F32    1
 
 typedef int64_t skainet_weight_t;   /* opaque handle of a device-resident packed weight */
+typedef int64_t skainet_kv_t;       /* opaque handle of a device-resident KV-cache store    */
 typedef void*   skainet_stream_t;   /* a cudaStream_t, or NULL for the default stream   */
 
 /* ---- library / device ------------------------------------------------------------------------ */
@@ -198,6 +199,25 @@ SKAINET_CUDA_API int32_t skainet_cuda_matmul_dev(skainet_weight_t w, const float
 SKAINET_CUDA_API int32_t skainet_cuda_matvec_fused_dev(skainet_weight_t w, const float* x_dev, const float* gamma_dev,
     float eps, const float* resid_dev, float* y_dev, skainet_stream_t stream);
 
+/* Graph-level fused ops (skainet-compile/skainet-compile-opt/src/commonMain/kotlin/sk/ainet/compile/opt/passes/LLMFusionPass.kt:17-23):
+ * the entries a CUDA FusedOpHandler calls in place of the CPU decompositions of
+ * skainet-compile/skainet-compile-dag/src/commonMain/kotlin/sk/ainet/lang/graph/exec/LLMFusedOpHandlers.kt. Both take an optional
+ * RMSNorm in front (gamma_dev != NULL: the fused_rms_norm node that feeds them, LLMFusedOpHandlers.kt:44-68), so a decoder
+ * block is norm+qkv and norm+ffn. Q4_K / Q8_0 weights; m activation rows. */
+/* Rows of a, then b, then c (0 = none) as one new resident weight: what a handler does once when it first sees the three
+ * projections of a fused_qkv_proj node (LLMFusedOpHandlers.kt:143-196 "concatenate the weight matrices and do a single
+ * matmul + split") or gate and up of a fused_swiglu_ffn node. The parts stay valid and owned by the caller. */
+SKAINET_CUDA_API int32_t skainet_cuda_weight_concat_rows(skainet_weight_t a, skainet_weight_t b, skainet_weight_t c, skainet_weight_t* out);
+/* fused_qkv_proj (LLMFusionPass.kt:117, LLMFusedOpHandlers.kt:143-196): q[m, q_rows], k[m, k_rows], v[m, v_rows] = x[m, cols] . W^T
+ * for the merged weight's three row ranges, one pass over the activation. */
+SKAINET_CUDA_API int32_t skainet_cuda_fused_qkv_proj_dev(skainet_weight_t w_qkv, int32_t q_rows, int32_t k_rows, int32_t v_rows,
+    const float* x_dev, const float* gamma_dev, float eps, int32_t m, float* q_dev, float* k_dev, float* v_dev, skainet_stream_t stream);
+/* fused_swiglu_ffn (LLMFusionPass.kt:86, LLMFusedOpHandlers.kt:86-127): out[m, d] = (resid +) W_down . (silu(W_gate x) * (W_up x)),
+ * gate and up as one merged weight (gate rows first); the intermediate never leaves the device and is quantized for the
+ * down projection inside the SwiGLU kernel. resid_dev may be NULL or equal out_dev. */
+SKAINET_CUDA_API int32_t skainet_cuda_fused_swiglu_ffn_dev(skainet_weight_t w_gate_up, skainet_weight_t w_down, const float* x_dev,
+    const float* gamma_dev, float eps, int32_t m, const float* resid_dev, float* out_dev, skainet_stream_t stream);
+
 /* Measurement aid with no counterpart in the reference: reads every byte of a resident weight once
  * with plain vector loads and computes nothing. The bench times it over the same weights as the matvec
  * to report the floor a launch of that many bytes can reach on this GPU. */
@@ -256,6 +276,43 @@ SKAINET_CUDA_API int32_t skainet_cuda_attn_decode_noalloc_dev(const float* q, co
     const int32_t* kv_len_dev, int32_t max_kv_len, float scale, int32_t window, skainet_stream_t stream);
 /* fp32 [n] -> binary16 [n], round to nearest even (filling the cache from host-prepared K/V). */
 SKAINET_CUDA_API int32_t skainet_cuda_f32_to_f16_dev(const float* in, uint16_t* out, int64_t n, skainet_stream_t stream);
+
+/* ---- 3. KV-cache store resident in HBM -------------------------------------------------------- */
+/* The device counterpart of the reference's KvCacheStore
+ * (skainet-lang/skainet-lang-core/src/commonMain/kotlin/sk/ainet/lang/tensor/storage/KvCacheStore.kt:125-157) as
+ * DefaultKvCacheStore implements it (DefaultKvCacheStore.kt:76-131,170-177,235-263): one sequence, per layer keys and
+ * values [heads, max_seq, head_dim], here in binary16 (the store's configurable element type, KvCacheStore.kt:58-74;
+ * reads convert back exactly). Positions are absolute. sliding_window != 0 makes the buffer a ring that keeps the
+ * newest max_seq positions (appending past max_seq overwrites the oldest); otherwise a full cache refuses the append.
+ * The sequence length advances when the last layer has been appended. head_dim 64 or 128. */
+SKAINET_CUDA_API int32_t skainet_cuda_kv_create(int32_t n_layers, int32_t n_heads, int32_t head_dim, int32_t max_seq,
+    int32_t sliding_window, skainet_kv_t* out);
+SKAINET_CUDA_API int32_t skainet_cuda_kv_free(skainet_kv_t kv);
+/* appendToken(layer, key, value): key / value are [heads, head_dim] fp32; host pointers, or device pointers with a stream.
+ * A full non-ring cache -> SKAINET_CUDA_ERR_INVALID ("KV cache is full", IllegalStateException in the reference). */
+SKAINET_CUDA_API int32_t skainet_cuda_kv_append(skainet_kv_t kv, int32_t layer, const float* key_host, const float* value_host);
+SKAINET_CUDA_API int32_t skainet_cuda_kv_append_dev(skainet_kv_t kv, int32_t layer, const float* key_dev, const float* value_dev,
+    skainet_stream_t stream);
+/* readKeys / readValues (which = 0 / 1): positions [start_pos, end_pos) as fp32 [heads, end_pos - start_pos, head_dim] on the
+ * host, oldest first also when the range crosses the end of the ring. start_pos before the oldest held position or end_pos
+ * beyond the sequence -> SKAINET_CUDA_ERR_INVALID. */
+SKAINET_CUDA_API int32_t skainet_cuda_kv_read(skainet_kv_t kv, int32_t layer, int32_t which, int32_t start_pos, int32_t end_pos,
+    float* host_out);
+/* evict(fromPos): the sequence length becomes from_pos (truncation, speculative-decoding rollback). On a cache that has not
+ * wrapped the evicted slots are zeroed like the reference does; positions a wrapped ring had already overwritten stay
+ * unavailable afterwards (reads and windows before them are refused). */
+SKAINET_CUDA_API int32_t skainet_cuda_kv_evict(skainet_kv_t kv, int32_t from_pos);
+SKAINET_CUDA_API int32_t skainet_cuda_kv_clear(skainet_kv_t kv);
+/* out8 = {currentSeqLen, windowStart, maxSeqLen, layers, heads, head_dim, ring (0/1), physical bytes of keys + values}. */
+SKAINET_CUDA_API int32_t skainet_cuda_kv_info(skainet_kv_t kv, int64_t* out8);
+/* One decode step of attention over positions [from_pos, to_pos) of a layer: out[h] = softmax(q[h] . K^T * scale) V for
+ * q_heads query heads (a multiple 1, 2, 4 or 8 of the cache's heads; query head h reads cache head h / group), q / out
+ * device fp32 [q_heads, head_dim]; scale 0 means 1/sqrt(head_dim). The window is read in place, as the one or two runs it
+ * occupies in the ring: the device form of WindowedAttention.decodeStep over keyWindow / valueWindow
+ * (skainet-lang/skainet-lang-core/src/commonMain/kotlin/sk/ainet/lang/memory/WindowedAttention.kt:32-80). to_pos may be
+ * currentSeqLen + 1 while a token's layers are being appended (the sequence length advances only with the last layer). */
+SKAINET_CUDA_API int32_t skainet_cuda_kv_attn_decode_dev(skainet_kv_t kv, int32_t layer, const float* q_dev, float* out_dev,
+    int32_t q_heads, int32_t from_pos, int32_t to_pos, float scale, skainet_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -76,6 +76,18 @@ SIGNATURES = {
     "skainet_cuda_attn_decode_dev": [vp, vp, vp, vp, i32, i32, i32, i32, i64, vp, i32, f32, i32, vp],
     "skainet_cuda_attn_decode_noalloc_dev": [vp, vp, vp, vp, i32, i32, i32, i32, i64, vp, i32, f32, i32, vp],
     "skainet_cuda_f32_to_f16_dev": [vp, vp, i64, vp],
+    "skainet_cuda_weight_concat_rows": [i64, i64, i64, i64p],
+    "skainet_cuda_fused_qkv_proj_dev": [i64, i32, i32, i32, vp, vp, f32, i32, vp, vp, vp, vp],
+    "skainet_cuda_fused_swiglu_ffn_dev": [i64, i64, vp, vp, f32, i32, vp, vp, vp],
+    "skainet_cuda_kv_create": [i32, i32, i32, i32, i32, i64p],
+    "skainet_cuda_kv_free": [i64],
+    "skainet_cuda_kv_append": [i64, i32, f32p, f32p],
+    "skainet_cuda_kv_append_dev": [i64, i32, vp, vp, vp],
+    "skainet_cuda_kv_read": [i64, i32, i32, i32, i32, f32p],
+    "skainet_cuda_kv_evict": [i64, i32],
+    "skainet_cuda_kv_clear": [i64],
+    "skainet_cuda_kv_info": [i64, i64p],
+    "skainet_cuda_kv_attn_decode_dev": [i64, i32, vp, vp, i32, i32, i32, f32, vp],
     # include/skainet_cuda_llama.h
     "skainet_cuda_llama_create": [vp, i64p],
     "skainet_cuda_llama_free": [i64],

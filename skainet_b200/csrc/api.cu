@@ -111,9 +111,44 @@ int* device_timeout_flag() {
     return g_timeout_flag[dev];
 }
 
+// {next, done} counter pairs for kernels that hand out their work items dynamically: one block of pairs per
+// (device, stream), rotated over consecutive launches so that a launch overlapping its successor (programmatic
+// dependent launch) never shares a pair with it. A kernel leaves its pair zeroed when its last CTA finishes.
+// Returns nullptr (the kernel then schedules statically) when the block would have to be allocated while the
+// stream is being captured.
+constexpr int SCHED_PAIRS = 16;
+struct SchedBlock { int* p = nullptr; unsigned seq = 0; };
+static std::map<std::pair<int, cudaStream_t>, SchedBlock> g_sched;
+int* stream_sched_pair(cudaStream_t stream) {
+    const int dev = current_device();
+    std::lock_guard<std::mutex> lk(g_mu);
+    SchedBlock& b = g_sched[{dev, stream}];
+    if (!b.p) {
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) { cudaGetLastError(); return nullptr; }
+        if (cudaMalloc(&b.p, 2 * SCHED_PAIRS * sizeof(int)) != cudaSuccess) { cudaGetLastError(); b.p = nullptr; return nullptr; }
+        cudaMemset(b.p, 0, 2 * SCHED_PAIRS * sizeof(int));
+    }
+    return b.p + 2 * (int) (b.seq++ % SCHED_PAIRS);
+}
+// A kernel that gave up a bounded wait may leave its pair non-zero: zero every block of the device.
+static void sched_reset_all(int dev) {
+    for (auto& kv : g_sched)
+        if (kv.first.first == dev && kv.second.p) cudaMemset(kv.second.p, 0, 2 * SCHED_PAIRS * sizeof(int));
+}
+void stream_sched_release(cudaStream_t stream) {
+    const int dev = current_device();
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_sched.find({dev, stream});
+    if (it == g_sched.end()) return;
+    if (it->second.p) cudaFree(it->second.p);
+    g_sched.erase(it);
+}
+
 // Turns a raised flag value into the status and message the entry points return.
 int32_t timeout_status(int value) {
     if (value == 0) return SKAINET_CUDA_OK;
+    { std::lock_guard<std::mutex> lk(g_mu); sched_reset_all(current_device()); }
     if (value == 2) set_error("a kernel's bounded wait on a tensor-parallel peer ran out (a rank is late or gone); the step's outputs are not valid");
     else set_error("a kernel's bounded wait on an asynchronous copy or tensor-core barrier ran out; its outputs are not valid");
     return SKAINET_CUDA_ERR_TIMEOUT;
@@ -327,6 +362,7 @@ int32_t skainet_cuda_stream_destroy(skainet_stream_t stream) {
     if (stream) {
         SK_CUDA(cudaStreamSynchronize(as_stream(stream)));
         scratch_release(as_stream(stream));          // the stream's scratch goes with it
+        stream_sched_release(as_stream(stream));
         SK_CUDA(cudaStreamDestroy(as_stream(stream)));
     }
     return SKAINET_CUDA_OK;
@@ -456,17 +492,19 @@ int32_t skainet_cuda_matmul_dev(skainet_weight_t h, const float* x_dev, int32_t 
     SK_TRY(ensure_device());
     cudaStream_t s = as_stream(stream);
     if (w->cols == 0) { SK_CUDA(cudaMemsetAsync(y_dev, 0, sizeof(float) * (size_t) m * w->rows, s)); return SKAINET_CUDA_OK; }
-    // One activation row in the native mode: a single launch that quantizes the row in its own prologue while
-    // its first weight tiles are already in flight (one-tile kernel, or the ring kernel for large weights).
-    if (m == 1 && act_mode == SKAINET_ACT_NATIVE && (w->enc == SKAINET_ENC_Q4_K || w->enc == SKAINET_ENC_Q8_0)) {
-        MatvecIn in; in.x = x_dev;
-        const int32_t st = launch_matvec_fused(*w, in, PREP_F32, y_dev, nullptr, s);
-        if (st != 1) return st;
-    }
     void* scratch = nullptr;
     const size_t need = act_scratch_bytes(w->enc, act_mode, m, w->cols);
     if (need) SK_TRY(scratch_get(s, SCRATCH_ACT, need, &scratch));
     SK_TRY(launch_act_quant(w->enc, act_mode, x_dev, m, w->cols, scratch, s));
+    // One activation row: quantizer launch, then the streaming matvec over the quantized row (one-tile kernel, or the
+    // ring kernel for large weights). Quantizing in every CTA's prologue instead measured slower at these widths
+    // (config 2: 9.9 against 9.0 us per matvec): each CTA would pull the fp32 row out of L2 again.
+    if (m == 1 && act_mode == SKAINET_ACT_NATIVE && (w->enc == SKAINET_ENC_Q4_K || w->enc == SKAINET_ENC_Q8_0)) {
+        MatvecIn in;
+        if (w->enc == SKAINET_ENC_Q8_0) in.split = act_split_layout(scratch, 1, w->cols); else in.q8 = act_q8k_layout(scratch, 1, w->cols);
+        const int32_t st = launch_matvec_fused(*w, in, PREP_QUANTIZED, y_dev, nullptr, s);
+        if (st != 1) return st;
+    }
     return launch_matvec(*w, x_dev, scratch, m, y_dev, act_mode, s);
 }
 

@@ -120,7 +120,8 @@ template <int D>
 __global__ void __launch_bounds__(AM_WARPS * 32)
 attn_decode_mma_kernel(const float* __restrict__ q, int64_t q_row_stride, const __half* __restrict__ kc, const __half* __restrict__ vc,
                        float* __restrict__ part, int heads, int kv_heads, int G, int64_t cache_stride,
-                       const int32_t* __restrict__ kv_len, float scale, int window, int chunk, int splits, float* __restrict__ out_direct) {
+                       const int32_t* __restrict__ kv_len, float scale, int window, int chunk, int splits, float* __restrict__ out_direct,
+                       int max_len, int ring_start, int ring_cap) {
     constexpr int S4 = D / 32;     // chunks of a K row per lane
     constexpr int KS = D / 16;     // k-steps of the score contraction
     constexpr int U = D / 64;      // chunks of a V row per lane
@@ -133,7 +134,7 @@ attn_decode_mma_kernel(const float* __restrict__ q, int64_t q_row_stride, const 
 
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    const int len = __ldg(kv_len + b);
+    const int len = min(__ldg(kv_len + b), max_len);      // never past what the launch was sized (and the cache allocated) for
     int first = 0;
     if (window > 0 && len - window > first) first = len - window;
     const int begin = max(first, split * chunk), stop = min(len, (split + 1) * chunk);
@@ -141,6 +142,14 @@ attn_decode_mma_kernel(const float* __restrict__ q, int64_t q_row_stride, const 
     const __half* kb = kc + ((int64_t) b * kv_heads + kvh) * cache_stride * D;
     const __half* vb = vc + ((int64_t) b * kv_heads + kvh) * cache_stride * D;
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
+    // Key i of the visible run sits in cache slot i, or, when the cache is a ring of ring_cap slots whose oldest
+    // visible key is in slot ring_start, in slot (ring_start + i) mod ring_cap: a wrapped window is read as the two
+    // runs it occupies, in place. The softmax is a sum over keys, so the slot order needs no gather.
+    auto slot_of = [&](int key) -> int64_t {
+        int sl = key + ring_start;
+        if (ring_cap > 0 && sl >= ring_cap) sl -= ring_cap;
+        return (int64_t) sl;
+    };
 
     // loads of a 16-key tile: K as (key g | g+8, chunks t+4s), V as (keys 2t,2t+1,2t+8,2t+9, chunks g+8u).
     // Two tiles (A, B) are kept in flight per warp: with one CTA of eight warps per SM that is 128 KB of
@@ -151,13 +160,13 @@ attn_decode_mma_kernel(const float* __restrict__ q, int64_t q_row_stride, const 
         for (int nt = 0; nt < 2; ++nt) {
             const int key = k0 + 8 * nt + g;
 #pragma unroll
-            for (int s = 0; s < S4; ++s) kr[nt][s] = key < stop ? skd::ld_stream(kb + (int64_t) key * D + (t + 4 * s) * 8) : zero4;
+            for (int s = 0; s < S4; ++s) kr[nt][s] = key < stop ? skd::ld_stream(kb + slot_of(key) * D + (t + 4 * s) * 8) : zero4;
         }
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
             const int key = k0 + 2 * t + (kk & 1) + 8 * (kk >> 1);
 #pragma unroll
-            for (int u = 0; u < U; ++u) vr[kk][u] = key < stop ? skd::ld_stream(vb + (int64_t) key * D + (g + 8 * u) * 8) : zero4;
+            for (int u = 0; u < U; ++u) vr[kk][u] = key < stop ? skd::ld_stream(vb + slot_of(key) * D + (g + 8 * u) * 8) : zero4;
         }
     };
     constexpr int STEP = AM_WARPS * 16;
@@ -346,23 +355,34 @@ attn_merge_quant_kernel(const float* __restrict__ part, float* __restrict__ out,
 template <int D, int G>
 static void launch_decode_dg(const float* q, const __half* k, const __half* v, float* out, float* part, int batch,
                              int heads, int kv_heads, int64_t cache_stride, const int32_t* kv_len, float scale,
-                             int window, int chunk, int splits, int64_t q_row_stride, int always_partials, cudaStream_t s) {
+                             int window, int chunk, int splits, int64_t q_row_stride, int always_partials, int max_len, int ring_start,
+                             int ring_cap, cudaStream_t s) {
     dim3 grid(splits, kv_heads, batch);
     const bool direct = splits == 1 && !always_partials;
     launch_pdl(attn_decode_mma_kernel<D>, grid, dim3(AM_WARPS * 32), 0, s, q, q_row_stride, k, v, part, heads, kv_heads, G, cache_stride, kv_len,
-               scale, window, chunk, splits, direct ? out : (float*) nullptr);
+               scale, window, chunk, splits, direct ? out : (float*) nullptr, max_len, ring_start, ring_cap);
     if (!always_partials && !direct) launch_pdl(attn_merge_kernel<D>, dim3(batch * heads), dim3(D * MG), 0, s, (const float*) part, out, splits);
 }
 
 static int32_t attn_decode_impl(const float* q, int64_t q_row_stride, const __half* k, const __half* v, float* out, int batch, int heads,
                                 int kv_heads, int d, int64_t cache_stride, const int32_t* kv_len, int max_kv_len,
-                                float scale, int window, void* scratch, int always_partials, int* splits_out, cudaStream_t s);
+                                float scale, int window, void* scratch, int always_partials, int* splits_out, cudaStream_t s,
+                                int ring_start = 0, int ring_cap = 0);
 
 int32_t launch_attn_decode(const float* q, const __half* k, const __half* v, float* out, int batch, int heads,
                            int kv_heads, int d, int64_t cache_stride, const int32_t* kv_len, int max_kv_len,
                            float scale, int window, void* scratch, cudaStream_t s) {
     return attn_decode_impl(q, (int64_t) heads * d, k, v, out, batch, heads, kv_heads, d, cache_stride, kv_len, max_kv_len, scale, window,
                             scratch, 0, nullptr, s);
+}
+
+// One sequence over a cache that may be a ring: the visible keys are the `len` slots starting at ring_start,
+// wrapping at ring_cap (0 = a plain cache). kv_len_dev holds len.
+int32_t launch_attn_decode_ring(const float* q, const __half* k, const __half* v, float* out, int heads, int kv_heads, int d,
+                                int64_t cache_stride, const int32_t* kv_len_dev, int len, float scale, int ring_start, int ring_cap,
+                                void* scratch, cudaStream_t s) {
+    return attn_decode_impl(q, (int64_t) heads * d, k, v, out, 1, heads, kv_heads, d, cache_stride, kv_len_dev, len, scale, 0,
+                            scratch, 0, nullptr, s, ring_start, ring_cap);
 }
 
 // Decode attention whose result is also quantized for the projection that follows (q8 per 256 for
@@ -388,7 +408,8 @@ int32_t launch_attn_decode_quant(const float* q, int64_t q_row_stride, const __h
 
 static int32_t attn_decode_impl(const float* q, int64_t q_row_stride, const __half* k, const __half* v, float* out, int batch, int heads,
                                 int kv_heads, int d, int64_t cache_stride, const int32_t* kv_len, int max_kv_len,
-                                float scale, int window, void* scratch, int always_partials, int* splits_out, cudaStream_t s) {
+                                float scale, int window, void* scratch, int always_partials, int* splits_out, cudaStream_t s,
+                                int ring_start, int ring_cap) {
     if (batch <= 0 || heads <= 0) return SKAINET_CUDA_OK;
     const int G = heads / kv_heads;
     const int splits = decode_splits(batch, kv_heads, std::max(1, max_kv_len));
@@ -396,7 +417,7 @@ static int32_t attn_decode_impl(const float* q, int64_t q_row_stride, const __ha
     chunk = (chunk + 31) & ~31;
     float* part = (float*) scratch;
     if (splits_out) *splits_out = splits;
-#define SK_AD(DD, GG) launch_decode_dg<DD, GG>(q, k, v, out, part, batch, heads, kv_heads, cache_stride, kv_len, scale, window, chunk, splits, q_row_stride, always_partials, s)
+#define SK_AD(DD, GG) launch_decode_dg<DD, GG>(q, k, v, out, part, batch, heads, kv_heads, cache_stride, kv_len, scale, window, chunk, splits, q_row_stride, always_partials, std::max(1, max_kv_len), ring_start, ring_cap, s)
     if (d == 128) {
         switch (G) { case 1: SK_AD(128, 1); break; case 2: SK_AD(128, 2); break; case 4: SK_AD(128, 4); break; case 8: SK_AD(128, 8); break;
             default: set_error("attn_decode: heads/kv_heads = %d not in {1,2,4,8}", G); return SKAINET_CUDA_ERR_INVALID; }

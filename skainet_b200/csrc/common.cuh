@@ -84,6 +84,8 @@ enum { SCRATCH_ACT = 0, SCRATCH_ATTN = 1, SCRATCH_TWIN_A = 2, SCRATCH_TWIN_B = 3
 int sm_count();
 int32_t launch_bounded_wait_selftest(int* reached_end, cudaStream_t s);   // probe.cu
 int* device_timeout_flag();   // current device's int, set by a kernel whose bounded wait ran out (nullptr if unavailable)
+int* stream_sched_pair(cudaStream_t stream);   // zeroed {next, done} counters for one launch of a dynamically scheduled kernel (nullptr: schedule statically)
+void stream_sched_release(cudaStream_t stream);
 int32_t timeout_status(int flag_value);       // OK for 0, else ERR_TIMEOUT with a message naming the kind of wait
 int32_t set_thread_device(int device);        // cudaSetDevice + the thread's device bookkeeping
 
@@ -129,6 +131,9 @@ size_t attn_scratch_bytes(int batch, int heads, int head_dim, int max_kv_len);
 int32_t launch_attn_decode(const float* q, const __half* k, const __half* v, float* out, int batch, int heads,
                            int kv_heads, int d, int64_t cache_stride, const int32_t* kv_len, int max_kv_len,
                            float scale, int window, void* scratch, cudaStream_t s);
+int32_t launch_attn_decode_ring(const float* q, const __half* k, const __half* v, float* out, int heads, int kv_heads, int d,
+                                int64_t cache_stride, const int32_t* kv_len_dev, int len, float scale, int ring_start, int ring_cap,
+                                void* scratch, cudaStream_t s);
 int32_t launch_sdpa_f32(const float* q, const float* k, const float* v, float* out, int batch, int heads, int kv_heads,
                         int seq_q, int seq_kv, int d, float scale, int causal, int window, int right_context,
                         const int32_t* lengths, const float* mask, int mb, int mh, int mq, int mk, cudaStream_t s);

@@ -14,6 +14,7 @@
 #include "matvec_fused.cuh"
 #include "tma.cuh"
 #include "comm.cuh"
+#include "stepops.cuh"
 #include "../../include/skainet_cuda_llama.h"
 
 #include <cmath>
@@ -27,78 +28,7 @@ namespace sk {
 // ================================================================================================
 // small kernels of the step
 // ================================================================================================
-enum { PK_QUANT = 0, PK_NORM = 1, PK_SWIGLU = 2 };
-
-// Activation prep between two matvecs: (optional RMSNorm | SwiGLU) then quantization for the next
-// matvec, q8 per 256 (K-quant weights) or the two-term split per 32 (Q8_0 weights).
-// grid (ceil(n/2048), rows), 256 threads: a CTA quantizes 2048 consecutive elements of one row (eight
-// per thread; a warp = one 256-block, four lanes = one 32-block). For RMSNorm every CTA of the row sums
-// the whole row's squares itself (n fp32 values out of L2) instead of synchronising across CTAs.
-// in: [rows][n] (PK_SWIGLU: [rows][2n] = gate | up).
-template <int MODE, bool SPLIT>
-__global__ void __launch_bounds__(256)
-prep_kernel(const float* __restrict__ in, const float* __restrict__ gamma, float eps, int n, ActQ8K oq, ActSplit os) {
-    __shared__ float red[8];
-    skd::pdl_launch_dependents();
-    skd::pdl_wait();
-    const int row = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const float* x = in + (size_t) row * (MODE == PK_SWIGLU ? 2 * n : n);
-    float nscale = 1.0f;
-    if (MODE == PK_NORM) {
-        float ss = 0.0f;
-        for (int i0 = threadIdx.x; i0 < (n >> 2); i0 += 256 * 4) {      // four loads in flight per thread
-            float4 v[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int i = i0 + j * 256;
-                v[j] = i < (n >> 2) ? __ldg(reinterpret_cast<const float4*>(x) + i) : make_float4(0, 0, 0, 0);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
-        }
-        ss = skd::warp_sum(ss);
-        if (lane == 0) red[warp] = ss;
-        __syncthreads();
-        float t = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) t += red[i];
-        nscale = 1.0f / sqrtf(t * (1.0f / (float) n) + eps);
-    }
-    const int n8 = n >> 3;
-    const int c = blockIdx.x * 256 + threadIdx.x;          // this thread's 8-element chunk of the row
-    const bool ok = c < n8;
-    const int cc = ok ? c : 0;
-    float v[8];
-    {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(x) + 2 * cc), b = __ldg(reinterpret_cast<const float4*>(x) + 2 * cc + 1);
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-    }
-    if (MODE == PK_NORM) {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * cc), b = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * cc + 1);
-        const float g[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = (v[i] * nscale) * g[i];
-    }
-    if (MODE == PK_SWIGLU) {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(x + n) + 2 * cc), b = __ldg(reinterpret_cast<const float4*>(x + n) + 2 * cc + 1);
-        const float u[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = (v[i] * (1.0f / (1.0f + expf(-v[i])))) * u[i];
-    }
-    if (!ok) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = 0.0f;
-    }
-    if (SPLIT) {
-        ActSplit o = os;
-        o.hi += (size_t) row * n; o.lo += (size_t) row * n; o.d += (size_t) row * (n >> 5);
-        skd::quant_split_regs(v, o, cc >> 2, cc & 3, ok);
-    } else if (c - lane < n8) {       // warp-uniform: the warp's 256-block lies inside the row
-        const int blk = cc >> 5;
-        skd::quant_q8k_regs(v, oq.q + (size_t) row * n + (size_t) blk * 256, oq.d + (size_t) row * (n >> 8) + blk,
-                            oq.bsums + (size_t) row * (n >> 5) + (size_t) blk * 8, lane);
-    }
-}
+constexpr int PROLOGUE_PREP_MAX_COLS = 4096;
 
 // After the merged q|k|v matvec: rotate q in place, rotate k and append it with v to the f16 cache at
 // each sequence's position. grid (rows, heads + 2*kv_heads), head_dim/2 threads. The rotation factors
@@ -176,12 +106,6 @@ argmax_advance_kernel(const float* __restrict__ logits, int cols, int32_t* __res
 }
 __global__ void bump_cursor_kernel(int32_t* cursor) { skd::pdl_launch_dependents(); skd::pdl_wait(); cursor[0] += 1; }
 
-__global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__ y, int64_t n) {
-    skd::pdl_launch_dependents();
-    skd::pdl_wait();
-    for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) x[i] += y[i];
-}
-
 // Seeded f16 noise into the cache (fake_prefill). The value of an element depends only on the seed and on its
 // place in the unsharded cache (global kv head, position, dim), so every tensor-parallel size decodes the same context.
 __global__ void fill_cache_kernel(__half* kc, __half* vc, int64_t n, int64_t per_head, int head0, uint64_t seed) {
@@ -258,25 +182,6 @@ static int32_t check_weight_shape(const Weight* w, int enc, int rows, int cols, 
     return SKAINET_CUDA_OK;
 }
 
-// rows of `a` then rows of `b` (then `c`) in one resident weight; the parts must share cols and encoding.
-static int32_t concat_rows(const Weight* a, const Weight* b, const Weight* c, Weight** out) {
-    const int rows = a->rows + b->rows + (c ? c->rows : 0);
-    SK_TRY(weight_alloc(a->enc, rows, a->cols, out));
-    Weight* w = *out;
-    const Weight* parts[3] = {a, b, c};
-    size_t row_off = 0;
-    for (int i = 0; i < 3; ++i) {
-        const Weight* p = parts[i];
-        if (!p) continue;
-        const size_t nb = (size_t) p->rows * p->bpr, off = row_off * a->bpr;
-        const size_t qs_b = a->enc == SKAINET_ENC_Q8_0 ? 32 : 128, hdr_b = a->enc == SKAINET_ENC_Q8_0 ? 2 : 16;
-        SK_CUDA(cudaMemcpy(w->qs + off * qs_b, p->qs, nb * qs_b, cudaMemcpyDeviceToDevice));
-        SK_CUDA(cudaMemcpy(w->hdr + off * hdr_b, p->hdr, nb * hdr_b, cudaMemcpyDeviceToDevice));
-        row_off += p->rows;
-    }
-    return SKAINET_CUDA_OK;
-}
-
 static int bucket_of(const Model& m, int len) {
     int b = 256;
     while (b < len) b <<= 1;
@@ -285,53 +190,27 @@ static int bucket_of(const Model& m, int len) {
 
 // y[rows][w.rows] (= resid +) W . act   for activation rows already quantized into m.act.
 static int32_t linear(Model& m, const Weight& w, int rows, float* y, float* resid_inplace, cudaStream_t s) {
-    if (rows == 1) {
-        MatvecIn in;
-        if (w.enc == SKAINET_ENC_Q8_0) in.split = act_split_layout(m.act, 1, w.cols); else in.q8 = act_q8k_layout(m.act, 1, w.cols);
-        const int32_t st = launch_matvec_fused(w, in, PREP_QUANTIZED, resid_inplace ? resid_inplace : y, resid_inplace, s);
-        if (st != 1) return st;
-    }
-    if (rows >= 2) {
-        const int32_t st = w.enc == SKAINET_ENC_Q8_0
-            ? launch_gemm_mma_q8(w, act_split_layout(m.act, rows, w.cols), rows, resid_inplace ? resid_inplace : y, resid_inplace, s)
-            : launch_gemm_mma(w, act_q8k_layout(m.act, rows, w.cols), rows, resid_inplace ? resid_inplace : y, resid_inplace, s);
-        if (st != 1) return st;
-    }
-    float* out = resid_inplace ? m.tmp : y;
-    SK_TRY(launch_matvec(w, nullptr, m.act, rows, out, SKAINET_ACT_NATIVE, s));
-    if (resid_inplace) {
-        const int64_t n = (int64_t) rows * w.rows;
-        SK_CUDA(launch_pdl(add_rows_kernel, dim3((unsigned) std::min<int64_t>((n + 255) / 256, 1184)), dim3(256), 0, s, resid_inplace, (const float*) out, n));
-    }
-    return SKAINET_CUDA_OK;
+    return launch_linear_q(w, m.act, rows, y, resid_inplace, m.tmp, s);
 }
 
 template <int MODE>
-static int32_t prep(Model& m, const float* in, const float* gamma, int rows, int n, bool split, cudaStream_t s);
+static int32_t prep(Model& m, const float* in, const float* gamma, int rows, int n, bool split, cudaStream_t s) {
+    return launch_prep(MODE, in, gamma, m.cfg.rms_eps, rows, n, split, m.act, s);
+}
 
-// y[rows][w.rows] = W . quantize(rmsnorm(x, gamma)). One activation row takes a single launch: the matvec
-// kernel normalises and quantizes the row in its own prologue while its first weight tiles are in flight.
+// y[rows][w.rows] = W . quantize(rmsnorm(x, gamma)). One activation row of up to 4096 elements takes a single
+// launch: the matvec kernel normalises and quantizes the row in its own prologue while its first weight tiles
+// are in flight. Wider rows keep the separate prep kernel: every CTA of the matvec would re-read the fp32 row
+// and the gains (12 bytes per element out of L2 against one for the quantized row), which measured slower
+// (70B shape, 8192 columns: 9.88 against 9.38 ms per step).
 static int32_t linear_normed(Model& m, const Weight& w, const float* x, const float* gamma, int rows, float* y, cudaStream_t s) {
-    if (rows == 1) {
+    if (rows == 1 && w.cols <= PROLOGUE_PREP_MAX_COLS) {
         MatvecIn in; in.x = x; in.gamma = gamma; in.eps = m.cfg.rms_eps;
         const int32_t st = launch_matvec_fused(w, in, PREP_NORM_F32, y, nullptr, s);
         if (st != 1) return st;
     }
     SK_TRY(prep<PK_NORM>(m, x, gamma, rows, w.cols, w.enc == SKAINET_ENC_Q8_0, s));
     return linear(m, w, rows, y, nullptr, s);
-}
-
-template <int MODE>
-static int32_t prep(Model& m, const float* in, const float* gamma, int rows, int n, bool split, cudaStream_t s) {
-    ActQ8K oq = {nullptr, nullptr, nullptr}; ActSplit os = {nullptr, nullptr, nullptr};
-    if (split) {
-        os = act_split_layout(m.act, rows, n);
-        SK_CUDA(launch_pdl(prep_kernel<MODE, true>, dim3((n + 2047) / 2048, rows), dim3(256), 0, s, in, gamma, m.cfg.rms_eps, n, oq, os));
-    } else {
-        oq = act_q8k_layout(m.act, rows, n);
-        SK_CUDA(launch_pdl(prep_kernel<MODE, false>, dim3((n + 2047) / 2048, rows), dim3(256), 0, s, in, gamma, m.cfg.rms_eps, n, oq, os));
-    }
-    return SKAINET_CUDA_OK;
 }
 
 // Sum over the TP group, in place (no-op on one GPU).
@@ -546,7 +425,7 @@ static void free_model(Model* m) {
         if (p) cudaFree(p);
     comm_destroy(m->comm);
     if (m->h_flag) cudaFreeHost(m->h_flag);
-    if (m->stream) { scratch_release(m->stream); cudaStreamDestroy(m->stream); }
+    if (m->stream) { scratch_release(m->stream); stream_sched_release(m->stream); cudaStreamDestroy(m->stream); }
     m->magic = 0;
     delete m;
 }
@@ -610,6 +489,7 @@ int32_t skainet_cuda_llama_create(const skainet_llama_config* cfg, skainet_model
     A(dalloc(&m->log, (size_t) m->log_cap * c.max_batch)); A(dalloc(&m->log_cursor, 1)); A(dalloc(&m->row_seq, R));
     if (st == SKAINET_CUDA_OK && cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) != cudaSuccess) st = cuda_fail(cudaGetLastError(), "cudaStreamCreate", __FILE__, __LINE__);
     if (st == SKAINET_CUDA_OK) {
+        stream_sched_pair(m->stream);       // the stream's work-queue counters exist before any step is captured
         cudaMemset(m->pos, 0, sizeof(int32_t) * c.max_batch); cudaMemset(m->log_cursor, 0, sizeof(int32_t));
         std::vector<float> ones(c.d_model, 1.0f);
         for (auto& L : m->layers) { cudaMemcpy(L.g_attn, ones.data(), 4 * c.d_model, cudaMemcpyHostToDevice); cudaMemcpy(L.g_ffn, ones.data(), 4 * c.d_model, cudaMemcpyHostToDevice); }
@@ -746,8 +626,8 @@ int32_t skainet_cuda_llama_finalize(skainet_model_t h) {
     for (int l = 0; l < m->cfg.n_layers; ++l) {
         Layer& L = m->layers[l];
         SK_REQUIRE(L.wq && L.wk && L.wv && L.wo && L.wgate && L.wup && L.wdown, "llama_finalize: layer %d is missing a weight", l);
-        SK_TRY(concat_rows(L.wq, L.wk, L.wv, &L.wqkv));
-        SK_TRY(concat_rows(L.wgate, L.wup, nullptr, &L.wgu));
+        SK_TRY(weight_concat_rows(L.wq, L.wk, L.wv, &L.wqkv));
+        SK_TRY(weight_concat_rows(L.wgate, L.wup, nullptr, &L.wgu));
         // the merged copies replace the parts
         for (Weight** w : {&L.wq, &L.wk, &L.wv, &L.wgate, &L.wup}) { weight_release(*w); *w = nullptr; }
     }

@@ -29,7 +29,10 @@ constexpr int MF_WARPS = 4;
 constexpr int MF_THREADS = MF_WARPS * 32;
 constexpr int MF_MAX_RW = 4;
 constexpr size_t MF_SMEM_MAX = 100 * 1024;
-constexpr size_t RING_MIN_BYTES = (size_t) 20 << 20;   // measured crossover between the one-tile and the ring kernel
+#ifndef SK_RING_MIN_MB
+#define SK_RING_MIN_MB 20
+#endif
+constexpr size_t RING_MIN_BYTES = (size_t) SK_RING_MIN_MB << 20;   // measured crossover between the one-tile and the ring kernel
 
 // ================================================================================================
 // Q4_K (activation preparation: actprep.cuh)

@@ -183,3 +183,24 @@ def attn_decode_noalloc(q_ptr: int, k_ptr: int, v_ptr: int, out_ptr: int, batch:
     Raises ValueError when the problem does not fit it. Calls that overlap on the GPU race on that area."""
     L.check(L.lib().skainet_cuda_attn_decode_noalloc_dev(q_ptr, k_ptr, v_ptr, out_ptr, batch, heads, kv_heads, head_dim,
                                                          cache_stride, kv_len_ptr, max_kv_len, scale, window, stream))
+
+
+def concat_rows(a: Weight, b: Weight, c: Optional[Weight] = None) -> Weight:
+    """Rows of a, b (and c) as one new resident weight (merged q|k|v or gate|up); the parts stay valid."""
+    h = C.c_int64()
+    L.check(L.lib().skainet_cuda_weight_concat_rows(a.handle, b.handle, c.handle if c is not None else 0, C.byref(h)))
+    return Weight(h.value)
+
+
+def fused_qkv_proj(w_qkv: Weight, q_rows: int, k_rows: int, v_rows: int, x_ptr: int, m: int, q_ptr: int, k_ptr: int, v_ptr: int,
+                   gamma_ptr: int = 0, eps: float = 0.0, stream: int = 0) -> None:
+    """The graph-level fused op `fused_qkv_proj` (optionally with the RMSNorm that feeds it)."""
+    L.check(L.lib().skainet_cuda_fused_qkv_proj_dev(w_qkv.handle, q_rows, k_rows, v_rows, x_ptr, gamma_ptr or None, eps, m, q_ptr, k_ptr,
+                                                    v_ptr, stream))
+
+
+def fused_swiglu_ffn(w_gate_up: Weight, w_down: Weight, x_ptr: int, m: int, out_ptr: int, resid_ptr: int = 0, gamma_ptr: int = 0,
+                     eps: float = 0.0, stream: int = 0) -> None:
+    """The graph-level fused op `fused_swiglu_ffn`: out = (resid +) down(silu(gate(x)) * up(x)), optionally normalised first."""
+    L.check(L.lib().skainet_cuda_fused_swiglu_ffn_dev(w_gate_up.handle, w_down.handle, x_ptr, gamma_ptr or None, eps, m, resid_ptr or None,
+                                                      out_ptr, stream))

@@ -1,0 +1,82 @@
+"""The graph-level fused ops fused_qkv_proj and fused_swiglu_ffn through the C ABI, against the CPU decomposition the
+reference's fallback handlers perform (LLMFusedOpHandlers.kt:86-127,143-196: separate matmuls, silu, multiply), each
+step computed with the reference's own kernels on the same packed bytes."""
+import numpy as np
+import pytest
+
+from conftest import rel_err_ok
+
+pytestmark = pytest.mark.gpu
+
+
+def _weights(gpu, oracle, enc, shapes, seed):
+    rng = np.random.default_rng(seed)
+    packed = []
+    for n, k in shapes:
+        wf = (0.03 * rng.standard_normal((n, k))).astype(np.float32)
+        packed.append(oracle.quantize_q4k(wf) if enc == "Q4_K" else oracle.quantize_q8_0(wf))
+    return packed, [gpu.Weight.upload(p, enc, n, k) for p, (n, k) in zip(packed, shapes)]
+
+
+@pytest.mark.parametrize("enc,d,qr,kr,m,norm", [("Q4_K", 1024, 1024, 256, 1, True), ("Q4_K", 4096, 4096, 1024, 1, False), ("Q4_K", 8192, 256, 128, 1, True),
+                                                ("Q4_K", 1024, 512, 128, 5, True), ("Q8_0", 1024, 1024, 256, 1, True), ("Q8_0", 512, 256, 256, 9, False),
+                                                ("Q4_K", 2048, 768, 256, 150, True)])
+def test_fused_qkv_proj_equals_three_reference_matmuls(gpu, oracle, enc, d, qr, kr, m, norm):
+    use_ref = oracle.ref() is not None
+    (pq, pk, pv), (wq, wk, wv) = _weights(gpu, oracle, enc, [(qr, d), (kr, d), (kr, d)], seed=d + m)
+    merged = gpu.concat_rows(wq, wk, wv)
+    assert merged.rows == qr + 2 * kr
+    np.testing.assert_array_equal(merged.export(), np.concatenate([pq, pk, pv]))      # a pure row concatenation of the packed bytes
+    rng = np.random.default_rng(m)
+    x = (2 * rng.standard_normal((m, d))).astype(np.float32)
+    gamma = (1 + 0.1 * rng.standard_normal(d)).astype(np.float32)
+    dx, dg = gpu.DeviceBuffer.from_host(x), gpu.DeviceBuffer.from_host(gamma)
+    # one row: outputs back to back in one buffer (written directly); several rows: three separate buffers
+    if m == 1:
+        dall = gpu.DeviceBuffer((qr + 2 * kr) * 4)
+        ptrs = (dall.ptr, dall.ptr + qr * 4, dall.ptr + (qr + kr) * 4)
+    else:
+        bufs = [gpu.DeviceBuffer(m * r * 4) for r in (qr, kr, kr)]
+        ptrs = tuple(b.ptr for b in bufs)
+    gpu.fused_qkv_proj(merged, qr, kr, kr, dx.ptr, m, *ptrs, gamma_ptr=dg.ptr if norm else 0, eps=1e-5)
+    xin = oracle.rms_norm(x, gamma, 1e-5, use_ref=use_ref) if norm else x
+    tol = 2e-3 if norm else 1e-3          # behind a norm one activation code may flip
+    for (p, r, name), ptr in zip(((pq, qr, "q"), (pk, kr, "k"), (pv, kr, "v")), ptrs):
+        got = np.empty(m * r, np.float32)
+        from skainet_b200 import _lib as L
+        L.check(L.lib().skainet_cuda_memcpy_d2h(got.ctypes.data, ptr, got.nbytes, 0))
+        rel_err_ok(got.reshape(m, r), oracle.matmul(enc, xin, p, d, r, "rm", use_ref=use_ref).reshape(m, r), tol)
+    with pytest.raises(ValueError):
+        gpu.fused_qkv_proj(merged, qr, kr, kr + 1, dx.ptr, m, *ptrs)
+    for w in (wq, wk, wv, merged):
+        w.free()
+
+
+@pytest.mark.parametrize("enc,d,f,m,norm,resid", [("Q4_K", 1024, 2816, 1, True, True), ("Q4_K", 4096, 11008, 1, False, False), ("Q4_K", 1024, 2048, 6, True, True),
+                                                  ("Q8_0", 512, 1024, 1, True, True), ("Q8_0", 512, 768, 4, False, True), ("Q4_K", 512, 1024, 140, False, False)])
+def test_fused_swiglu_ffn_equals_the_reference_decomposition(gpu, oracle, enc, d, f, m, norm, resid):
+    use_ref = oracle.ref() is not None
+    (pg, pu, pd), (wg, wu, wd) = _weights(gpu, oracle, enc, [(f, d), (f, d), (d, f)], seed=f + m)
+    wgu = gpu.concat_rows(wg, wu)
+    rng = np.random.default_rng(f)
+    x = (2 * rng.standard_normal((m, d))).astype(np.float32)
+    gamma = (1 + 0.1 * rng.standard_normal(d)).astype(np.float32)
+    r = rng.standard_normal((m, d)).astype(np.float32)
+    dx, dg, dr = gpu.DeviceBuffer.from_host(x), gpu.DeviceBuffer.from_host(gamma), gpu.DeviceBuffer.from_host(r)
+    dout = gpu.DeviceBuffer(m * d * 4)
+    gpu.fused_swiglu_ffn(wgu, wd, dx.ptr, m, dout.ptr, resid_ptr=dr.ptr if resid else 0, gamma_ptr=dg.ptr if norm else 0, eps=1e-5)
+    got = dout.download(np.float32, m * d).reshape(m, d)
+    xin = oracle.rms_norm(x, gamma, 1e-5, use_ref=use_ref) if norm else x
+    gate = oracle.matmul(enc, xin, pg, d, f, "rm", use_ref=use_ref).reshape(m, f)
+    up = oracle.matmul(enc, xin, pu, d, f, "rm", use_ref=use_ref).reshape(m, f)
+    ref = oracle.matmul(enc, oracle.swiglu(gate, up), pd, f, d, "rm", use_ref=use_ref).reshape(m, d)
+    # two chained quantizers: a code flip in the first moves the second's input slightly; the bar stays at the one-flip level
+    rel_err_ok(got - (r if resid else 0), ref, 5e-3)
+    err = np.sqrt(np.mean((got - (r if resid else 0) - ref) ** 2) / np.mean(ref ** 2))
+    assert err < 1e-3, err
+    # in place: out == resid
+    if resid:
+        gpu.fused_swiglu_ffn(wgu, wd, dx.ptr, m, dr.ptr, resid_ptr=dr.ptr, gamma_ptr=dg.ptr if norm else 0, eps=1e-5)
+        np.testing.assert_array_equal(dr.download(np.float32, m * d).reshape(m, d), got)
+    for w in (wg, wu, wd, wgu):
+        w.free()
