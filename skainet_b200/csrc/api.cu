@@ -111,44 +111,9 @@ int* device_timeout_flag() {
     return g_timeout_flag[dev];
 }
 
-// {next, done} counter pairs for kernels that hand out their work items dynamically: one block of pairs per
-// (device, stream), rotated over consecutive launches so that a launch overlapping its successor (programmatic
-// dependent launch) never shares a pair with it. A kernel leaves its pair zeroed when its last CTA finishes.
-// Returns nullptr (the kernel then schedules statically) when the block would have to be allocated while the
-// stream is being captured.
-constexpr int SCHED_PAIRS = 16;
-struct SchedBlock { int* p = nullptr; unsigned seq = 0; };
-static std::map<std::pair<int, cudaStream_t>, SchedBlock> g_sched;
-int* stream_sched_pair(cudaStream_t stream) {
-    const int dev = current_device();
-    std::lock_guard<std::mutex> lk(g_mu);
-    SchedBlock& b = g_sched[{dev, stream}];
-    if (!b.p) {
-        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
-        if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) { cudaGetLastError(); return nullptr; }
-        if (cudaMalloc(&b.p, 2 * SCHED_PAIRS * sizeof(int)) != cudaSuccess) { cudaGetLastError(); b.p = nullptr; return nullptr; }
-        cudaMemset(b.p, 0, 2 * SCHED_PAIRS * sizeof(int));
-    }
-    return b.p + 2 * (int) (b.seq++ % SCHED_PAIRS);
-}
-// A kernel that gave up a bounded wait may leave its pair non-zero: zero every block of the device.
-static void sched_reset_all(int dev) {
-    for (auto& kv : g_sched)
-        if (kv.first.first == dev && kv.second.p) cudaMemset(kv.second.p, 0, 2 * SCHED_PAIRS * sizeof(int));
-}
-void stream_sched_release(cudaStream_t stream) {
-    const int dev = current_device();
-    std::lock_guard<std::mutex> lk(g_mu);
-    auto it = g_sched.find({dev, stream});
-    if (it == g_sched.end()) return;
-    if (it->second.p) cudaFree(it->second.p);
-    g_sched.erase(it);
-}
-
 // Turns a raised flag value into the status and message the entry points return.
 int32_t timeout_status(int value) {
     if (value == 0) return SKAINET_CUDA_OK;
-    { std::lock_guard<std::mutex> lk(g_mu); sched_reset_all(current_device()); }
     if (value == 2) set_error("a kernel's bounded wait on a tensor-parallel peer ran out (a rank is late or gone); the step's outputs are not valid");
     else set_error("a kernel's bounded wait on an asynchronous copy or tensor-core barrier ran out; its outputs are not valid");
     return SKAINET_CUDA_ERR_TIMEOUT;
@@ -362,7 +327,6 @@ int32_t skainet_cuda_stream_destroy(skainet_stream_t stream) {
     if (stream) {
         SK_CUDA(cudaStreamSynchronize(as_stream(stream)));
         scratch_release(as_stream(stream));          // the stream's scratch goes with it
-        stream_sched_release(as_stream(stream));
         SK_CUDA(cudaStreamDestroy(as_stream(stream)));
     }
     return SKAINET_CUDA_OK;

@@ -34,6 +34,7 @@ struct NcclApi {
     ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
     ncclResult_t (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
@@ -54,6 +55,7 @@ static void load_nccl() {
     g_nccl.GetUniqueId = (decltype(g_nccl.GetUniqueId)) sym("ncclGetUniqueId");
     g_nccl.CommInitRank = (decltype(g_nccl.CommInitRank)) sym("ncclCommInitRank");
     g_nccl.CommDestroy = (decltype(g_nccl.CommDestroy)) sym("ncclCommDestroy");
+    g_nccl.CommAbort = (decltype(g_nccl.CommAbort)) sym("ncclCommAbort");
     g_nccl.AllReduce = (decltype(g_nccl.AllReduce)) sym("ncclAllReduce");
     g_nccl.AllGather = (decltype(g_nccl.AllGather)) sym("ncclAllGather");
     g_nccl.GetErrorString = (decltype(g_nccl.GetErrorString)) sym("ncclGetErrorString");
@@ -70,69 +72,83 @@ static int32_t nccl_fail(ncclResult_t r, const char* what) {
     return SKAINET_CUDA_ERR_COMM;
 }
 
-constexpr int P2P_MAX_WORLD = 8;
-constexpr int P2P_CTA_ELEMS = 1024;                 // floats per CTA (256 threads x float4)
-constexpr int P2P_MAX_CTAS = 64;
-constexpr int P2P_MAX_ELEMS = P2P_CTA_ELEMS * P2P_MAX_CTAS;
-constexpr int P2P_SPIN_LIMIT = 1 << 25;             // several seconds of polling (ranks may enter their first step apart), then the kernel gives up and reports
+// ------------------------------------------------------------------------------------------------
+// Peer-memory exchange without flags. Every 32-bit word of an inbox carries its own arrival state: an inbox
+// is filled with a sentinel bit pattern, a sender stores plain data words over NVLink, and the receiver polls
+// the words themselves until none is the sentinel (a data word that happens to equal it is replaced by another
+// NaN pattern before it is sent). There is no flag, no fence and no second round trip: the cost of a sum is one
+// NVLink store latency. The receiver puts the sentinel back as soon as it has read a word, so an inbox cleans
+// itself; two inbox copies alternate by round because a fast peer may already send round r+1 while this rank
+// still reads round r (it cannot reach r+2 before this rank has finished r: it needs this rank's r+1 data).
+//
+// Per-rank region, identical layout on every rank (peers map it through CUDA IPC):
+//   channel A  [2][world][P2P_MAX_ELEMS] words   in-place all-reduce of a vector (allreduce_words_kernel)
+//   channel B  [2][world][P2P_MAX_ELEMS] words   outputs of a row-parallel matvec, written by the matvec's own
+//                                                epilogue (matvec_fused.cu / matvec_ring.cu) or by the receiving
+//                                                kernel itself, summed + RMS-normalised + quantized on arrival
+//   control    seqA[P2P_MAX_CTAS] | roundB | ticketB     (local only, zeroed)
+// ------------------------------------------------------------------------------------------------
+constexpr int P2P_CTA_ELEMS = 1024;                 // floats per CTA of the vector all-reduce (256 threads x float4)
+constexpr int P2P_MAX_CTAS = P2P_MAX_ELEMS / P2P_CTA_ELEMS;
+constexpr int P2P_SPIN_LIMIT = 1 << 24;             // seconds of polling (ranks may enter their first step apart), then the kernel gives up and reports
+constexpr uint32_t P2P_SENTINEL = 0xFFFFFFFFu;
+constexpr uint32_t P2P_SENTINEL_ALIAS = 0x7FFFFFFFu;   // what a data word equal to the sentinel is sent as (both are NaNs)
 
-// Per-rank region, identical layout on every rank:
-//   inbox [2][world][P2P_MAX_ELEMS] float | flags [world][P2P_MAX_CTAS] int | seq [P2P_MAX_CTAS] int (local only)
+static size_t p2p_channel_bytes(int world) { return (size_t) 2 * world * P2P_MAX_ELEMS * 4; }
+static size_t p2p_ctl_bytes() { return ((size_t) (P2P_MAX_CTAS + 2) * 4 + 255) & ~(size_t) 255; }
+static size_t p2p_region_bytes(int world) { return 2 * p2p_channel_bytes(world) + p2p_ctl_bytes(); }
+
 struct P2PView {
-    float* inbox[P2P_MAX_WORLD];    // base of each rank's channel as mapped into this process
+    uint32_t* chan[P2P_MAX_WORLD];   // base of one channel in each rank's region, as mapped into this process
+    int* ctl;                        // this rank's control words
     int rank, world;
 };
-static size_t p2p_channel_bytes(int world) {
-    return (size_t) 2 * world * P2P_MAX_ELEMS * 4 + (size_t) world * P2P_MAX_CTAS * 4 + P2P_MAX_CTAS * 4;
-}
-// Two channels with the layout above: channel 0 for the plain all-reduce (slot = 1024 floats), channel 1 for the
-// fused all-reduce + RMSNorm + quantize (slot = 2048 floats). Inside a channel a slot always covers the same
-// floats, which is what lets the two inbox copies alternate safely; mixing slot sizes in one channel would not.
-static size_t p2p_region_bytes(int world) { return 2 * ((p2p_channel_bytes(world) + 255) & ~(size_t) 255); }
-__device__ __forceinline__ int* p2p_flags(float* base, int world) { return (int*) (base + (size_t) 2 * world * P2P_MAX_ELEMS); }
 
+__device__ __forceinline__ uint32_t p2p_word(float v) {
+    const uint32_t u = __float_as_uint(v);
+    return u == P2P_SENTINEL ? P2P_SENTINEL_ALIAS : u;
+}
+__device__ __forceinline__ uint4 p2p_words(float4 v) { return make_uint4(p2p_word(v.x), p2p_word(v.y), p2p_word(v.z), p2p_word(v.w)); }
+__device__ __forceinline__ uint4 ld_volatile_u4(const uint32_t* p) {
+    uint4 r;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+    return r;
+}
+// Waits (bounded) until the four words at p have all arrived, returns them and puts the sentinel back.
+__device__ __forceinline__ float4 p2p_take(uint32_t* p, int* timeout_flag) {
+    uint4 r = ld_volatile_u4(p);
+    int spins = 0;
+    while ((r.x == P2P_SENTINEL || r.y == P2P_SENTINEL || r.z == P2P_SENTINEL || r.w == P2P_SENTINEL) && ++spins < P2P_SPIN_LIMIT) r = ld_volatile_u4(p);
+    if (spins >= P2P_SPIN_LIMIT && timeout_flag) atomicExch(timeout_flag, 2);
+    *reinterpret_cast<uint4*>(p) = make_uint4(P2P_SENTINEL, P2P_SENTINEL, P2P_SENTINEL, P2P_SENTINEL);
+    return make_float4(__uint_as_float(r.x), __uint_as_float(r.y), __uint_as_float(r.z), __uint_as_float(r.w));
+}
+
+// In-place sum of buf[n] over the group (n a multiple of 4, n <= P2P_MAX_ELEMS). CTA c owns floats
+// [1024 c, 1024 (c+1)); its round counter picks the inbox copy. Slots are summed in rank order, so every rank
+// gets the same bits.
 __global__ void __launch_bounds__(256)
-allreduce_oneshot_kernel(P2PView v, float* __restrict__ buf, int n, int* __restrict__ timeout_flag) {
+allreduce_words_kernel(P2PView v, float* __restrict__ buf, int n, int* __restrict__ timeout_flag) {
     __shared__ int s_seq;
     skd::pdl_launch_dependents();
     const int cta = blockIdx.x, world = v.world, rank = v.rank;
-    float* mine = v.inbox[rank];
-    int* my_flags = p2p_flags(mine, world);
-    int* seq_slot = my_flags + world * P2P_MAX_CTAS + cta;
+    int* seq_slot = v.ctl + cta;
     const int i = cta * P2P_CTA_ELEMS + threadIdx.x * 4;          // this thread's float4
-    const bool live = i < n;                                      // n is a multiple of 4
+    const bool live = i < n;
     // buf is the predecessor's output, and the round counter is the previous round's: nothing is read before
     // every earlier kernel of the stream has completed
     skd::pdl_wait();
     if (threadIdx.x == 0) s_seq = *seq_slot + 1;
     __syncthreads();
     const int seq = s_seq, par = seq & 1;
-    float4 own = make_float4(0.f, 0.f, 0.f, 0.f);
     if (live) {
-        own = *reinterpret_cast<const float4*>(buf + i);
+        const float4 own = *reinterpret_cast<const float4*>(buf + i);
+        const uint4 w = p2p_words(own);
         for (int p = 0; p < world; ++p)
-            if (p != rank) *reinterpret_cast<float4*>(v.inbox[p] + ((size_t) par * world + rank) * P2P_MAX_ELEMS + i) = own;
-    }
-    __syncthreads();
-    if (threadIdx.x < world && (int) threadIdx.x != rank) {
-        // publish: the barrier above ordered the CTA's stores before this thread; the fence and the release
-        // store make them visible system-wide before the number is
-        __threadfence_system();
-        int* peer_flag = p2p_flags(v.inbox[threadIdx.x], world) + rank * P2P_MAX_CTAS + cta;
-        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(peer_flag), "r"(seq) : "memory");
-        // wait for the same peer's number (bounded)
-        const int* f = my_flags + threadIdx.x * P2P_MAX_CTAS + cta;
-        int got = 0, spins = 0;
-        do {
-            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(got) : "l"(f) : "memory");
-        } while (got < seq && ++spins < P2P_SPIN_LIMIT);
-        if (got < seq && timeout_flag) atomicExch(timeout_flag, 2);
-    }
-    __syncthreads();
-    if (live) {
+            if (p != rank) *reinterpret_cast<uint4*>(v.chan[p] + ((size_t) par * world + rank) * P2P_MAX_ELEMS + i) = w;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int p = 0; p < world; ++p) {
-            const float4 x = p == rank ? own : __ldcg(reinterpret_cast<const float4*>(mine + ((size_t) par * world + p) * P2P_MAX_ELEMS + i));
+            const float4 x = p == rank ? own : p2p_take(v.chan[rank] + ((size_t) par * world + p) * P2P_MAX_ELEMS + i, timeout_flag);
             acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
         }
         *reinterpret_cast<float4*>(buf + i) = acc;
@@ -140,65 +156,47 @@ allreduce_oneshot_kernel(P2PView v, float* __restrict__ buf, int n, int* __restr
     if (threadIdx.x == 0) *seq_slot = seq;
 }
 
-// All-reduce of rows of x over the group fused with what always follows it in the decoder: RMSNorm with weights
-// gamma and the int8-per-256 activation quantizer. One thread-block cluster per row, one CTA per 2048 floats
-// (256 threads x 8): exchange and sum as above (the sum is also written back to x, the residual stream), then the
-// CTAs of the cluster add up their sums of squares through distributed shared memory and each normalises and
-// quantizes its own 2048 values (one warp = one 256-block, as in prep_kernel).
+// Sum over the group of the rows a row-parallel matvec produced, fused with what always follows it in the decoder:
+// the sum is written to x (the residual stream), RMS-normalised with gamma and quantized to int8 per 256 for the
+// next matvec. One thread-block cluster per row, one CTA per 2048 floats (256 threads x 8). With SEND the kernel
+// first stores this rank's partial row (in x) into every inbox; without, the matvec's epilogue has already done
+// so (matvec_fused.cu, matvec_ring.cu: EPI_PEER) and x is only written. The CTAs of the cluster add up their sums
+// of squares through distributed shared memory. The CTA that finishes last advances the channel's round.
 constexpr int P2P_FUSED_CTA_ELEMS = 2048;
+template <bool SEND>
 __global__ void __launch_bounds__(256)
-allreduce_norm_quant_kernel(P2PView v, float* __restrict__ x, int n, const float* __restrict__ gamma, float eps, ActQ8K act,
-                            int* __restrict__ timeout_flag) {
+gather_sum_norm_quant_kernel(P2PView v, float* __restrict__ x, int n, const float* __restrict__ gamma, float eps, ActQ8K act,
+                             int* __restrict__ timeout_flag) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
-    __shared__ int s_seq;
     __shared__ float s_red[8];
     __shared__ float s_part;                           // this CTA's sum of squares, read by the whole cluster
     skd::pdl_launch_dependents();
     const int cs = gridDim.x, cx = blockIdx.x, row = blockIdx.y;
-    const int cta = row * cs + cx, world = v.world, rank = v.rank;
+    const int world = v.world, rank = v.rank;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    float* mine = v.inbox[rank];
-    int* my_flags = p2p_flags(mine, world);
-    int* seq_slot = my_flags + world * P2P_MAX_CTAS + cta;
+    int* round_ctr = v.ctl + P2P_MAX_CTAS;
+    int* ticket = round_ctr + 1;
     const int col = cx * P2P_FUSED_CTA_ELEMS + threadIdx.x * 8;           // this thread's 8 floats of the row
-    const int64_t i = (int64_t) cta * P2P_FUSED_CTA_ELEMS + threadIdx.x * 8;   // ... and of the inbox
-    float* xr = x + (size_t) row * n + col;
+    const int64_t i = (int64_t) row * n + col;                              // ... and of every inbox slot
+    float* xr = x + i;
     skd::pdl_wait();
-    if (threadIdx.x == 0) s_seq = *seq_slot + 1;
-    __syncthreads();
-    const int seq = s_seq, par = seq & 1;
-    const float4 own0 = *reinterpret_cast<const float4*>(xr), own1 = *reinterpret_cast<const float4*>(xr + 4);
-    for (int p = 0; p < world; ++p)
-        if (p != rank) {
-            float* dst = v.inbox[p] + ((size_t) par * world + rank) * P2P_MAX_ELEMS + i;
-            *reinterpret_cast<float4*>(dst) = own0; *reinterpret_cast<float4*>(dst + 4) = own1;
+    const int par = *reinterpret_cast<volatile int*>(round_ctr) & 1;
+    if (SEND) {
+        const uint4 w0 = p2p_words(*reinterpret_cast<const float4*>(xr)), w1 = p2p_words(*reinterpret_cast<const float4*>(xr + 4));
+        for (int p = 0; p < world; ++p) {
+            uint32_t* dst = v.chan[p] + ((size_t) par * world + rank) * P2P_MAX_ELEMS + i;
+            *reinterpret_cast<uint4*>(dst) = w0; *reinterpret_cast<uint4*>(dst + 4) = w1;
         }
-    __syncthreads();
-    if (threadIdx.x < world && (int) threadIdx.x != rank) {
-        __threadfence_system();
-        int* peer_flag = p2p_flags(v.inbox[threadIdx.x], world) + rank * P2P_MAX_CTAS + cta;
-        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(peer_flag), "r"(seq) : "memory");
-        const int* f = my_flags + threadIdx.x * P2P_MAX_CTAS + cta;
-        int got = 0, spins = 0;
-        do {
-            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(got) : "l"(f) : "memory");
-        } while (got < seq && ++spins < P2P_SPIN_LIMIT);
-        if (got < seq && timeout_flag) atomicExch(timeout_flag, 2);
     }
-    __syncthreads();
     float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int p = 0; p < world; ++p) {                  // rank order: every rank gets the same bits
-        float4 u0 = own0, u1 = own1;
-        if (p != rank) {
-            const float* src = mine + ((size_t) par * world + p) * P2P_MAX_ELEMS + i;
-            u0 = __ldcg(reinterpret_cast<const float4*>(src)); u1 = __ldcg(reinterpret_cast<const float4*>(src + 4));
-        }
+        uint32_t* src = v.chan[rank] + ((size_t) par * world + p) * P2P_MAX_ELEMS + i;
+        const float4 u0 = p2p_take(src, timeout_flag), u1 = p2p_take(src + 4, timeout_flag);
         a[0] += u0.x; a[1] += u0.y; a[2] += u0.z; a[3] += u0.w; a[4] += u1.x; a[5] += u1.y; a[6] += u1.z; a[7] += u1.w;
     }
     *reinterpret_cast<float4*>(xr) = make_float4(a[0], a[1], a[2], a[3]);
     *reinterpret_cast<float4*>(xr + 4) = make_float4(a[4], a[5], a[6], a[7]);
-    if (threadIdx.x == 0) *seq_slot = seq;
     // sum of squares of the row: warp, CTA, cluster (fixed orders)
     float ss = 0.0f;
 #pragma unroll
@@ -211,6 +209,9 @@ allreduce_norm_quant_kernel(P2PView v, float* __restrict__ x, int n, const float
 #pragma unroll
         for (int k = 0; k < 8; ++k) t += s_red[k];
         s_part = t;
+        // the last CTA of the launch to get here advances the round (every CTA has read it by then)
+        __threadfence();
+        if (atomicAdd(ticket, 1) == (int) (gridDim.x * gridDim.y) - 1) { *ticket = 0; *round_ctr = *round_ctr + 1; }
     }
     cluster.sync();
     float total = 0.0f;
@@ -230,60 +231,72 @@ struct Comm {
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1;
     bool p2p = false;
-    P2PView view = {};              // channel 0: plain all-reduce
-    P2PView view_fused = {};        // channel 1: all-reduce + RMSNorm + quantize
+    P2PView view = {};              // channel A: plain all-reduce
+    P2PView view_fused = {};        // channel B: row-parallel matvec outputs -> sum + RMSNorm + quantize
     void* region = nullptr;          // this rank's region (cudaMalloc)
     void* peers[P2P_MAX_WORLD] = {}; // opened IPC mappings (null for self)
 };
 
-// Exchanges IPC handles of the per-rank regions through NCCL and maps every peer's region. Any failure
-// leaves the communicator on NCCL only.
-static void p2p_setup(Comm* c) {
-    static const bool off = []() { const char* e = getenv("SKAINET_TP_ALLREDUCE"); return e && strcmp(e, "nccl") == 0; }();
-    if (off || c->world < 2 || c->world > P2P_MAX_WORLD) return;
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return;
+// Exchanges IPC handles of the per-rank regions through NCCL and maps every peer's region. Every rank takes part in
+// both collectives below whatever happened to its own preparation (a rank that returned early would leave the others
+// waiting inside NCCL): a failed rank contributes a zeroed handle and a "no" vote, and the vote turns the peer-memory
+// path off on all ranks together. SKAINET_TP_ALLREDUCE=nccl is such a "no" vote.
+static int32_t p2p_setup(Comm* c) {
+    if (c->world < 2 || c->world > P2P_MAX_WORLD) return SKAINET_CUDA_OK;      // the same decision on every rank
+    const char* env = getenv("SKAINET_TP_ALLREDUCE");
+    bool ok = !(env && strcmp(env, "nccl") == 0);
+    // the exchange buffers come first: without them this rank could not even take part in the gather
+    const size_t hsz = sizeof(cudaIpcMemHandle_t);
+    uint8_t* xchg = nullptr;
+    if (cudaMalloc((void**) &xchg, hsz * (c->world + 1) + 256) != cudaSuccess) {
+        cudaGetLastError();
+        if (g_nccl.CommAbort) g_nccl.CommAbort(c->comm);       // releases the peers' collectives with an error instead of a hang
+        set_error("tensor-parallel setup: no device memory for the handle exchange");
+        return SKAINET_CUDA_ERR_OOM;
+    }
+    uint8_t* d_send = xchg; uint8_t* d_recv = xchg + hsz; float* d_vote = (float*) (xchg + hsz * (c->world + 1));
     const size_t bytes = p2p_region_bytes(c->world);
-    if (cudaMalloc(&c->region, bytes) != cudaSuccess) { c->region = nullptr; cudaGetLastError(); return; }
-    cudaMemset(c->region, 0, bytes);
     cudaIpcMemHandle_t h;
-    void* d_send = nullptr; void* d_recv = nullptr;
+    memset(&h, 0, sizeof(h));
+    if (ok) {
+        if (cudaMalloc(&c->region, bytes) != cudaSuccess) { c->region = nullptr; cudaGetLastError(); ok = false; }
+        else {
+            cudaMemset(c->region, 0xFF, 2 * p2p_channel_bytes(c->world));                                      // inboxes: every word the sentinel
+            cudaMemset((uint8_t*) c->region + 2 * p2p_channel_bytes(c->world), 0, p2p_ctl_bytes());              // counters
+            if (cudaIpcGetMemHandle(&h, c->region) != cudaSuccess) { cudaGetLastError(); memset(&h, 0, sizeof(h)); ok = false; }
+        }
+    }
     std::vector<cudaIpcMemHandle_t> all(c->world);
-    bool ok = cudaIpcGetMemHandle(&h, c->region) == cudaSuccess && cudaMalloc(&d_send, sizeof(h)) == cudaSuccess &&
-              cudaMalloc(&d_recv, sizeof(h) * c->world) == cudaSuccess;
-    // every rank takes part in the gather even when its own preparation failed (a zero handle then fails to open)
-    if (!ok) memset(&h, 0, sizeof(h));
-    if (d_send && d_recv) {
-        cudaMemcpy(d_send, &h, sizeof(h), cudaMemcpyHostToDevice);
-        ok = g_nccl.AllGather(d_send, d_recv, sizeof(h), ncclInt8, c->comm, (cudaStream_t) 0) == 0 && ok;
-        ok = cudaStreamSynchronize(0) == cudaSuccess && ok;
-        cudaMemcpy(all.data(), d_recv, sizeof(h) * c->world, cudaMemcpyDeviceToHost);
-    } else ok = false;
-    cudaFree(d_send); cudaFree(d_recv);
+    cudaMemcpy(d_send, &h, hsz, cudaMemcpyHostToDevice);
+    bool gathered = g_nccl.AllGather(d_send, d_recv, hsz, ncclInt8, c->comm, (cudaStream_t) 0) == 0;
+    gathered = cudaStreamSynchronize(0) == cudaSuccess && gathered;
+    if (gathered) cudaMemcpy(all.data(), d_recv, hsz * c->world, cudaMemcpyDeviceToHost); else ok = false;
+    uint32_t* base[P2P_MAX_WORLD] = {};
     for (int p = 0; ok && p < c->world; ++p) {
-        if (p == c->rank) { c->view.inbox[p] = (float*) c->region; continue; }
-        if (cudaIpcOpenMemHandle(&c->peers[p], all[p], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { ok = false; c->peers[p] = nullptr; break; }
-        c->view.inbox[p] = (float*) c->peers[p];
+        if (p == c->rank) { base[p] = (uint32_t*) c->region; continue; }
+        if (cudaIpcOpenMemHandle(&c->peers[p], all[p], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); ok = false; c->peers[p] = nullptr; break; }
+        base[p] = (uint32_t*) c->peers[p];
     }
     // agree: the fast path is used only when every rank mapped every peer
-    int* d_ok = nullptr;
-    int mine = ok ? 1 : 0, sum = 0;
-    if (cudaMalloc(&d_ok, sizeof(int)) == cudaSuccess) {
-        float f = (float) mine;
-        cudaMemcpy(d_ok, &f, sizeof(float), cudaMemcpyHostToDevice);
-        if (g_nccl.AllReduce(d_ok, d_ok, 1, ncclFloat32, ncclSum, c->comm, (cudaStream_t) 0) == 0 && cudaStreamSynchronize(0) == cudaSuccess) {
-            cudaMemcpy(&f, d_ok, sizeof(float), cudaMemcpyDeviceToHost);
-            sum = (int) f;
-        }
-        cudaFree(d_ok);
+    float vote = ok ? 1.0f : 0.0f;
+    int sum = 0;
+    cudaMemcpy(d_vote, &vote, sizeof(float), cudaMemcpyHostToDevice);
+    if (g_nccl.AllReduce(d_vote, d_vote, 1, ncclFloat32, ncclSum, c->comm, (cudaStream_t) 0) == 0 && cudaStreamSynchronize(0) == cudaSuccess) {
+        cudaMemcpy(&vote, d_vote, sizeof(float), cudaMemcpyDeviceToHost);
+        sum = (int) vote;
     }
+    cudaFree(xchg);
     cudaGetLastError();
-    c->view.rank = c->rank; c->view.world = c->world;
-    c->view_fused = c->view;
-    const size_t ch = (p2p_channel_bytes(c->world) + 255) & ~(size_t) 255;
-    for (int p = 0; p < c->world; ++p)
-        if (c->view.inbox[p]) c->view_fused.inbox[p] = (float*) ((uint8_t*) c->view.inbox[p] + ch);
     c->p2p = sum == c->world;
+    if (c->p2p) {
+        c->view.rank = c->view_fused.rank = c->rank; c->view.world = c->view_fused.world = c->world;
+        c->view.ctl = c->view_fused.ctl = (int*) ((uint8_t*) c->region + 2 * p2p_channel_bytes(c->world));
+        for (int p = 0; p < c->world; ++p) {
+            c->view.chan[p] = base[p];
+            c->view_fused.chan[p] = (uint32_t*) ((uint8_t*) base[p] + p2p_channel_bytes(c->world));
+        }
+    }
+    return SKAINET_CUDA_OK;
 }
 
 int32_t comm_unique_id(uint8_t* id128) {
@@ -303,7 +316,8 @@ int32_t comm_create(int rank, int world, const uint8_t* id128, Comm** out) {
     c->rank = rank; c->world = world;
     const ncclResult_t r = g_nccl.CommInitRank(&c->comm, world, id, rank);
     if (r != 0) { delete c; return nccl_fail(r, "ncclCommInitRank"); }
-    p2p_setup(c);
+    const int32_t st = p2p_setup(c);
+    if (st != SKAINET_CUDA_OK) { c->comm = nullptr; comm_destroy(c); return st; }
     *out = c;
     return SKAINET_CUDA_OK;
 }
@@ -321,20 +335,22 @@ int32_t comm_all_reduce_sum(Comm* c, float* buf, int64_t n, cudaStream_t s) {
     if (!c) { set_error("tensor-parallel model without a communicator (call llama_tp_init)"); return SKAINET_CUDA_ERR_COMM; }
     if (c->p2p && n <= P2P_MAX_ELEMS && n % 4 == 0 && ((uintptr_t) buf & 15) == 0) {
         const int ctas = (int) ((n + P2P_CTA_ELEMS - 1) / P2P_CTA_ELEMS);
-        SK_CUDA(launch_pdl(allreduce_oneshot_kernel, dim3(ctas), dim3(256), 0, s, c->view, buf, (int) n, device_timeout_flag()));
+        SK_CUDA(launch_pdl(allreduce_words_kernel, dim3(ctas), dim3(256), 0, s, c->view, buf, (int) n, device_timeout_flag()));
         return SKAINET_CUDA_OK;
     }
     const ncclResult_t r = g_nccl.AllReduce(buf, buf, (size_t) n, ncclFloat32, ncclSum, c->comm, s);
     return r == 0 ? SKAINET_CUDA_OK : nccl_fail(r, "ncclAllReduce");
 }
 
-// In place: x[rows][n] <- sum over the group; act <- quantize(rmsnorm(x, gamma)). Returns 1 when the fused kernel
-// does not apply (no peer mapping, shapes outside its slots): the caller then runs the two steps separately.
-int32_t comm_all_reduce_norm_quant(Comm* c, float* x, int rows, int n, const float* gamma, float eps, ActQ8K act, cudaStream_t s) {
-    static const bool off = []() { const char* e = getenv("SKAINET_TP_FUSE"); return e && strcmp(e, "0") == 0; }();
-    if (off || !c || !c->p2p || n % P2P_FUSED_CTA_ELEMS != 0) return 1;
+static bool fused_shape_ok(const Comm* c, const float* x, int rows, int n) {
+    if (!c || !c->p2p || n % P2P_FUSED_CTA_ELEMS != 0) return false;
     const int cs = n / P2P_FUSED_CTA_ELEMS;
-    if (cs > 8 || rows * cs > P2P_MAX_CTAS || (int64_t) rows * n > P2P_MAX_ELEMS || ((uintptr_t) x & 15) != 0) return 1;
+    return cs <= 8 && (int64_t) rows * n <= P2P_MAX_ELEMS && ((uintptr_t) x & 15) == 0;
+}
+
+template <bool SEND>
+static int32_t launch_gather(Comm* c, float* x, int rows, int n, const float* gamma, float eps, ActQ8K act, cudaStream_t s) {
+    const int cs = n / P2P_FUSED_CTA_ELEMS;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(cs, rows); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = s;
     cudaLaunchAttribute attrs[2];
@@ -343,8 +359,30 @@ int32_t comm_all_reduce_norm_quant(Comm* c, float* x, int rows, int n, const flo
     attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attrs[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attrs; cfg.numAttrs = 2;
-    SK_CUDA(cudaLaunchKernelEx(&cfg, allreduce_norm_quant_kernel, c->view_fused, x, n, gamma, eps, act, device_timeout_flag()));
+    SK_CUDA(cudaLaunchKernelEx(&cfg, gather_sum_norm_quant_kernel<SEND>, c->view_fused, x, n, gamma, eps, act, device_timeout_flag()));
     return SKAINET_CUDA_OK;
+}
+
+// In place: x[rows][n] <- sum over the group; act <- quantize(rmsnorm(x, gamma)). Returns 1 when the fused kernel
+// does not apply (no peer mapping, shapes outside its slots): the caller then runs the two steps separately.
+int32_t comm_all_reduce_norm_quant(Comm* c, float* x, int rows, int n, const float* gamma, float eps, ActQ8K act, cudaStream_t s) {
+    static const bool off = []() { const char* e = getenv("SKAINET_TP_FUSE"); return e && strcmp(e, "0") == 0; }();
+    if (off || !fused_shape_ok(c, x, rows, n)) return 1;
+    return launch_gather<true>(c, x, rows, n, gamma, eps, act, s);
+}
+
+bool comm_peer_out(Comm* c, int rows, int n, PeerOut* out) {
+    static const bool off = []() { const char* e = getenv("SKAINET_TP_FUSE"); return e && (strcmp(e, "0") == 0 || strcmp(e, "1") == 0); }();
+    if (off || rows != 1 || !fused_shape_ok(c, nullptr, rows, n)) return false;
+    for (int p = 0; p < c->world; ++p) out->inbox[p] = c->view_fused.chan[p];
+    out->round = c->view_fused.ctl + P2P_MAX_CTAS;
+    out->world = c->world; out->rank = c->rank;
+    return true;
+}
+
+int32_t comm_gather_norm_quant(Comm* c, float* x, int rows, int n, const float* gamma, float eps, ActQ8K act, cudaStream_t s) {
+    if (!fused_shape_ok(c, x, rows, n)) { set_error("comm_gather_norm_quant: shape outside the peer-memory path"); return SKAINET_CUDA_ERR_INVALID; }
+    return launch_gather<false>(c, x, rows, n, gamma, eps, act, s);
 }
 
 int32_t comm_all_gather(Comm* c, const void* send, void* recv, int64_t nbytes, cudaStream_t s) {

@@ -84,8 +84,6 @@ enum { SCRATCH_ACT = 0, SCRATCH_ATTN = 1, SCRATCH_TWIN_A = 2, SCRATCH_TWIN_B = 3
 int sm_count();
 int32_t launch_bounded_wait_selftest(int* reached_end, cudaStream_t s);   // probe.cu
 int* device_timeout_flag();   // current device's int, set by a kernel whose bounded wait ran out (nullptr if unavailable)
-int* stream_sched_pair(cudaStream_t stream);   // zeroed {next, done} counters for one launch of a dynamically scheduled kernel (nullptr: schedule statically)
-void stream_sched_release(cudaStream_t stream);
 int32_t timeout_status(int flag_value);       // OK for 0, else ERR_TIMEOUT with a message naming the kind of wait
 int32_t set_thread_device(int device);        // cudaSetDevice + the thread's device bookkeeping
 

@@ -221,7 +221,10 @@ static int32_t tp_sum(Model& m, float* buf, int64_t n, cudaStream_t s) {
 
 // The transformer body over `rows` activation rows in m.x. decode: row b = sequence b, one token each;
 // prefill: rows = consecutive tokens of sequence `seq`. kv_bound bounds the keys attention visits.
-static int32_t body(Model& m, int rows, bool prefill, int seq, int kv_bound, cudaStream_t s) {
+// final_gamma != nullptr asks for the output norm to be folded into the last group sum where that is possible;
+// *final_prepared then says whether m.act already holds the quantized, normalised rows for the output head.
+static int32_t body(Model& m, int rows, bool prefill, int seq, int kv_bound, cudaStream_t s, const float* final_gamma = nullptr,
+                    bool* final_prepared = nullptr) {
     const auto& c = m.cfg;
     const int D = c.head_dim, H = m.heads_l, HK = m.kv_heads_l, qkv_dim = (H + 2 * HK) * D;
     const bool lin_split = c.linear_enc == SKAINET_ENC_Q8_0;
@@ -237,6 +240,27 @@ static int32_t body(Model& m, int rows, bool prefill, int seq, int kv_bound, cud
             if (st == SKAINET_CUDA_OK) *prepared = true;
             if (st != 1) return st;
         }
+        return tp_sum(m, m.x, (int64_t) rows * c.d_model, s);
+    };
+    // A row-parallel projection (o, down) and what follows it. Under TP with one activation row the matvec's own
+    // epilogue stores its partial rows into every rank's inbox (rank 0 carries the residual), and the kernel that
+    // follows only gathers, sums, normalises with gamma_next and quantizes. Otherwise: the projection into the
+    // residual stream, then the group sum (fused with norm + quantizer where the peer-memory kernel applies).
+    auto row_parallel = [&](const Weight& w, const float* gamma_next, bool* prepared) -> int32_t {
+        *prepared = false;
+        PeerOut po;
+        if (tp && !lin_split && gamma_next && comm_peer_out(m.comm, rows, c.d_model, &po)) {
+            MatvecIn in; in.q8 = act_q8k_layout(m.act, 1, w.cols);
+            const int32_t st = launch_matvec_fused(w, in, PREP_QUANTIZED, nullptr, rank0 ? m.x : nullptr, s, &po);
+            if (st == SKAINET_CUDA_OK) {
+                SK_TRY(comm_gather_norm_quant(m.comm, m.x, rows, c.d_model, gamma_next, c.rms_eps, act_q8k_layout(m.act, rows, c.d_model), s));
+                *prepared = true;
+                return SKAINET_CUDA_OK;
+            }
+            if (st != 1) return st;
+        }
+        if (tp && !rank0) SK_TRY(linear(m, w, rows, m.x, nullptr, s)); else SK_TRY(linear(m, w, rows, nullptr, m.x, s));
+        if (tp && gamma_next) return sum_then_norm(gamma_next, prepared);
         return tp_sum(m, m.x, (int64_t) rows * c.d_model, s);
     };
     bool normed = false;
@@ -263,17 +287,14 @@ static int32_t body(Model& m, int rows, bool prefill, int seq, int kv_bound, cud
             SK_TRY(launch_attn_decode(m.q, L.kc, L.vc, m.attn, rows, H, HK, D, c.max_seq, m.kv_len, kv_bound, scale, 0, m.attn_scratch, s));
         }
         if (!fused_attn) SK_TRY(prep<PK_QUANT>(m, m.attn, nullptr, rows, H * D, lin_split, s));
-        // row-parallel projections under TP: rank 0 carries the residual, then the group sums
-        if (tp && !rank0) SK_TRY(linear(m, *L.wo, rows, m.x, nullptr, s)); else SK_TRY(linear(m, *L.wo, rows, nullptr, m.x, s));
         bool ffn_ready = false;
-        SK_TRY(sum_then_norm(L.g_ffn, &ffn_ready));
+        SK_TRY(row_parallel(*L.wo, L.g_ffn, &ffn_ready));
         if (ffn_ready) SK_TRY(linear(m, *L.wgu, rows, m.gu, nullptr, s));
         else SK_TRY(linear_normed(m, *L.wgu, m.x, L.g_ffn, rows, m.gu, s));
         SK_TRY(prep<PK_SWIGLU>(m, m.gu, nullptr, rows, m.ffn_l, lin_split, s));
-        if (tp && !rank0) SK_TRY(linear(m, *L.wdown, rows, m.x, nullptr, s)); else SK_TRY(linear(m, *L.wdown, rows, nullptr, m.x, s));
-        if (tp && l + 1 < c.n_layers) SK_TRY(sum_then_norm(m.layers[l + 1].g_attn, &normed));
-        else SK_TRY(tp_sum(m, m.x, (int64_t) rows * c.d_model, s));
+        SK_TRY(row_parallel(*L.wdown, l + 1 < c.n_layers ? m.layers[l + 1].g_attn : final_gamma, &normed));
     }
+    if (final_prepared) *final_prepared = normed;
     return SKAINET_CUDA_OK;
 }
 
@@ -337,8 +358,11 @@ static int32_t enqueue_step(Model& m, int batch, int kv_bound, cudaStream_t s) {
     const auto& c = m.cfg;
     begin_step_kernel<<<(batch + 255) / 256, 256, 0, s>>>(m.pos, m.kv_len, batch);
     SK_TRY(launch_embed(*m.embed, m.cur_token, batch, m.x, s));
-    SK_TRY(body(m, batch, false, 0, kv_bound, s));
-    SK_TRY(linear_normed(m, *m.head, m.x, m.g_out, batch, m.logits, s));
+    bool head_ready = false;
+    const bool fold_out_norm = c.tp_world > 1 && c.table_enc != SKAINET_ENC_Q8_0;      // the fused sum quantizes for K-quant weights
+    SK_TRY(body(m, batch, false, 0, kv_bound, s, fold_out_norm ? m.g_out : nullptr, &head_ready));
+    if (head_ready) SK_TRY(linear(m, *m.head, batch, m.logits, nullptr, s));
+    else SK_TRY(linear_normed(m, *m.head, m.x, m.g_out, batch, m.logits, s));
     if (c.tp_world > 1) {
         float* vals = m.tmp; int32_t* idxs = (int32_t*) (m.tmp + batch);
         float2* mine = (float2*) (m.tmp + 2 * batch); float2* all = mine + batch;
@@ -425,7 +449,7 @@ static void free_model(Model* m) {
         if (p) cudaFree(p);
     comm_destroy(m->comm);
     if (m->h_flag) cudaFreeHost(m->h_flag);
-    if (m->stream) { scratch_release(m->stream); stream_sched_release(m->stream); cudaStreamDestroy(m->stream); }
+    if (m->stream) { scratch_release(m->stream); cudaStreamDestroy(m->stream); }
     m->magic = 0;
     delete m;
 }
@@ -489,7 +513,6 @@ int32_t skainet_cuda_llama_create(const skainet_llama_config* cfg, skainet_model
     A(dalloc(&m->log, (size_t) m->log_cap * c.max_batch)); A(dalloc(&m->log_cursor, 1)); A(dalloc(&m->row_seq, R));
     if (st == SKAINET_CUDA_OK && cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) != cudaSuccess) st = cuda_fail(cudaGetLastError(), "cudaStreamCreate", __FILE__, __LINE__);
     if (st == SKAINET_CUDA_OK) {
-        stream_sched_pair(m->stream);       // the stream's work-queue counters exist before any step is captured
         cudaMemset(m->pos, 0, sizeof(int32_t) * c.max_batch); cudaMemset(m->log_cursor, 0, sizeof(int32_t));
         std::vector<float> ones(c.d_model, 1.0f);
         for (auto& L : m->layers) { cudaMemcpy(L.g_attn, ones.data(), 4 * c.d_model, cudaMemcpyHostToDevice); cudaMemcpy(L.g_ffn, ones.data(), 4 * c.d_model, cudaMemcpyHostToDevice); }

@@ -41,7 +41,7 @@ template <int RW, int PREP, int EPI>
 __global__ void __launch_bounds__(MF_THREADS)
 q4k_matvec_fused_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ hdr, int rows, int bpr,
                         MatvecIn in, int cols, float* __restrict__ y, const float* __restrict__ resid,
-                        int* __restrict__ timeout_flag) {
+                        int* __restrict__ timeout_flag, PeerOut peer) {
     constexpr int R = MF_WARPS * RW;
     extern __shared__ __align__(128) uint8_t smem[];
     // layout: qs tile | hdr tile | q8 (swizzled) | bsums | d | reduce scratch | barriers
@@ -52,6 +52,7 @@ q4k_matvec_fused_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restric
     float* s_d = (float*) ((uint8_t*) s_bs + cols / 16);
     float* s_red = (float*) ((uint8_t*) s_d + ((bpr * 4 + 15) & ~15));
     uint64_t* bars = (uint64_t*) (s_red + 4);
+    float* s_out = (float*) (bars + MF_MAX_RW);          // the tile's results, gathered for the peer stores
 
     const int row0 = blockIdx.x * R;
     const int nrows = min(R, rows - row0);
@@ -145,7 +146,20 @@ q4k_matvec_fused_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restric
             }
         }
         const float v = skd::warp_sum(acc);
-        if (lane == 0 && rl < nrows) y[row0 + rl] = EPI == EPI_ADD ? resid[row0 + rl] + v : v;
+        if (EPI == EPI_PEER) { if (lane == 0) s_out[rl] = rl < nrows ? (resid ? resid[row0 + rl] + v : v) : 0.0f; }
+        else if (lane == 0 && rl < nrows) y[row0 + rl] = EPI == EPI_ADD ? resid[row0 + rl] + v : v;
+    }
+    if (EPI == EPI_PEER) {
+        // the tile's rows, four at a time, into this rank's slot of every rank's inbox: the exchange of the group sum
+        // rides on the matvec instead of following it
+        __syncthreads();
+        const int par = *reinterpret_cast<const volatile int*>(peer.round) & 1;
+        constexpr int G4 = R / 4;
+        for (int t = threadIdx.x; t < G4 * peer.world; t += MF_THREADS) {
+            const int g = t % G4, p = t / G4, base = row0 + 4 * g;
+            if (base + 3 < rows) peer_store4(peer, par, p, base, s_out[4 * g], s_out[4 * g + 1], s_out[4 * g + 2], s_out[4 * g + 3]);
+            else for (int k = 0; k < 4 && base + k < rows; ++k) peer_store1(peer, par, p, base + k, s_out[4 * g + k]);
+        }
     }
 }
 
@@ -242,12 +256,13 @@ static int pick_rw(size_t fixed, size_t row_bytes, int rows) {
 }
 
 template <int RW, int PREP, int EPI>
-static int32_t launch_q4k_f(const Weight& w, const MatvecIn& in, float* y, const float* resid, size_t smem, int* flag, cudaStream_t s) {
+static int32_t launch_q4k_f(const Weight& w, const MatvecIn& in, float* y, const float* resid, size_t smem, int* flag, cudaStream_t s,
+                            const PeerOut& peer = PeerOut()) {
     static bool done = false;
     SK_TRY(set_smem_once(q4k_matvec_fused_kernel<RW, PREP, EPI>, &done));
     const int R = MF_WARPS * RW;
     SK_CUDA(launch_pdl(q4k_matvec_fused_kernel<RW, PREP, EPI>, dim3((w.rows + R - 1) / R), dim3(MF_THREADS), smem, s,
-                       (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr, in, w.cols, y, resid, flag));
+                       (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr, in, w.cols, y, resid, flag, peer));
     return SKAINET_CUDA_OK;
 }
 template <int RW, int PREP, int EPI>
@@ -276,21 +291,30 @@ static int32_t launch_q8_f(const Weight& w, const MatvecIn& in, float* y, const 
         default: SK_MF_PE(FN, 1)              \
     }
 
-int32_t launch_matvec_fused(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s) {
+int32_t launch_matvec_fused(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s,
+                            const PeerOut* peer) {
     int* flag = device_timeout_flag();
     if (w.rows <= 0) return 1;
+    if (peer && (w.enc != SKAINET_ENC_Q4_K || prep != PREP_QUANTIZED)) return 1;
     // Large weights go to the persistent ring kernel.
     const int64_t ring_min = (int64_t) RING_MIN_BYTES;
     if (w.packed_bytes >= ring_min) {
-        const int32_t st = launch_matvec_ring(w, in, prep, y, resid, s);
+        const int32_t st = launch_matvec_ring(w, in, prep, y, resid, s, peer);
         if (st != 1) return st;
     }
     const int epi = resid ? EPI_ADD : EPI_STORE;
     if (w.enc == SKAINET_ENC_Q4_K) {
-        const size_t fixed = (size_t) w.cols + w.cols / 16 + ((w.bpr * 4 + 15) & ~15) + 16 + MF_MAX_RW * 8 + 64;
+        const size_t fixed = (size_t) w.cols + w.cols / 16 + ((w.bpr * 4 + 15) & ~15) + 16 + MF_MAX_RW * 8 + 64 + 64;
         const int rw = pick_rw(fixed, (size_t) w.bpr * 144, w.rows);
         if (rw == 0) return 1;
         const size_t smem = fixed + (size_t) MF_WARPS * rw * w.bpr * 144;
+        if (peer) {
+            switch (rw) {
+                case 4: return launch_q4k_f<4, PREP_QUANTIZED, EPI_PEER>(w, in, y, resid, smem, flag, s, *peer);
+                case 2: return launch_q4k_f<2, PREP_QUANTIZED, EPI_PEER>(w, in, y, resid, smem, flag, s, *peer);
+                default: return launch_q4k_f<1, PREP_QUANTIZED, EPI_PEER>(w, in, y, resid, smem, flag, s, *peer);
+            }
+        }
         SK_MF_RW(launch_q4k_f)
     }
     if (w.enc == SKAINET_ENC_Q8_0) {

@@ -2,6 +2,7 @@
 #pragma once
 #include "common.cuh"
 #include "actquant.cuh"
+#include "comm.cuh"
 
 namespace sk {
 
@@ -9,7 +10,8 @@ namespace sk {
 enum { PREP_QUANTIZED = 0,   // already quantized in global memory (q8 for K-quants, split for Q8_0)
        PREP_F32 = 1,         // fp32 row, quantized inside the kernel
        PREP_NORM_F32 = 2 };  // fp32 row, RMS-normalised with gamma and eps, then quantized
-enum { EPI_STORE = 0, EPI_ADD = 1 };   // y = W x   |   y = resid + W x
+enum { EPI_STORE = 0, EPI_ADD = 1,     // y = W x   |   y = resid + W x
+       EPI_PEER = 2 };                 // (resid +) W x stored into every tensor-parallel rank's inbox instead of y
 
 struct MatvecIn {
     const float* x = nullptr;       // PREP_F32 / PREP_NORM_F32
@@ -21,10 +23,14 @@ struct MatvecIn {
 
 // y[rows] (= resid +) W . prep(x). Returns SKAINET_CUDA_OK, an error status, or 1 when the shape is
 // outside what the kernel takes (the caller then uses the general kernels).
-int32_t launch_matvec_fused(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s);
+// With a peer-output descriptor (tensor parallelism, Q4_K, activation already quantized) the result rows go to the
+// group's inboxes from the kernel's own epilogue and y is not written.
+int32_t launch_matvec_fused(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s,
+                            const PeerOut* peer = nullptr);
 
 // matvec_ring.cu: the persistent ring kernel for large weights, same activation forms and return convention.
-int32_t launch_matvec_ring(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s);
+int32_t launch_matvec_ring(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s,
+                           const PeerOut* peer = nullptr);
 // gemm_mma.cu: y[m][w.rows] (= resid +) for m >= 2 quantized activation rows on the tensor cores; 1 = not taken
 int32_t launch_gemm_mma(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s);
 int32_t launch_gemm_mma_q8(const Weight& w, ActSplit a, int m, float* y, const float* resid, cudaStream_t s);

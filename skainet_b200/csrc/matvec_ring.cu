@@ -34,22 +34,10 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(skd::smem_u32(bar)) : "memory");
 }
 
-// Work distribution. A CTA's first row group is its block index; every later one comes from a device counter
-// (sched[0], handed out in increasing order), so CTAs that finish early take more groups and the launch ends
-// without the tail a fixed round-robin split leaves when the group count is a few times the grid. The CTA that
-// retires last zeroes the pair for the launch that uses it next. Without a counter pair (sched == nullptr) the
-// split is the fixed round robin. Which CTA computes a row never changes the row's arithmetic.
-__device__ __forceinline__ int ring_next_group(int* sched, int rg, int lane) {
-    if (sched == nullptr) return rg + (int) gridDim.x;
-    int next = 0;
-    if (lane == 0) next = (int) gridDim.x + atomicAdd(sched, 1);
-    return next;
-}
-__device__ __forceinline__ void ring_retire(int* sched, int lane) {
-    if (sched == nullptr || lane != 0) return;
-    __threadfence();
-    if (atomicAdd(sched + 1, 1) == (int) gridDim.x - 1) { sched[0] = 0; sched[1] = 0; }
-}
+// Work distribution: row group g belongs to CTA g mod grid. Handing groups out through a device counter instead
+// (CTAs that finish early take more) was measured and dropped: the consumers are latency-bound, and learning
+// the group's index from shared memory after each stage barrier cost them more (48.5 against 42.2 us on the
+// 57344 x 8192 weight) than the evener finish gained.
 
 // ================================================================================================
 // Q4_K. Stage: qs part [NC][16][128] then hdr part [NC][16][16].
@@ -57,8 +45,7 @@ __device__ __forceinline__ void ring_retire(int* sched, int lane) {
 template <int NC, int PREP, int EPI>
 __global__ void __launch_bounds__((NC + 1) * 32)
 q4k_matvec_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ hdr, int rows, int bpr, MatvecIn in,
-                       int cols, float* __restrict__ y, const float* __restrict__ resid, int nstages, int* __restrict__ sched,
-                       int* __restrict__ timeout_flag) {
+                       int cols, float* __restrict__ y, const float* __restrict__ resid, int nstages, int* __restrict__ timeout_flag, PeerOut peer) {
     constexpr int S_QS = NC * 16 * 128, S_HDR = NC * 16 * 16, S_BYTES = S_QS + S_HDR;
     extern __shared__ __align__(128) uint8_t smem[];
     // layout: ring | q8 (swizzled) | split sub-block sums | d | reduce scratch | barriers
@@ -69,11 +56,12 @@ q4k_matvec_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict
     float* s_red = (float*) ((uint8_t*) s_d + ((bpr * 4 + 15) & ~15));
     uint64_t* full = (uint64_t*) (s_red + 8);
     uint64_t* empty = full + RG_MAX_STAGES;
-    int* s_rg = (int*) (empty + RG_MAX_STAGES);               // row group held by each stage (-1: no more work)
+    float* s_out = (float*) (empty + RG_MAX_STAGES);          // [2][NC]: a row group's results, gathered for the peer stores
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nrg = (rows + NC - 1) / NC;                     // row groups in the matrix
     const int ncg = (bpr + 15) >> 4;                          // column groups per row
+    const int my_rgs = (int) blockIdx.x < nrg ? (nrg - 1 - (int) blockIdx.x) / (int) gridDim.x + 1 : 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < nstages; ++s) { skd::mbar_init(full + s, 1); skd::mbar_init(empty + s, NC); }
@@ -85,19 +73,13 @@ q4k_matvec_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict
     if (warp == NC) {
         // ---------------- producer: the weights depend on no predecessor ----------------
         int stage = 0, round = 0;
-        for (int rg = (int) blockIdx.x;;) {
-            if (round > 0 && !skd::mbar_wait_bounded(empty + stage, (round - 1) & 1, timeout_flag)) return;
-            if (rg >= nrg) {                   // out of work: an empty stage tells the consumers
-                if (lane == 0) { s_rg[stage] = -1; mbar_arrive(full + stage); }
-                break;
-            }
-            const int next = ring_next_group(sched, rg, lane);       // in flight while this group's copies are posted
-            const int row0 = rg * NC, nr = min(NC, rows - row0);
+        for (int rgi = 0; rgi < my_rgs; ++rgi) {
+            const int row0 = ((int) blockIdx.x + rgi * (int) gridDim.x) * NC, nr = min(NC, rows - row0);
             for (int cg = 0; cg < ncg; ++cg) {
-                if (cg > 0 && round > 0 && !skd::mbar_wait_bounded(empty + stage, (round - 1) & 1, timeout_flag)) return;
+                if (round > 0 && !skd::mbar_wait_bounded(empty + stage, (round - 1) & 1, timeout_flag)) return;
                 const int b0 = cg * 16, nb = min(16, bpr - b0);
                 uint8_t* dst = s_ring + (size_t) stage * S_BYTES;
-                if (lane == 0) { s_rg[stage] = rg; skd::mbar_expect_tx(full + stage, (uint32_t) nr * nb * 144); }
+                if (lane == 0) skd::mbar_expect_tx(full + stage, (uint32_t) nr * nb * 144);
                 __syncwarp();
                 if (bpr == 16) {               // rows are contiguous: two copies move the whole stage
                     if (lane == 0) skd::bulk_g2s(dst, qs + (size_t) row0 * 16 * 128, (uint32_t) nr * 16 * 128, full + stage);
@@ -110,9 +92,7 @@ q4k_matvec_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict
                 }
                 if (++stage == nstages) { stage = 0; ++round; }
             }
-            rg = __shfl_sync(0xffffffffu, next, 0);
         }
-        ring_retire(sched, lane);
         skd::pdl_wait();
         return;
     }
@@ -137,9 +117,13 @@ q4k_matvec_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict
     uint2 bs = make_uint2(0, 0);
     float di = 0.0f;
     int stage = 0, phase = 0;
+    const int par = EPI == EPI_PEER ? (*reinterpret_cast<const volatile int*>(peer.round) & 1) : 0;
+    int obuf = 0;
 
-    for (bool first = true;; first = false) {
-        int row = 0;
+    // Rows past the end of the matrix (last group only) are computed on whatever the stage holds and never written.
+    for (int rgi = 0; rgi < my_rgs; ++rgi) {
+        const bool first = rgi == 0;
+        const int rg = (int) blockIdx.x + rgi * (int) gridDim.x;
         float acc = 0.0f;
         for (int cg = 0; cg < ncg; ++cg) {
             const int b = cg * 16 + slot;
@@ -155,12 +139,7 @@ q4k_matvec_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict
                 di = s_d[b];
             }
             if (!skd::mbar_wait_bounded(full + stage, phase, timeout_flag)) return;
-            if (cg == 0) {
-                const int rg = s_rg[stage];
-                if (rg < 0) return;                    // the producer ran out of work
-                row = rg * NC + warp;
-            }
-            if (live && row < rows) {
+            if (live) {
                 const uint8_t* st = s_ring + (size_t) stage * S_BYTES;
                 const uint8_t* qp = st + ((size_t) warp * 16 + slot) * 128 + h * 16;
                 const uint4 hd = skd::lds128(st + S_QS + ((size_t) warp * 16 + slot) * 16);
@@ -193,7 +172,20 @@ q4k_matvec_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict
             if (++stage == nstages) { stage = 0; phase ^= 1; }
         }
         const float v = skd::warp_sum(acc);
-        if (lane == 0 && row < rows) y[row] = EPI == EPI_ADD ? resid[row] + v : v;
+        const int row = rg * NC + warp;
+        if (EPI == EPI_PEER) {
+            // the group's NC rows, four at a time, into this rank's slot of every rank's inbox: the exchange of the
+            // group sum rides on the matvec instead of following it (two result buffers: one barrier per group)
+            if (lane == 0) s_out[obuf * NC + warp] = row < rows ? (resid ? resid[row] + v : v) : 0.0f;
+            consumer_sync<NC>();
+            if (warp == 0 && lane < (NC / 4) * peer.world) {
+                const int g = lane % (NC / 4), p = lane / (NC / 4), base = rg * NC + 4 * g;
+                const float* o = s_out + obuf * NC + 4 * g;
+                if (base + 3 < rows) peer_store4(peer, par, p, base, o[0], o[1], o[2], o[3]);
+                else for (int k = 0; k < 4 && base + k < rows; ++k) peer_store1(peer, par, p, base + k, o[k]);
+            }
+            obuf ^= 1;
+        } else if (lane == 0 && row < rows) y[row] = EPI == EPI_ADD ? resid[row] + v : v;
     }
 }
 
@@ -205,8 +197,7 @@ constexpr int RG8_COLS = 2048;
 template <int NC, int PREP, int EPI>
 __global__ void __launch_bounds__((NC + 1) * 32)
 q8_0_matvec_ring_kernel(const int8_t* __restrict__ codes, const __half* __restrict__ scales, int rows, int cols, MatvecIn in,
-                        float* __restrict__ y, const float* __restrict__ resid, int nstages, int* __restrict__ sched,
-                        int* __restrict__ timeout_flag) {
+                        float* __restrict__ y, const float* __restrict__ resid, int nstages, int* __restrict__ timeout_flag) {
     constexpr int S_CODES = NC * RG8_COLS, S_SC = NC * (RG8_COLS / 32) * 2, S_BYTES = S_CODES + S_SC;
     extern __shared__ __align__(128) uint8_t smem[];
     const int bpr = cols >> 5;
@@ -217,11 +208,11 @@ q8_0_matvec_ring_kernel(const int8_t* __restrict__ codes, const __half* __restri
     float* s_red = (float*) ((uint8_t*) s_dx + ((bpr * 4 + 15) & ~15));
     uint64_t* full = (uint64_t*) (s_red + 8);
     uint64_t* empty = full + RG_MAX_STAGES;
-    int* s_rg = (int*) (empty + RG_MAX_STAGES);
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nrg = (rows + NC - 1) / NC;
     const int ncg = (cols + RG8_COLS - 1) / RG8_COLS;
+    const int my_rgs = (int) blockIdx.x < nrg ? (nrg - 1 - (int) blockIdx.x) / (int) gridDim.x + 1 : 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < nstages; ++s) { skd::mbar_init(full + s, 1); skd::mbar_init(empty + s, NC); }
@@ -232,19 +223,13 @@ q8_0_matvec_ring_kernel(const int8_t* __restrict__ codes, const __half* __restri
 
     if (warp == NC) {
         int stage = 0, round = 0;
-        for (int rg = (int) blockIdx.x;;) {
-            if (round > 0 && !skd::mbar_wait_bounded(empty + stage, (round - 1) & 1, timeout_flag)) return;
-            if (rg >= nrg) {
-                if (lane == 0) { s_rg[stage] = -1; mbar_arrive(full + stage); }
-                break;
-            }
-            const int next = ring_next_group(sched, rg, lane);
-            const int row0 = rg * NC, nr = min(NC, rows - row0);
+        for (int rgi = 0; rgi < my_rgs; ++rgi) {
+            const int row0 = ((int) blockIdx.x + rgi * (int) gridDim.x) * NC, nr = min(NC, rows - row0);
             for (int cg = 0; cg < ncg; ++cg) {
-                if (cg > 0 && round > 0 && !skd::mbar_wait_bounded(empty + stage, (round - 1) & 1, timeout_flag)) return;
+                if (round > 0 && !skd::mbar_wait_bounded(empty + stage, (round - 1) & 1, timeout_flag)) return;
                 const int c0 = cg * RG8_COLS, nc = min(RG8_COLS, cols - c0);
                 uint8_t* dst = s_ring + (size_t) stage * S_BYTES;
-                if (lane == 0) { s_rg[stage] = rg; skd::mbar_expect_tx(full + stage, (uint32_t) nr * (nc + nc / 16)); }
+                if (lane == 0) skd::mbar_expect_tx(full + stage, (uint32_t) nr * (nc + nc / 16));
                 __syncwarp();
                 if (lane < 2 * nr) {
                     const int r = lane < nr ? lane : lane - nr;
@@ -253,9 +238,7 @@ q8_0_matvec_ring_kernel(const int8_t* __restrict__ codes, const __half* __restri
                 }
                 if (++stage == nstages) { stage = 0; ++round; }
             }
-            rg = __shfl_sync(0xffffffffu, next, 0);
         }
-        ring_retire(sched, lane);
         skd::pdl_wait();
         return;
     }
@@ -267,8 +250,9 @@ q8_0_matvec_ring_kernel(const int8_t* __restrict__ codes, const __half* __restri
     uint4 ah[4], al[4];
     float dx[4];
     int stage = 0, phase = 0;
-    for (bool first = true;; first = false) {
-        int row = 0;
+    for (int rgi = 0; rgi < my_rgs; ++rgi) {
+        const bool first = rgi == 0;
+        const int rg = (int) blockIdx.x + rgi * (int) gridDim.x;
         float acc = 0.0f;
         for (int cg = 0; cg < ncg; ++cg) {
             const int c0 = cg * RG8_COLS, nc = min(RG8_COLS, cols - c0);
@@ -283,12 +267,7 @@ q8_0_matvec_ring_kernel(const int8_t* __restrict__ codes, const __half* __restri
                 }
             }
             if (!skd::mbar_wait_bounded(full + stage, phase, timeout_flag)) return;
-            if (cg == 0) {
-                const int rg = s_rg[stage];
-                if (rg < 0) return;
-                row = rg * NC + warp;
-            }
-            if (row < rows) {
+            {
                 const uint8_t* st = s_ring + (size_t) stage * S_BYTES;
                 const int8_t* wr = (const int8_t*) st + (size_t) warp * RG8_COLS;
                 const __half* sr = (const __half*) (st + S_CODES) + (size_t) warp * (RG8_COLS / 32);
@@ -311,6 +290,7 @@ q8_0_matvec_ring_kernel(const int8_t* __restrict__ codes, const __half* __restri
             if (++stage == nstages) { stage = 0; phase ^= 1; }
         }
         const float v = skd::warp_sum(acc);
+        const int row = rg * NC + warp;
         if (lane == 0 && row < rows) y[row] = EPI == EPI_ADD ? resid[row] + v : v;
     }
 }
@@ -333,17 +313,6 @@ static bool plan_ring(size_t fixed, size_t stage_bytes_per_row, RingPlan* p) {
     return false;
 }
 
-// Dynamic hand-out only pays when CTAs take several row groups each; a launch whose grid covers every group in
-// one wave needs no counter.
-static int* ring_sched_for(int rows, const RingPlan& plan, cudaStream_t s) {
-#ifdef SK_RING_STATIC
-    return nullptr;
-#else
-    const int nrg = (rows + plan.nc - 1) / plan.nc;
-    return nrg > sm_count() * plan.cps ? stream_sched_pair(s) : nullptr;
-#endif
-}
-
 template <typename K>
 static int32_t set_smem_once(K kernel, bool* done) {
     if (!*done) {
@@ -364,44 +333,44 @@ static int32_t set_smem_once(K kernel, bool* done) {
     } while (0)
 
 template <int PREP, int EPI>
-static int32_t launch_q4k_ring(const Weight& w, const MatvecIn& in, float* y, const float* resid, const RingPlan& plan, int* sched, int* flag, cudaStream_t s) {
+static int32_t launch_q4k_ring(const Weight& w, const MatvecIn& in, float* y, const float* resid, const RingPlan& plan, int* flag, cudaStream_t s,
+                               const PeerOut& peer = PeerOut()) {
     if (plan.nc == 4)
-        SK_RG_LAUNCH((q4k_matvec_ring_kernel<4, PREP, EPI>), 4, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr, in, w.cols, y, resid, plan.nstages, sched, flag);
-    SK_RG_LAUNCH((q4k_matvec_ring_kernel<8, PREP, EPI>), 8, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr, in, w.cols, y, resid, plan.nstages, sched, flag);
+        SK_RG_LAUNCH((q4k_matvec_ring_kernel<4, PREP, EPI>), 4, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr, in, w.cols, y, resid, plan.nstages, flag, peer);
+    SK_RG_LAUNCH((q4k_matvec_ring_kernel<8, PREP, EPI>), 8, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr, in, w.cols, y, resid, plan.nstages, flag, peer);
 }
 template <int PREP, int EPI>
-static int32_t launch_q8_ring(const Weight& w, const MatvecIn& in, float* y, const float* resid, const RingPlan& plan, int* sched, int* flag, cudaStream_t s) {
+static int32_t launch_q8_ring(const Weight& w, const MatvecIn& in, float* y, const float* resid, const RingPlan& plan, int* flag, cudaStream_t s) {
     if (plan.nc == 4)
-        SK_RG_LAUNCH((q8_0_matvec_ring_kernel<4, PREP, EPI>), 4, (const int8_t*) w.qs, (const __half*) w.hdr, w.rows, w.cols, in, y, resid, plan.nstages, sched, flag);
-    SK_RG_LAUNCH((q8_0_matvec_ring_kernel<8, PREP, EPI>), 8, (const int8_t*) w.qs, (const __half*) w.hdr, w.rows, w.cols, in, y, resid, plan.nstages, sched, flag);
+        SK_RG_LAUNCH((q8_0_matvec_ring_kernel<4, PREP, EPI>), 4, (const int8_t*) w.qs, (const __half*) w.hdr, w.rows, w.cols, in, y, resid, plan.nstages, flag);
+    SK_RG_LAUNCH((q8_0_matvec_ring_kernel<8, PREP, EPI>), 8, (const int8_t*) w.qs, (const __half*) w.hdr, w.rows, w.cols, in, y, resid, plan.nstages, flag);
 }
 
 #define SK_RG_PE(FN)                                                                                              \
     switch (prep * 2 + (resid ? EPI_ADD : EPI_STORE)) {                                                           \
-        case PREP_QUANTIZED * 2 + EPI_STORE: return FN<PREP_QUANTIZED, EPI_STORE>(w, in, y, resid, plan, sched, flag, s); \
-        case PREP_QUANTIZED * 2 + EPI_ADD:   return FN<PREP_QUANTIZED, EPI_ADD>(w, in, y, resid, plan, sched, flag, s);   \
-        case PREP_F32 * 2 + EPI_STORE:       return FN<PREP_F32, EPI_STORE>(w, in, y, resid, plan, sched, flag, s);       \
-        case PREP_F32 * 2 + EPI_ADD:         return FN<PREP_F32, EPI_ADD>(w, in, y, resid, plan, sched, flag, s);         \
-        case PREP_NORM_F32 * 2 + EPI_STORE:  return FN<PREP_NORM_F32, EPI_STORE>(w, in, y, resid, plan, sched, flag, s);  \
-        default:                             return FN<PREP_NORM_F32, EPI_ADD>(w, in, y, resid, plan, sched, flag, s);    \
+        case PREP_QUANTIZED * 2 + EPI_STORE: return FN<PREP_QUANTIZED, EPI_STORE>(w, in, y, resid, plan, flag, s); \
+        case PREP_QUANTIZED * 2 + EPI_ADD:   return FN<PREP_QUANTIZED, EPI_ADD>(w, in, y, resid, plan, flag, s);   \
+        case PREP_F32 * 2 + EPI_STORE:       return FN<PREP_F32, EPI_STORE>(w, in, y, resid, plan, flag, s);       \
+        case PREP_F32 * 2 + EPI_ADD:         return FN<PREP_F32, EPI_ADD>(w, in, y, resid, plan, flag, s);         \
+        case PREP_NORM_F32 * 2 + EPI_STORE:  return FN<PREP_NORM_F32, EPI_STORE>(w, in, y, resid, plan, flag, s);  \
+        default:                             return FN<PREP_NORM_F32, EPI_ADD>(w, in, y, resid, plan, flag, s);    \
     }
 
-int32_t launch_matvec_ring(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s) {
+int32_t launch_matvec_ring(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s, const PeerOut* peer) {
     int* flag = device_timeout_flag();
     if (w.rows <= 0) return 1;
+    if (peer && (w.enc != SKAINET_ENC_Q4_K || prep != PREP_QUANTIZED)) return 1;
     RingPlan plan;
-    int* sched = nullptr;
     if (w.enc == SKAINET_ENC_Q4_K) {
-        const size_t fixed = (size_t) w.cols + w.cols / 16 + ((w.bpr * 4 + 15) & ~15) + 32 + 2 * RG_MAX_STAGES * 8 + RG_MAX_STAGES * 4;
+        const size_t fixed = (size_t) w.cols + w.cols / 16 + ((w.bpr * 4 + 15) & ~15) + 32 + 2 * RG_MAX_STAGES * 8 + 64;
         if (!plan_ring(fixed, 16 * 144, &plan)) return 1;
-        sched = ring_sched_for(w.rows, plan, s);
+        if (peer) return launch_q4k_ring<PREP_QUANTIZED, EPI_PEER>(w, in, y, resid, plan, flag, s, *peer);
         SK_RG_PE(launch_q4k_ring)
     }
     if (w.enc == SKAINET_ENC_Q8_0) {
         if (w.cols % 256 != 0) return 1;
-        const size_t fixed = (size_t) 2 * w.cols + ((w.bpr * 4 + 15) & ~15) + 32 + 2 * RG_MAX_STAGES * 8 + RG_MAX_STAGES * 4;
+        const size_t fixed = (size_t) 2 * w.cols + ((w.bpr * 4 + 15) & ~15) + 32 + 2 * RG_MAX_STAGES * 8 + 64;
         if (!plan_ring(fixed, RG8_COLS + RG8_COLS / 16, &plan)) return 1;
-        sched = ring_sched_for(w.rows, plan, s);
         SK_RG_PE(launch_q8_ring)
     }
     return 1;

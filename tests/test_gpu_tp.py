@@ -14,9 +14,9 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def run_world(world: int, d_model: int) -> dict:
+def run_world(world: int, d_model: int, extra_env: dict | None = None) -> dict:
     work = tempfile.mkdtemp(prefix=f"tp{world}_")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **(extra_env or {}))
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), str(r), str(world), work, str(d_model)], env=env,
                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
     outs = []
@@ -33,19 +33,69 @@ def run_world(world: int, d_model: int) -> dict:
     return dict(np.load(os.path.join(work, "out.npz")))
 
 
-# d_model 1024: group sums by the plain one-shot all-reduce, norm separately; 4096: the fused all-reduce + RMSNorm +
-# quantize kernel (two CTAs per row in one cluster) takes the sums inside the layer stack
-@pytest.mark.parametrize("d_model", [1024, 4096])
-def test_tp2_matches_single_gpu(gpu, d_model):
-    if gpu.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    one, two = run_world(1, d_model), run_world(2, d_model)
+def check_against_single(one: dict, many: dict, what: str) -> None:
     # same seeded tensors, sharded: logits agree to fp32 summation order (K-shards quantize their slice
     # of the activation exactly as the unsharded kernel does), tokens identical unless a near tie
-    rel_err_ok(two["logits0"], one["logits0"], 2e-3)
-    assert list(two["firsts"]) == list(one["firsts"])
-    if not np.array_equal(two["toks"], one["toks"]):
+    rel_err_ok(many["logits0"], one["logits0"], 2e-3)
+    assert list(many["firsts"]) == list(one["firsts"]), what
+    if not np.array_equal(many["toks"], one["toks"]):
         lg = one["logits"]
         srt = np.sort(lg, axis=1)
         margin = float(((srt[:, -1] - srt[:, -2]) / np.sqrt((lg ** 2).mean(axis=1))).min())
-        assert margin < 0.05, f"TP2 tokens differ without a near tie (margin {margin:.3f})"
+        assert margin < 0.05, f"{what}: tokens differ without a near tie (margin {margin:.3f})"
+
+
+_single = {}
+
+
+def single(d_model: int) -> dict:
+    if d_model not in _single:
+        _single[d_model] = run_world(1, d_model)
+    return _single[d_model]
+
+
+# d_model 1024: group sums by the plain peer-memory all-reduce, norm separately. d_model 4096 (two CTAs per row in one
+# cluster): by default the row-parallel matvecs store their partial rows into the peers' inboxes from their own epilogue
+# and a gather kernel sums + normalises + quantizes; SKAINET_TP_FUSE=1 keeps the exchange inside that kernel (what rows of
+# a batch or of a prompt use), =0 separates sum and norm, SKAINET_TP_ALLREDUCE=nccl takes every sum through NCCL.
+@pytest.mark.parametrize("d_model,env", [(1024, {}), (4096, {}), (4096, {"SKAINET_TP_FUSE": "1"}), (4096, {"SKAINET_TP_FUSE": "0"}),
+                                         (4096, {"SKAINET_TP_ALLREDUCE": "nccl"})])
+def test_tp2_matches_single_gpu(gpu, d_model, env):
+    if gpu.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    check_against_single(single(d_model), run_world(2, d_model, env), f"TP2 {env}")
+
+
+def test_tp4_matches_single_gpu(gpu):
+    if gpu.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    check_against_single(single(4096), run_world(4, 4096), "TP4")
+
+
+def test_two_models_on_two_gpus_from_one_thread(gpu, cuda_lib):
+    """One host thread drives a model on each of two GPUs: every call must use the flag, the SM count and the scratch of
+    the device its kernels run on. Same seed, same prompt: both models give the same tokens, and neither device reports
+    a bounded wait that gave up."""
+    if gpu.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from skainet_b200.llama import Llama, LlamaConfig
+    models = []
+    for dev in (0, 1):
+        gpu.set_device(dev)
+        m = Llama(LlamaConfig(2, 512, 8, 4, 64, 1024, 1000, max_seq=64))
+        m.synth(seed=9, std=0.05); m.finalize()
+        models.append(m)
+    outs = []
+    for rounds in range(2):                      # interleave the two devices
+        for m in models:
+            if rounds == 0:
+                outs.append([m.prefill([3, 1, 4, 1, 5])])
+            else:
+                outs[models.index(m)] += [int(t) for t in m.generate([outs[models.index(m)][0]], 6)[:, 0]]
+    assert outs[0] == outs[1]
+    for dev in (0, 1):
+        gpu.set_device(dev)
+        assert cuda_lib.skainet_cuda_device_status() == 0
+    for m in models:
+        m.free()
+    gpu.set_device(0)

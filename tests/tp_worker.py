@@ -21,7 +21,7 @@ def main():
     from skainet_b200.llama import Llama, LlamaConfig
     device.set_device(rank if device.device_count() > rank else 0)
     d_model = int(sys.argv[4]) if len(sys.argv) > 4 else 1024
-    cfg = LlamaConfig(2, d_model, 8, 4, 64, 2048, 1000, max_seq=64, max_batch=2, tp_rank=rank, tp_world=world)
+    cfg = LlamaConfig(2, d_model, 16, 4, 64, 2048, 1000, max_seq=64, max_batch=2, tp_rank=rank, tp_world=world)
     m = Llama(cfg)
     m.synth(seed=77, std=0.05)
     m.finalize()
