@@ -245,6 +245,14 @@ SKAINET_CUDA_API int32_t skainet_cuda_argmax_dev(const float* x, int32_t rows, i
 SKAINET_CUDA_API int32_t skainet_cuda_embed_dev(skainet_weight_t table, const int32_t* ids_dev, int32_t n, float* out,
     skainet_stream_t stream);
 
+/* The full attention contract of skainet_cuda_f32_sdpa (skainet_kernels.h:578-585) on device-resident fp32 tensors: what a
+ * resident-activation ops class calls for ops.scaledDotProductAttention (TensorOps.kt:410-458) so that q, k, v and the
+ * result never cross to the host. lengths_dev / mask_dev are device pointers (NULL = none). */
+SKAINET_CUDA_API int32_t skainet_cuda_sdpa_dev(const float* q, const float* k, const float* v, float* out,
+    int32_t batch, int32_t heads, int32_t kv_heads, int32_t seq_q, int32_t seq_kv, int32_t head_dim,
+    float scale, int32_t causal, int32_t window, int32_t right_context, const int32_t* lengths_dev,
+    const float* mask_dev, int32_t mask_b, int32_t mask_h, int32_t mask_q, int32_t mask_k, skainet_stream_t stream);
+
 /* GQA decode attention over an f16 KV cache resident in HBM: one query row per (batch, head),
  * split over the key axis with an fp32 softmax merge. k_cache / v_cache are binary16
  * [batch, kv_heads, cache_stride(keys), head_dim]; kv_len[b] keys are visible to batch b's query

@@ -100,7 +100,8 @@ SKAINET_CUDA_API int32_t skainet_cuda_llama_logits(skainet_model_t m, int32_t ba
  * and the number of kernels one step launches: the roofline inputs of the bench. out2 = {bytes, launches}. */
 SKAINET_CUDA_API int32_t skainet_cuda_llama_step_cost(skainet_model_t m, int32_t batch, int64_t* out2);
 /* Diagnostic: the first n floats of an activation buffer as the last step left it
- * (0 residual stream, 1 merged q|k|v with q rotated, 2 attention output, 3 gate|up, 4 q). */
+ * (0 residual stream, 1 merged q|k|v as projected — a decode step rotates q and k inside its attention kernel, a prompt
+ * chunk rotates q in place —, 2 attention output, 3 gate|up, 4 q). */
 SKAINET_CUDA_API int32_t skainet_cuda_llama_peek(skainet_model_t m, int32_t which, float* host_out, int64_t n);
 /* The stream the model runs on (for event timing by the caller). */
 SKAINET_CUDA_API int32_t skainet_cuda_llama_stream(skainet_model_t m, skainet_stream_t* out);

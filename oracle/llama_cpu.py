@@ -16,10 +16,11 @@ from . import ref as R
 
 
 class CpuLlama:
-    def __init__(self, cfg, weights: dict, norms: dict | None = None, use_ref: bool | None = None):
+    def __init__(self, cfg, weights: dict, norms: dict | None = None, use_ref: bool | None = None, encs: dict | None = None):
         """cfg: an object with the fields of skainet_b200.llama.LlamaConfig. weights: {(layer, name): packed uint8}
-        with names q,k,v,o,gate,up,down per layer and ('embed'), ('head') at layer -1. norms: {(layer, name): gamma}."""
-        self.cfg, self.w, self.norms = cfg, weights, norms or {}
+        with names q,k,v,o,gate,up,down per layer and ('embed'), ('head') at layer -1. norms: {(layer, name): gamma}.
+        encs: {(layer, name): encoding} for tensors whose encoding differs from the model's (a Q6_K tensor in a Q4_K model)."""
+        self.cfg, self.w, self.norms, self.encs = cfg, weights, norms or {}, encs or {}
         self.use_ref = (R.ref() is not None) if use_ref is None else use_ref
         self.k = [[] for _ in range(cfg.n_layers)]
         self.v = [[] for _ in range(cfg.n_layers)]
@@ -30,11 +31,11 @@ class CpuLlama:
         return self.norms.get((layer, name), np.ones(self.cfg.d_model, np.float32))
 
     def _mm(self, layer, name, x, rows, cols):
-        enc = self.cfg.table_enc if name in ("embed", "head") else self.cfg.linear_enc
+        enc = self.encs.get((layer, name), self.cfg.table_enc if name in ("embed", "head") else self.cfg.linear_enc)
         return R.matmul(enc, x, self.w[(layer, name)], cols, rows, "rm", use_ref=self.use_ref)
 
     def embed_row(self, token: int) -> np.ndarray:
-        enc = self.cfg.table_enc
+        enc = self.encs.get((-1, "embed"), self.cfg.table_enc)
         bpr = self.cfg.d_model // R.BLOCK_ELEMS[enc]
         nb = R.BLOCK_BYTES[enc] * bpr
         return R.dequant(enc, self.w[(-1, "embed")][token * nb:(token + 1) * nb])

@@ -73,6 +73,7 @@ SIGNATURES = {
     "skainet_cuda_rope_dev": [vp, vp, i32, i32, i32, f32, i32, vp],
     "skainet_cuda_argmax_dev": [vp, i32, i32, vp, vp],
     "skainet_cuda_embed_dev": [i64, vp, i32, vp, vp],
+    "skainet_cuda_sdpa_dev": [vp, vp, vp, vp] + [i32] * 6 + [f32] + [i32] * 3 + [vp, vp] + [i32] * 4 + [vp],
     "skainet_cuda_attn_decode_dev": [vp, vp, vp, vp, i32, i32, i32, i32, i64, vp, i32, f32, i32, vp],
     "skainet_cuda_attn_decode_noalloc_dev": [vp, vp, vp, vp, i32, i32, i32, i32, i64, vp, i32, f32, i32, vp],
     "skainet_cuda_f32_to_f16_dev": [vp, vp, i64, vp],

@@ -24,6 +24,10 @@ int32_t launch_attn_decode_quant(const float* q, int64_t q_row_stride, const __h
                                  int heads, int kv_heads, int d, int64_t cache_stride, const int32_t* kv_len, int max_kv_len,
                                  float scale, int window, void* scratch, bool split, ActQ8K oq, ActSplit os, cudaStream_t s);
 ActSplit act_split_layout(void* scratch, int m, int cols);
+// attention.cu: the attention of one decode step (rope and cache append inside the split-K kernel, then merge + quantizer)
+int32_t launch_attn_step(const float* qkv, __half* k, __half* v, float* out, int batch, int heads, int kv_heads, int d,
+                         int64_t cache_stride, const int32_t* kv_len, int max_kv_len, float scale, int window, const float* cos_t,
+                         const float* sin_t, int rope_mode, void* scratch, bool split, ActQ8K oq, ActSplit os, cudaStream_t s);
 
 }  // namespace sk
 

@@ -577,6 +577,26 @@ int32_t skainet_cuda_f32_to_f16_dev(const float* in, uint16_t* out, int64_t n, s
     return launch_f32_to_f16(in, out, n, as_stream(stream));
 }
 
+int32_t skainet_cuda_sdpa_dev(const float* q, const float* k, const float* v, float* out, int32_t batch, int32_t heads, int32_t kv_heads,
+                              int32_t seq_q, int32_t seq_kv, int32_t head_dim, float scale, int32_t causal, int32_t window, int32_t right_context,
+                              const int32_t* lengths_dev, const float* mask_dev, int32_t mask_b, int32_t mask_h, int32_t mask_q, int32_t mask_k,
+                              skainet_stream_t stream) {
+    if (batch <= 0 || heads <= 0 || kv_heads <= 0 || seq_q <= 0 || head_dim <= 0) return SKAINET_CUDA_OK;
+    SK_REQUIRE(q && out, "sdpa: null pointer");
+    SK_TRY(ensure_device());
+    cudaStream_t s = as_stream(stream);
+    if (seq_kv <= 0) { SK_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * (size_t) batch * heads * seq_q * head_dim, s)); return SKAINET_CUDA_OK; }
+    SK_REQUIRE(k && v, "sdpa: null pointer");
+    SK_REQUIRE(heads % kv_heads == 0, "sdpa: heads %d not a multiple of kv_heads %d", heads, kv_heads);
+    SK_REQUIRE(head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256, "sdpa: head_dim %d not in {32,64,128,256}", head_dim);
+    if (mask_dev) {
+        SK_REQUIRE((mask_b == 1 || mask_b == batch) && (mask_h == 1 || mask_h == heads || mask_h == kv_heads) &&
+                   (mask_q == 1 || mask_q == seq_q) && (mask_k == 1 || mask_k == seq_kv), "sdpa: mask dims do not broadcast");
+    }
+    return launch_sdpa_f32(q, k, v, out, batch, heads, kv_heads, seq_q, seq_kv, head_dim, scale, causal, window, right_context, lengths_dev,
+                           mask_dev, mask_b, mask_h, mask_q, mask_k, s);
+}
+
 int32_t skainet_cuda_attn_decode_dev(const float* q, const uint16_t* k_cache, const uint16_t* v_cache, float* out,
                                      int32_t batch, int32_t heads, int32_t kv_heads, int32_t head_dim, int64_t cache_stride,
                                      const int32_t* kv_len_dev, int32_t max_kv_len, float scale, int32_t window,

@@ -116,19 +116,66 @@ constexpr float LOG2E = 1.4426950408889634f;
 // exp(x) for x <= 0 through the ex2 unit (relative error ~1e-7 after the fp32 pre-scale)
 __device__ __forceinline__ float fast_exp(float x) { return exp2f(x * LOG2E); }
 
+// What the decode step folds into the attention kernel (FUSE): the rotary embedding of q and of the token's new key,
+// and the append of that key and value to the f16 cache. q, k, v of the token arrive unrotated in one merged row
+// [q heads | k heads | v heads]. (Folding the key splits inside the kernel as well, by the CTA of a kv head that
+// finishes last, was measured and dropped: that one CTA's serial pass over the records cost more than the merge
+// kernel's launch, 9.34 against 8.97 ms per step on the 70B shape.)
+struct AttnStep {
+    const float* qkv;            // [batch][(heads + 2 kv_heads) * D], unrotated
+    const float* cos_t;          // rotation factors [max_seq][D/2]
+    const float* sin_t;
+    __half* kc_w;                // the caches, writable: the key / value of position kv_len - 1 are written here
+    __half* vc_w;
+    int rope_mode;               // 0: pairs (2i, 2i+1), 1: pairs (i, i + D/2)
+};
+
+// (x, y) of one rotation pair -> rotated, each product and sum rounded on its own (the restatement's order)
+__device__ __forceinline__ void rope_pair(float& x, float& y, float c, float sn) {
+    const float rx = __fsub_rn(__fmul_rn(x, c), __fmul_rn(y, sn)), ry = __fadd_rn(__fmul_rn(x, sn), __fmul_rn(y, c));
+    x = rx; y = ry;
+}
+// Four consecutive elements [e0, e0+4) of a head row at `base`, rotated for position p.
 template <int D>
+__device__ __forceinline__ float4 rope_load4(const float* __restrict__ base, int e0, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                             int p, int mode) {
+    float4 f = __ldg((const float4*) (base + e0));
+    const float* cr = cos_t + (size_t) p * (D / 2);
+    const float* sr = sin_t + (size_t) p * (D / 2);
+    if (mode == 0) {
+        const int i = e0 >> 1;
+        rope_pair(f.x, f.y, __ldg(cr + i), __ldg(sr + i));
+        rope_pair(f.z, f.w, __ldg(cr + i + 1), __ldg(sr + i + 1));
+    } else {
+        const bool lower = e0 < D / 2;
+        const int i = lower ? e0 : e0 - D / 2;
+        float4 o = __ldg((const float4*) (base + (lower ? e0 + D / 2 : e0 - D / 2)));
+        float* fa = &f.x; float* oa = &o.x;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float x = lower ? fa[k] : oa[k], y = lower ? oa[k] : fa[k];
+            rope_pair(x, y, __ldg(cr + i + k), __ldg(sr + i + k));
+            fa[k] = lower ? x : y;
+        }
+    }
+    return f;
+}
+
+template <int D, bool FUSE>
 __global__ void __launch_bounds__(AM_WARPS * 32)
 attn_decode_mma_kernel(const float* __restrict__ q, int64_t q_row_stride, const __half* __restrict__ kc, const __half* __restrict__ vc,
                        float* __restrict__ part, int heads, int kv_heads, int G, int64_t cache_stride,
                        const int32_t* __restrict__ kv_len, float scale, int window, int chunk, int splits, float* __restrict__ out_direct,
-                       int max_len, int ring_start, int ring_cap) {
+                       int max_len, int ring_start, int ring_cap, AttnStep step) {
     constexpr int S4 = D / 32;     // chunks of a K row per lane
     constexpr int KS = D / 16;     // k-steps of the score contraction
     constexpr int U = D / 64;      // chunks of a V row per lane
     constexpr int NT = D / 8;      // 8-dim output tiles
-    __shared__ float sm_m[AM_WARPS][8], sm_l[AM_WARPS][8], sm_c[AM_WARPS][8];
+    constexpr int NP = AM_WARPS + (FUSE ? 1 : 0);      // partial records merged per CTA: one per warp (+ the token's own key)
+    __shared__ float sm_m[NP][8], sm_l[NP][8], sm_c[NP][8];
     __shared__ uint32_t sm_q[KS][4][32];
-    __shared__ float sm_acc[AM_WARPS][8][D + 4];
+    __shared__ float sm_acc[NP][8][D + 4];
+    __shared__ float sm_knew[FUSE ? D : 1];
     skd::pdl_launch_dependents();
     skd::pdl_wait();
 
@@ -137,7 +184,11 @@ attn_decode_mma_kernel(const float* __restrict__ q, int64_t q_row_stride, const 
     const int len = min(__ldg(kv_len + b), max_len);      // never past what the launch was sized (and the cache allocated) for
     int first = 0;
     if (window > 0 && len - window > first) first = len - window;
-    const int begin = max(first, split * chunk), stop = min(len, (split + 1) * chunk);
+    // FUSE: the newest key (index len - 1) is not in the cache yet; the CTA whose split would hold it appends it and
+    // accounts for it as one more partial record, so nobody reads that cache slot in this launch.
+    const int keys = FUSE ? len - 1 : len;
+    const bool owner = FUSE && len > 0 && split == min((len - 1) / chunk, splits - 1);
+    const int begin = max(first, split * chunk), stop = min(keys, (split + 1) * chunk);
 
     const __half* kb = kc + ((int64_t) b * kv_heads + kvh) * cache_stride * D;
     const __half* vb = vc + ((int64_t) b * kv_heads + kvh) * cache_stride * D;
@@ -176,15 +227,66 @@ attn_decode_mma_kernel(const float* __restrict__ q, int64_t q_row_stride, const 
 
     // q of head g as A fragments, per k-step {hi(k 2t..), lo(k 2t..), hi(k 2t+8..), lo(k 2t+8..)}: warp w
     // converts k-step w (k-step 2s+j covers floats 4j..4j+3 of chunk t+4s) and all warps read the result.
+    const int pos_new = len - 1;                       // FUSE: the position being decoded
     for (int ks = warp; ks < KS; ks += AM_WARPS) {
         float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (g < G) f = __ldg((const float4*) (q + (int64_t) b * q_row_stride + (int64_t) (kvh * G + g) * D + (t + 4 * (ks >> 1)) * 8 + 4 * (ks & 1)));
+        if (g < G) {
+            const float* qrow = q + (int64_t) b * q_row_stride + (int64_t) (kvh * G + g) * D;
+            const int e0 = (t + 4 * (ks >> 1)) * 8 + 4 * (ks & 1);
+            f = FUSE ? rope_load4<D>(qrow, e0, step.cos_t, step.sin_t, pos_new, step.rope_mode) : __ldg((const float4*) (qrow + e0));
+        }
         uint32_t h0, l0, h1, l1;
         split_pack(f.x, f.y, h0, l0);
         split_pack(f.z, f.w, h1, l1);
         sm_q[ks][0][lane] = h0; sm_q[ks][1][lane] = l0; sm_q[ks][2][lane] = h1; sm_q[ks][3][lane] = l1;
     }
+    if (FUSE) {
+        // the token's own key and value: rotated / rounded to binary16 exactly as the cache will hold them, appended by
+        // the owner CTA, and entered as partial record AM_WARPS (score of head hg against the new key, weight 1, its value)
+        if (owner) {
+            const float* krow = step.qkv + (int64_t) b * q_row_stride + (int64_t) (heads + kvh) * D;
+            const float* vrow = step.qkv + (int64_t) b * q_row_stride + (int64_t) (heads + kv_heads + kvh) * D;
+            int sl = pos_new + ring_start;
+            if (ring_cap > 0 && sl >= ring_cap) sl -= ring_cap;
+            __half* kdst = step.kc_w + (((int64_t) b * kv_heads + kvh) * cache_stride + sl) * D;
+            __half* vdst = step.vc_w + (((int64_t) b * kv_heads + kvh) * cache_stride + sl) * D;
+            if (threadIdx.x < D / 4) {
+                const int e0 = threadIdx.x * 4;
+                const float4 kf = rope_load4<D>(krow, e0, step.cos_t, step.sin_t, pos_new, step.rope_mode);
+                const __half2 k01 = __floats2half2_rn(kf.x, kf.y), k23 = __floats2half2_rn(kf.z, kf.w);
+                *reinterpret_cast<__half2*>(kdst + e0) = k01; *reinterpret_cast<__half2*>(kdst + e0 + 2) = k23;
+                const float2 a = __half22float2(k01), c2 = __half22float2(k23);
+                sm_knew[e0] = a.x; sm_knew[e0 + 1] = a.y; sm_knew[e0 + 2] = c2.x; sm_knew[e0 + 3] = c2.y;
+            } else if (threadIdx.x < D / 2) {
+                const int e0 = (threadIdx.x - D / 4) * 4;
+                const float4 vf = __ldg((const float4*) (vrow + e0));
+                const __half2 v01 = __floats2half2_rn(vf.x, vf.y), v23 = __floats2half2_rn(vf.z, vf.w);
+                *reinterpret_cast<__half2*>(vdst + e0) = v01; *reinterpret_cast<__half2*>(vdst + e0 + 2) = v23;
+                const float2 a = __half22float2(v01), c2 = __half22float2(v23);
+#pragma unroll
+                for (int hg = 0; hg < 8; ++hg) { sm_acc[AM_WARPS][hg][e0] = a.x; sm_acc[AM_WARPS][hg][e0 + 1] = a.y; sm_acc[AM_WARPS][hg][e0 + 2] = c2.x; sm_acc[AM_WARPS][hg][e0 + 3] = c2.y; }
+            }
+        } else {
+            for (int i = threadIdx.x; i < 8 * (D + 4); i += AM_WARPS * 32) (&sm_acc[AM_WARPS][0][0])[i] = 0.0f;
+        }
+    }
     __syncthreads();
+    if (FUSE) {
+        // warp hg: score of head hg against the new key (fp32 rotated q, the cache's binary16 key)
+        const int hg = warp;
+        float sc_new = MASKED;
+        if (owner && hg < G) {
+            const float* qrow = q + (int64_t) b * q_row_stride + (int64_t) (kvh * G + hg) * D;
+            float p = 0.0f;
+#pragma unroll
+            for (int e0 = lane * 4; e0 < D; e0 += 128) {
+                const float4 f = rope_load4<D>(qrow, e0, step.cos_t, step.sin_t, pos_new, step.rope_mode);
+                p += f.x * sm_knew[e0] + f.y * sm_knew[e0 + 1] + f.z * sm_knew[e0 + 2] + f.w * sm_knew[e0 + 3];
+            }
+            sc_new = skd::warp_sum(p) * scale;
+        }
+        if (lane == 0) { sm_m[AM_WARPS][hg] = sc_new; sm_l[AM_WARPS][hg] = (owner && hg < G) ? 1.0f : 0.0f; }
+    }
     uint32_t qa[KS][4];
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks)
@@ -263,23 +365,24 @@ attn_decode_mma_kernel(const float* __restrict__ q, int64_t q_row_stride, const 
             sm_acc[warp][g][8 * (2 * t + 1 + 8 * u) + i] = o[u * 8 + i][1] + o[u * 8 + i][3];
         }
     __syncthreads();
-    if (threadIdx.x < 8 * AM_WARPS) {       // weight of (warp w, head hg) in the merged record
+    if (threadIdx.x < 8 * NP) {             // weight of (record w, head hg) in the merged record
         const int w = threadIdx.x >> 3, hg = threadIdx.x & 7;
         float mxx = MASKED;
 #pragma unroll
-        for (int w2 = 0; w2 < AM_WARPS; ++w2) mxx = fmaxf(mxx, sm_m[w2][hg]);
-        sm_c[w][hg] = fast_exp(sm_m[w][hg] - mxx);
+        for (int w2 = 0; w2 < NP; ++w2) mxx = fmaxf(mxx, sm_m[w2][hg]);
+        sm_c[w][hg] = sm_m[w][hg] > 0.5f * MASKED ? fast_exp(sm_m[w][hg] - mxx) : 0.0f;
     }
     __syncthreads();
+    const bool direct = out_direct != nullptr;
     for (int idx = threadIdx.x; idx < G * D; idx += AM_WARPS * 32) {
         const int hg = idx / D, dd = idx % D;
         float at = 0.0f;
 #pragma unroll
-        for (int w = 0; w < AM_WARPS; ++w) at += sm_c[w][hg] * sm_acc[w][hg][dd];
-        if (out_direct) {            // a single key split: this is the final result, no records and no merge launch
+        for (int w = 0; w < NP; ++w) at += sm_c[w][hg] * sm_acc[w][hg][dd];
+        if (direct) {                // a single key split: this is the final result, no records and no merge launch
             float lt = 0.0f;
 #pragma unroll
-            for (int w = 0; w < AM_WARPS; ++w) lt += sm_c[w][hg] * sm_l[w][hg];
+            for (int w = 0; w < NP; ++w) lt += sm_c[w][hg] * sm_l[w][hg];
             out_direct[((int64_t) b * heads + kvh * G + hg) * D + dd] = lt > 0.0f ? at / lt : 0.0f;
             continue;
         }
@@ -288,7 +391,7 @@ attn_decode_mma_kernel(const float* __restrict__ q, int64_t q_row_stride, const 
         if (dd == 0) {
             float mxx = MASKED, lt = 0.0f;
 #pragma unroll
-            for (int w = 0; w < AM_WARPS; ++w) { mxx = fmaxf(mxx, sm_m[w][hg]); lt += sm_c[w][hg] * sm_l[w][hg]; }
+            for (int w = 0; w < NP; ++w) { mxx = fmaxf(mxx, sm_m[w][hg]); lt += sm_c[w][hg] * sm_l[w][hg]; }
             rec[0] = mxx; rec[1] = lt;
         }
     }
@@ -359,8 +462,8 @@ static void launch_decode_dg(const float* q, const __half* k, const __half* v, f
                              int ring_cap, cudaStream_t s) {
     dim3 grid(splits, kv_heads, batch);
     const bool direct = splits == 1 && !always_partials;
-    launch_pdl(attn_decode_mma_kernel<D>, grid, dim3(AM_WARPS * 32), 0, s, q, q_row_stride, k, v, part, heads, kv_heads, G, cache_stride, kv_len,
-               scale, window, chunk, splits, direct ? out : (float*) nullptr, max_len, ring_start, ring_cap);
+    launch_pdl(attn_decode_mma_kernel<D, false>, grid, dim3(AM_WARPS * 32), 0, s, q, q_row_stride, k, v, part, heads, kv_heads, G, cache_stride, kv_len,
+               scale, window, chunk, splits, direct ? out : (float*) nullptr, max_len, ring_start, ring_cap, AttnStep());
     if (!always_partials && !direct) launch_pdl(attn_merge_kernel<D>, dim3(batch * heads), dim3(D * MG), 0, s, (const float*) part, out, splits);
 }
 
@@ -383,6 +486,41 @@ int32_t launch_attn_decode_ring(const float* q, const __half* k, const __half* v
                                 void* scratch, cudaStream_t s) {
     return attn_decode_impl(q, (int64_t) heads * d, k, v, out, 1, heads, kv_heads, d, cache_stride, kv_len_dev, len, scale, 0,
                             scratch, 0, nullptr, s, ring_start, ring_cap);
+}
+
+// The attention of one decode step: q | k | v of the new token arrive unrotated in qkv [batch][(heads + 2 kv_heads) * d];
+// the split-K kernel rotates q and the new key, appends key and value to the f16 caches at position kv_len - 1 and attends
+// over the kv_len visible keys; the merge kernel folds the key splits and leaves out [batch][heads * d] together with its
+// quantized form for the projection that follows. Two launches (the separate rope + append kernel is gone). Needs
+// heads * d to be a multiple of 256; returns 1 when it is not (the caller then runs the separate kernels).
+int32_t launch_attn_step(const float* qkv, __half* k, __half* v, float* out, int batch, int heads, int kv_heads, int d,
+                         int64_t cache_stride, const int32_t* kv_len, int max_kv_len, float scale, int window, const float* cos_t,
+                         const float* sin_t, int rope_mode, void* scratch, bool split, ActQ8K oq, ActSplit os, cudaStream_t s) {
+    if (batch <= 0 || heads <= 0) return SKAINET_CUDA_OK;
+    const int G = heads / kv_heads;
+    if ((heads * d) % 256 != 0 || G > 8 || (G & (G - 1)) != 0 || (d != 64 && d != 128)) return 1;
+    const int splits = decode_splits(batch, kv_heads, std::max(1, max_kv_len));
+    int chunk = (std::max(1, max_kv_len) + splits - 1) / splits;
+    chunk = (chunk + 31) & ~31;
+    AttnStep st;
+    st.qkv = qkv; st.cos_t = cos_t; st.sin_t = sin_t; st.kc_w = k; st.vc_w = v; st.rope_mode = rope_mode;
+    const int64_t stride = (int64_t) (heads + 2 * kv_heads) * d;
+    dim3 grid(splits, kv_heads, batch);
+    if (d == 128)
+        SK_CUDA(launch_pdl(attn_decode_mma_kernel<128, true>, grid, dim3(AM_WARPS * 32), 0, s, qkv, stride, (const __half*) k, (const __half*) v, (float*) scratch,
+                           heads, kv_heads, G, cache_stride, kv_len, scale, window, chunk, splits, (float*) nullptr, std::max(1, max_kv_len), 0, 0, st));
+    else
+        SK_CUDA(launch_pdl(attn_decode_mma_kernel<64, true>, grid, dim3(AM_WARPS * 32), 0, s, qkv, stride, (const __half*) k, (const __half*) v, (float*) scratch,
+                           heads, kv_heads, G, cache_stride, kv_len, scale, window, chunk, splits, (float*) nullptr, std::max(1, max_kv_len), 0, 0, st));
+    dim3 mgrid(heads * d / 256, batch);
+    if (d == 128) {
+        if (split) SK_CUDA(launch_pdl(attn_merge_quant_kernel<128, true>, mgrid, dim3(256 * MG), 0, s, (const float*) scratch, out, splits, heads, oq, os));
+        else SK_CUDA(launch_pdl(attn_merge_quant_kernel<128, false>, mgrid, dim3(256 * MG), 0, s, (const float*) scratch, out, splits, heads, oq, os));
+    } else {
+        if (split) SK_CUDA(launch_pdl(attn_merge_quant_kernel<64, true>, mgrid, dim3(256 * MG), 0, s, (const float*) scratch, out, splits, heads, oq, os));
+        else SK_CUDA(launch_pdl(attn_merge_quant_kernel<64, false>, mgrid, dim3(256 * MG), 0, s, (const float*) scratch, out, splits, heads, oq, os));
+    }
+    return SKAINET_CUDA_OK;
 }
 
 // Decode attention whose result is also quantized for the projection that follows (q8 per 256 for

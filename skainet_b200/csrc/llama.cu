@@ -176,8 +176,10 @@ static int32_t dalloc(T** p, size_t count) {
     return SKAINET_CUDA_OK;
 }
 
+// A K-quant model takes Q6_K tensors beside its Q4_K ones (real Q4_K_M files carry ffn_down, attn_v and the output
+// head that way): both consume the same int8-per-256 activation (native/src/q6k_matmul.c:53-67 is the Q4_K quantizer).
 static int32_t check_weight_shape(const Weight* w, int enc, int rows, int cols, const char* what) {
-    SK_REQUIRE(w->enc == enc, "%s: encoding %d, model expects %d", what, w->enc, enc);
+    SK_REQUIRE(w->enc == enc || (enc == SKAINET_ENC_Q4_K && w->enc == SKAINET_ENC_Q6_K), "%s: encoding %d, model expects %d", what, w->enc, enc);
     SK_REQUIRE(w->rows == rows && w->cols == cols, "%s: shape [%d, %d], model expects [%d, %d]", what, w->rows, w->cols, rows, cols);
     return SKAINET_CUDA_OK;
 }
@@ -227,8 +229,21 @@ static int32_t body(Model& m, int rows, bool prefill, int seq, int kv_bound, cud
                     bool* final_prepared = nullptr) {
     const auto& c = m.cfg;
     const int D = c.head_dim, H = m.heads_l, HK = m.kv_heads_l, qkv_dim = (H + 2 * HK) * D;
-    const bool lin_split = c.linear_enc == SKAINET_ENC_Q8_0;
+    const bool lin_split = c.linear_enc == SKAINET_ENC_Q8_0;      // Q8_0 linears take the two-term activation, K-quants int8 per 256
     const float scale = 1.0f / sqrtf((float) D);
+    // Projections that share one input and write side by side into out[rows][stride]: one merged weight when their
+    // encodings agree (finalize merged them), else one linear per part over the same prepared activation.
+    auto projections = [&](Weight* merged, std::initializer_list<Weight*> parts, bool prepared, const float* gamma, float* out, int stride) -> int32_t {
+        if (merged) return prepared ? linear(m, *merged, rows, out, nullptr, s) : linear_normed(m, *merged, m.x, gamma, rows, out, s);
+        if (!prepared) SK_TRY(prep<PK_NORM>(m, m.x, gamma, rows, c.d_model, lin_split, s));
+        int off = 0;
+        for (Weight* w : parts) {
+            if (rows == 1) SK_TRY(linear(m, *w, 1, out + off, nullptr, s));
+            else { SK_TRY(linear(m, *w, rows, m.q, nullptr, s)); SK_TRY(launch_scatter_rows(m.q, out, rows, stride, off, w->rows, s)); }
+            off += w->rows;
+        }
+        return SKAINET_CUDA_OK;
+    };
     const bool tp = c.tp_world > 1, rank0 = c.tp_rank == 0;
     // Under TP the group sum of a row-parallel projection is fused with the RMSNorm + quantizer that follows it
     // when the peer-memory kernel applies; `normed` says the next layer's input is already prepared.
@@ -266,9 +281,24 @@ static int32_t body(Model& m, int rows, bool prefill, int seq, int kv_bound, cud
     bool normed = false;
     for (int l = 0; l < c.n_layers; ++l) {
         Layer& L = m.layers[l];
-        if (normed) SK_TRY(linear(m, *L.wqkv, rows, m.qkv, nullptr, s));       // the group sum already left the quantized row
-        else SK_TRY(linear_normed(m, *L.wqkv, m.x, L.g_attn, rows, m.qkv, s));
+        SK_TRY(projections(L.wqkv, {L.wq, L.wk, L.wv}, normed, L.g_attn, m.qkv, qkv_dim));    // normed: the group sum already left the quantized row
         normed = false;
+        const bool o_split = L.wo->enc == SKAINET_ENC_Q8_0;
+        if (!prefill) {          // rope of q and of the new key and the cache append ride inside the split-K attention kernel
+            ActQ8K oq = {nullptr, nullptr, nullptr}; ActSplit os = {nullptr, nullptr, nullptr};
+            if (o_split) os = act_split_layout(m.act, rows, H * D); else oq = act_q8k_layout(m.act, rows, H * D);
+            const int32_t st = launch_attn_step(m.qkv, L.kc, L.vc, m.attn, rows, H, HK, D, c.max_seq, m.kv_len, kv_bound, scale, 0, m.cos_t, m.sin_t,
+                                                c.rope_mode, m.attn_scratch, o_split, oq, os, s);
+            if (st != 1 && st != SKAINET_CUDA_OK) return st;
+            if (st == SKAINET_CUDA_OK) {
+                bool ffn_ready = false;
+                SK_TRY(row_parallel(*L.wo, L.g_ffn, &ffn_ready));
+                SK_TRY(projections(L.wgu, {L.wgate, L.wup}, ffn_ready, L.g_ffn, m.gu, 2 * m.ffn_l));
+                SK_TRY(prep<PK_SWIGLU>(m, m.gu, nullptr, rows, m.ffn_l, L.wdown->enc == SKAINET_ENC_Q8_0, s));
+                SK_TRY(row_parallel(*L.wdown, l + 1 < c.n_layers ? m.layers[l + 1].g_attn : final_gamma, &normed));
+                continue;
+            }
+        }
         SK_CUDA(launch_pdl(rope_append_kernel, dim3(rows, H + 2 * HK), dim3(D / 2), 0, s, m.qkv, H, HK, D, (const float*) m.cos_t,
                            (const float*) m.sin_t, (const int32_t*) m.pos, (const int32_t*) (prefill ? m.row_seq : nullptr), prefill ? 1 : 0,
                            L.kc, L.vc, (int64_t) c.max_seq, c.rope_mode));
@@ -280,18 +310,17 @@ static int32_t body(Model& m, int rows, bool prefill, int seq, int kv_bound, cud
             SK_TRY(launch_sdpa_cache(m.q, kc, vc, m.attn, 1, H, HK, rows, kv_bound, c.max_seq, D, scale, 0, m.pos + seq, s));
         } else if (fused_attn) {   // q read in place from the merged buffer; merge of the key splits quantizes for o_proj
             ActQ8K oq = {nullptr, nullptr, nullptr}; ActSplit os = {nullptr, nullptr, nullptr};
-            if (lin_split) os = act_split_layout(m.act, rows, H * D); else oq = act_q8k_layout(m.act, rows, H * D);
+            if (o_split) os = act_split_layout(m.act, rows, H * D); else oq = act_q8k_layout(m.act, rows, H * D);
             SK_TRY(launch_attn_decode_quant(m.qkv, qkv_dim, L.kc, L.vc, m.attn, rows, H, HK, D, c.max_seq, m.kv_len, kv_bound, scale, 0,
-                                            m.attn_scratch, lin_split, oq, os, s));
+                                            m.attn_scratch, o_split, oq, os, s));
         } else {
             SK_TRY(launch_attn_decode(m.q, L.kc, L.vc, m.attn, rows, H, HK, D, c.max_seq, m.kv_len, kv_bound, scale, 0, m.attn_scratch, s));
         }
-        if (!fused_attn) SK_TRY(prep<PK_QUANT>(m, m.attn, nullptr, rows, H * D, lin_split, s));
+        if (!fused_attn) SK_TRY(prep<PK_QUANT>(m, m.attn, nullptr, rows, H * D, o_split, s));
         bool ffn_ready = false;
         SK_TRY(row_parallel(*L.wo, L.g_ffn, &ffn_ready));
-        if (ffn_ready) SK_TRY(linear(m, *L.wgu, rows, m.gu, nullptr, s));
-        else SK_TRY(linear_normed(m, *L.wgu, m.x, L.g_ffn, rows, m.gu, s));
-        SK_TRY(prep<PK_SWIGLU>(m, m.gu, nullptr, rows, m.ffn_l, lin_split, s));
+        SK_TRY(projections(L.wgu, {L.wgate, L.wup}, ffn_ready, L.g_ffn, m.gu, 2 * m.ffn_l));
+        SK_TRY(prep<PK_SWIGLU>(m, m.gu, nullptr, rows, m.ffn_l, L.wdown->enc == SKAINET_ENC_Q8_0, s));
         SK_TRY(row_parallel(*L.wdown, l + 1 < c.n_layers ? m.layers[l + 1].g_attn : final_gamma, &normed));
     }
     if (final_prepared) *final_prepared = normed;
@@ -649,10 +678,16 @@ int32_t skainet_cuda_llama_finalize(skainet_model_t h) {
     for (int l = 0; l < m->cfg.n_layers; ++l) {
         Layer& L = m->layers[l];
         SK_REQUIRE(L.wq && L.wk && L.wv && L.wo && L.wgate && L.wup && L.wdown, "llama_finalize: layer %d is missing a weight", l);
-        SK_TRY(weight_concat_rows(L.wq, L.wk, L.wv, &L.wqkv));
-        SK_TRY(weight_concat_rows(L.wgate, L.wup, nullptr, &L.wgu));
-        // the merged copies replace the parts
-        for (Weight** w : {&L.wq, &L.wk, &L.wv, &L.wgate, &L.wup}) { weight_release(*w); *w = nullptr; }
+        // parts of one encoding are merged and the merged copy replaces them; mixed encodings (a Q6_K attn_v beside Q4_K
+        // q and k) keep their parts and run as separate linears over the same activation
+        if (L.wq->enc == L.wk->enc && L.wk->enc == L.wv->enc) {
+            SK_TRY(weight_concat_rows(L.wq, L.wk, L.wv, &L.wqkv));
+            for (Weight** w : {&L.wq, &L.wk, &L.wv}) { weight_release(*w); *w = nullptr; }
+        }
+        if (L.wgate->enc == L.wup->enc) {
+            SK_TRY(weight_concat_rows(L.wgate, L.wup, nullptr, &L.wgu));
+            for (Weight** w : {&L.wgate, &L.wup}) { weight_release(*w); *w = nullptr; }
+        }
     }
     // rotation factors: angle = pos * theta^(-2i/d) in double, rounded once
     const int half = m->cfg.head_dim / 2;
@@ -826,7 +861,8 @@ int32_t skainet_cuda_llama_step_cost(skainet_model_t h, int32_t batch, int64_t* 
     SK_REQUIRE(batch >= 1 && batch <= m->cfg.max_batch && out2, "llama_step_cost: bad arguments");
     const auto& c = m->cfg;
     int64_t bytes = m->head->packed_bytes;
-    for (const auto& L : m->layers) bytes += L.wqkv->packed_bytes + L.wo->packed_bytes + L.wgu->packed_bytes + L.wdown->packed_bytes;
+    for (const auto& L : m->layers)
+        for (const Weight* w : {L.wqkv, L.wq, L.wk, L.wv, L.wo, L.wgu, L.wgate, L.wup, L.wdown}) if (w) bytes += w->packed_bytes;
     for (int b = 0; b < batch; ++b)
         bytes += (int64_t) c.n_layers * 2 * m->kv_heads_l * c.head_dim * 2 * (m->host_pos[b] + 1)            // K and V visible, f16
                + (int64_t) (c.d_model / block_elems(c.table_enc)) * block_bytes(c.table_enc);                  // one table row

@@ -278,7 +278,10 @@ int32_t launch_matvec(const Weight& w, const float* x, const void* act_scratch, 
                       cudaStream_t s) {
     if (m == 0 || w.rows == 0) return SKAINET_CUDA_OK;
     if (w.enc == SKAINET_ENC_Q6_K || w.enc == SKAINET_ENC_Q5_K) {
-        if (x == nullptr) { set_error("matmul: Q5_K / Q6_K take the fp32 activation pointer"); return SKAINET_CUDA_ERR_INVALID; }
+        if (x == nullptr && (w.enc == SKAINET_ENC_Q5_K || act_mode == SKAINET_ACT_F32)) {      // Q6_K in the native mode reads the quantized rows only
+            set_error("matmul: Q5_K (and Q6_K in the F32 mode) take the fp32 activation pointer");
+            return SKAINET_CUDA_ERR_INVALID;
+        }
         return launch_matvec_kq(w, x, act_q8k_layout(const_cast<void*>(act_scratch), m, w.cols), m, y, act_mode, s);
     }
     if (w.enc != SKAINET_ENC_Q4_K && w.enc != SKAINET_ENC_Q8_0) {

@@ -136,19 +136,24 @@ int32_t weight_concat_rows(const Weight* a, const Weight* b, const Weight* c, We
     SK_TRY(weight_alloc(a->enc, rows, a->cols, out));
     Weight* w = *out;
     const Weight* parts[3] = {a, b, c};
+    // bytes per block of each plane (see the Weight record): main codes, header / scales, extra bit plane, aux scale plane
+    size_t pb[4] = {128, 16, 0, 0};
+    if (a->enc == SKAINET_ENC_Q8_0) { pb[0] = 32; pb[1] = 2; }
+    else if (a->enc == SKAINET_ENC_Q5_K) pb[2] = 32;
+    else if (a->enc == SKAINET_ENC_Q6_K) { pb[2] = 64; pb[3] = 2; }
     size_t row_off = 0;
     for (int i = 0; i < 3; ++i) {
         const Weight* p = parts[i];
         if (!p) continue;
         const size_t nb = (size_t) p->rows * p->bpr, off = row_off * a->bpr;
-        const size_t qs_b = a->enc == SKAINET_ENC_Q8_0 ? 32 : 128, hdr_b = a->enc == SKAINET_ENC_Q8_0 ? 2 : 16;
-        SK_CUDA(cudaMemcpy(w->qs + off * qs_b, p->qs, nb * qs_b, cudaMemcpyDeviceToDevice));
-        SK_CUDA(cudaMemcpy(w->hdr + off * hdr_b, p->hdr, nb * hdr_b, cudaMemcpyDeviceToDevice));
+        uint8_t* dst[4] = {w->qs, w->hdr, w->extra, w->aux};
+        const uint8_t* src[4] = {p->qs, p->hdr, p->extra, p->aux};
+        for (int k = 0; k < 4; ++k)
+            if (pb[k]) SK_CUDA(cudaMemcpy(dst[k] + off * pb[k], src[k], nb * pb[k], cudaMemcpyDeviceToDevice));
         row_off += p->rows;
     }
     return SKAINET_CUDA_OK;
 }
-
 
 // rows [r0, r0 + n) of src[m][stride] -> dst[m][n]
 __global__ void slice_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, int m, int stride, int r0, int n) {
@@ -156,6 +161,19 @@ __global__ void slice_rows_kernel(const float* __restrict__ src, float* __restri
     skd::pdl_wait();
     for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < (int64_t) m * n; i += (int64_t) gridDim.x * blockDim.x)
         dst[i] = src[(i / n) * stride + r0 + (i % n)];
+}
+
+// src[m][n] -> columns [r0, r0 + n) of dst[m][stride]
+__global__ void scatter_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, int m, int stride, int r0, int n) {
+    skd::pdl_launch_dependents();
+    skd::pdl_wait();
+    for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < (int64_t) m * n; i += (int64_t) gridDim.x * blockDim.x)
+        dst[(i / n) * stride + r0 + (i % n)] = src[i];
+}
+int32_t launch_scatter_rows(const float* src, float* dst, int m, int stride, int r0, int n, cudaStream_t s) {
+    const int64_t total = (int64_t) m * n;
+    SK_CUDA(launch_pdl(scatter_rows_kernel, dim3((unsigned) std::min<int64_t>((total + 255) / 256, 2368)), dim3(256), 0, s, src, dst, m, stride, r0, n));
+    return SKAINET_CUDA_OK;
 }
 
 // Quantized (optionally RMS-normalised) activation rows of x into the stream's activation scratch.
@@ -177,7 +195,6 @@ int32_t skainet_cuda_weight_concat_rows(skainet_weight_t a, skainet_weight_t b, 
     Weight *wa = weight_from_handle(a), *wb = wa ? weight_from_handle(b) : nullptr, *wc = nullptr;
     if (!wa || !wb) return SKAINET_CUDA_ERR_HANDLE;
     if (c != 0 && !(wc = weight_from_handle(c))) return SKAINET_CUDA_ERR_HANDLE;
-    SK_REQUIRE(wa->enc == SKAINET_ENC_Q4_K || wa->enc == SKAINET_ENC_Q8_0, "weight_concat_rows: encoding %d not supported", wa->enc);
     for (const Weight* p : {wb, wc})
         if (p) SK_REQUIRE(p->enc == wa->enc && p->cols == wa->cols, "weight_concat_rows: parts differ in encoding or input dimension");
     SK_TRY(ensure_device());

@@ -19,6 +19,9 @@ int32_t launch_prep(int mode, const float* in, const float* gamma, float eps, in
 // kernels have no residual epilogue.
 int32_t launch_linear_q(const Weight& w, void* act, int rows, float* y, float* resid_inplace, float* tmp, cudaStream_t s);
 
+// src[m][n] into columns [r0, r0 + n) of dst[m][stride]
+int32_t launch_scatter_rows(const float* src, float* dst, int m, int stride, int r0, int n, cudaStream_t s);
+
 // rows of a, then b (then c, may be null) in one new resident weight; the parts must share cols and encoding.
 int32_t weight_concat_rows(const Weight* a, const Weight* b, const Weight* c, Weight** out);
 

@@ -106,11 +106,16 @@ def test_operators_inside_the_step_match_the_reference_on_the_same_inputs(gpu, o
         g_q = g_qkv[:512]
         x = R.dequant("Q8_0", W[(-1, "embed")][t * 34 * 16:(t + 1) * 34 * 16])
         xn = R.rms_norm(x, ones, 1e-5, use_ref=use_ref)
-        stage(f"q@{pos}", g_q, R.rope(mm("q", xn, 512, 512).reshape(H, D), H, D, pos))
+        # q in the buffer: as projected when the step rotates it inside its attention kernel, rotated in place otherwise
+        q_ref = mm("q", xn, 512, 512)
+        q_ref_rot = R.rope(q_ref.reshape(H, D), H, D, pos).reshape(-1)
+        in_place = step_err(g_q, q_ref_rot) < step_err(g_q, q_ref)
+        stage(f"q@{pos}", g_q, q_ref_rot if in_place else q_ref)
+        q_rot = g_q.reshape(H, D) if in_place else R.rope(g_q.reshape(H, D), H, D, pos)
         stage(f"k@{pos}", g_qkv[512:768], mm("k", xn, 256, 512)); stage(f"v@{pos}", g_qkv[768:], mm("v", xn, 256, 512))
         # cache contents = binary16 of the runtime's own k (rotated) and v
         Ks.append(R.round_f16(R.rope(g_qkv[512:768].reshape(HK, D), HK, D, pos))); Vs.append(R.round_f16(g_qkv[768:].reshape(HK, D)))
-        a = R.sdpa(g_q.reshape(1, H, 1, D), np.stack(Ks, 1)[None], np.stack(Vs, 1)[None], 0.125, causal=True, use_ref=use_ref).reshape(-1)
+        a = R.sdpa(q_rot.reshape(1, H, 1, D), np.stack(Ks, 1)[None], np.stack(Vs, 1)[None], 0.125, causal=True, use_ref=use_ref).reshape(-1)
         stage(f"attn@{pos}", g_attn, a)
         x1 = x + mm("o", g_attn, 512, 512)
         xn2 = R.rms_norm(x1, ones, 1e-5, use_ref=use_ref)
