@@ -720,45 +720,74 @@ def run_attn(args) -> None:
 def tp_parity_check(torch, dist, m, cfg, model_name: str, ctx: int, batch: int, rank: int, world: int, n_steps: int = 4) -> dict:
     """Correctness of the tensor-parallel run against the single-GPU model, inside the bench: rank 0 also builds the
     unsharded model of the same seed (it fits beside its shard), both decode the same seeded context with the same
-    teacher tokens for a few steps, and the logits are compared. Logits agree to fp32 summation order unless an int8
-    activation code flips somewhere in the stack (one flip moves the outputs by ~3e-3 of their RMS): the bar of the
-    2-GPU parity test (2e-3) is reported as `within_bar`; only a gross error (> 5e-2: a wrong shard) fails the run."""
+    teacher tokens for a few steps, and the logits are compared.
+
+    What "agree" can mean here is measured, not assumed. Every int8 activation quantizer on the path turns a relative
+    input difference e into about 0.15 * sqrt(e) at its output, so two correct implementations that differ in fp32
+    summation order (as a sharded sum must) settle percents apart after 80 layers. The yardstick is therefore a
+    control: the unsharded model run twice on rank 0 through different kernels (one activation row: the streaming
+    matvecs; the same row as the first of two: the tile kernels). `within_control` says the sharded run is no further
+    from the single-GPU run than a few times that; the 2e-3 bar of the 2-layer parity test is reported as `within_bar`.
+    Only a gross error (beyond both 5e-2 and four times the control: a wrong shard, a lost partial sum) fails the run."""
     from skainet_b200.llama import Llama
+    first = (np.arange(1, batch + 1, dtype=np.int32) * 17 % cfg.vocab).astype(np.int32)
     ref = None
+    ref_logits, ref_tokens, margins, control = [], [], [], []
     if rank == 0:
-        ref = Llama(model_config(model_name, max_seq=cfg.max_seq, max_batch=batch, tp_rank=0, tp_world=1))
+        ref = Llama(model_config(model_name, max_seq=cfg.max_seq, max_batch=max(batch, 2), tp_rank=0, tp_world=1))
         ref.synth(seed=100, std=0.02)
         ref.finalize()
         for b in range(batch):
             ref.fake_prefill(ctx, seq=b, seed=7 + b)
+        tin, tout = first.copy(), np.zeros(batch, np.int32)
+        for _ in range(n_steps):                              # the single-GPU run: its greedy tokens are the teacher
+            ref_tokens.append(tin.copy())
+            ref.decode(tin, tout)
+            lg = ref.logits(batch).copy()
+            ref_logits.append(lg)
+            srt = np.sort(lg, axis=1)
+            margins.append(float(((srt[:, -1] - srt[:, -2]) / np.sqrt(np.mean(lg.astype(np.float64) ** 2))).min()))
+            tin = tout.copy()
+        if batch == 1:                                        # control: the same row as the first of two identical sequences
+            ref.reset()
+            ref.fake_prefill(ctx, seq=0, seed=7)
+            ref.fake_prefill(ctx, seq=1, seed=(7 - 31) % (1 << 64))      # the per-sequence seed offset cancels: same noise as sequence 0
+            t2, o2 = np.zeros(2, np.int32), np.zeros(2, np.int32)
+            for i in range(n_steps):
+                t2[:] = ref_tokens[i][0]
+                ref.decode(t2, o2)
+                lg2 = ref.logits(2)[0].astype(np.float64)
+                a = ref_logits[i][0].astype(np.float64)
+                control.append(float(np.abs(lg2 - a).max() / np.sqrt(np.mean(a * a))))
+        ref.free()
     m.reset()
     for b in range(batch):
         m.fake_prefill(ctx, seq=b, seed=7 + b)
-    tok = torch.from_numpy((np.arange(1, batch + 1, dtype=np.int32) * 17 % cfg.vocab).astype(np.int32)).cuda()
-    errs, equal, margins = [], True, []
+    errs, equal = [], True
     tin, tout = np.zeros(batch, np.int32), np.zeros(batch, np.int32)
-    for _ in range(n_steps):
+    tok = torch.zeros(batch, dtype=torch.int32, device="cuda")
+    for i in range(n_steps):
+        if rank == 0:
+            tok = torch.from_numpy(ref_tokens[i].copy()).cuda()
+        dist.broadcast(tok, src=0)                             # teacher tokens: the single-GPU model's greedy choice
         tin[:] = tok.cpu().numpy()
         m.decode(tin, tout)
-        lg_tp = m.logits(batch)                            # all ranks take part in the gather
+        lg_tp = m.logits(batch)                                # all ranks take part in the gather
         if rank == 0:
-            rtin, rtout = tin.copy(), np.zeros(batch, np.int32)
-            ref.decode(rtin, rtout)
-            lg = ref.logits(batch)
-            rms = float(np.sqrt(np.mean(lg.astype(np.float64) ** 2)))
-            errs.append(float(np.abs(lg_tp.astype(np.float64) - lg).max() / rms))
-            srt = np.sort(lg, axis=1)
-            margins.append(float(((srt[:, -1] - srt[:, -2]) / rms).min()))
-            equal = equal and bool(np.array_equal(tout, rtout))
-            tok = torch.from_numpy(rtout.copy()).cuda()
-        dist.broadcast(tok, src=0)                         # teacher tokens: the single-GPU model's greedy choice
-    out = None
+            a = ref_logits[i].astype(np.float64)
+            errs.append(float(np.abs(lg_tp.astype(np.float64) - a).max() / np.sqrt(np.mean(a * a))))
+            nxt = ref_tokens[i + 1] if i + 1 < n_steps else None
+            if nxt is not None:
+                equal = equal and bool(np.array_equal(tout, nxt))
+    out, ok = None, True
     if rank == 0:
-        ref.free()
-        worst = max(errs)
-        out = {"steps": n_steps, "max_rel_logit_err": worst, "tokens_equal": equal, "min_top2_margin": min(margins), "bar": 2e-3,
-               "within_bar": worst <= 2e-3, "reference": "the unsharded model of the same seed on rank 0, same seeded context, teacher-forced"}
-    flag = torch.tensor([1 if (rank != 0 or max(errs) <= 5e-2) else 0], device="cuda", dtype=torch.int32)
+        worst, ctl = max(errs), (max(control) if control else None)
+        ok = worst <= max(5e-2, 4.0 * (ctl or 0.0))
+        out = {"steps": n_steps, "max_rel_logit_err": worst, "per_step": errs, "tokens_equal": equal, "min_top2_margin": min(margins),
+               "control_rel_logit_err": ctl, "control": "the unsharded model on rank 0 through its one-row kernels against the same row through its tile kernels",
+               "within_control": (worst <= 4.0 * ctl) if ctl else None, "bar": 2e-3, "within_bar": worst <= 2e-3,
+               "reference": "the unsharded model of the same seed on rank 0, same seeded context, teacher-forced"}
+    flag = torch.tensor([1 if ok else 0], device="cuda", dtype=torch.int32)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if int(flag[0]) != 1:
         raise SystemExit(f"tensor-parallel logits differ grossly from the single-GPU model: {out}")

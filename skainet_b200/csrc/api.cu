@@ -94,6 +94,17 @@ int32_t set_thread_device(int device) {
     return SKAINET_CUDA_OK;
 }
 
+static std::map<std::pair<int, const void*>, int> g_smem_attr;
+int32_t ensure_dynamic_smem(const void* kernel, int bytes) {
+    const int dev = current_device();
+    std::lock_guard<std::mutex> lk(g_mu);
+    int& have = g_smem_attr[{dev, kernel}];
+    if (have >= bytes) return SKAINET_CUDA_OK;
+    SK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    have = bytes;
+    return SKAINET_CUDA_OK;
+}
+
 // One int per device, set by kernels whose bounded waits give up (1 = a wait on an asynchronous copy or
 // tensor-core barrier, 2 = a wait on a tensor-parallel peer). Keyed on the device that is current when it is
 // asked for, and allocated with that device current, so a kernel never receives a flag that lives on another GPU.

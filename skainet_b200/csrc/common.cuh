@@ -82,6 +82,9 @@ enum { SCRATCH_ACT = 0, SCRATCH_ATTN = 1, SCRATCH_TWIN_A = 2, SCRATCH_TWIN_B = 3
        SCRATCH_FFN = 11, SCRATCH_SLOTS = 12 };
 
 int sm_count();
+// Raises a kernel's dynamic shared-memory limit to at least `bytes` on the CURRENT device, once per (kernel, device):
+// the attribute belongs to each device's copy of the function, so a process that drives several GPUs sets it on each.
+int32_t ensure_dynamic_smem(const void* kernel, int bytes);
 int32_t launch_bounded_wait_selftest(int* reached_end, cudaStream_t s);   // probe.cu
 int* device_timeout_flag();   // current device's int, set by a kernel whose bounded wait ran out (nullptr if unavailable)
 int32_t timeout_status(int flag_value);       // OK for 0, else ERR_TIMEOUT with a message naming the kind of wait

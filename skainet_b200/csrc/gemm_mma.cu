@@ -201,14 +201,13 @@ template <int NW, int NT, int NS>
 int32_t launch_cfg(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s) {
     constexpr int RT = NW * 16, MT = NT * 8;
     constexpr size_t smem = (size_t) NS * (RT * GW_STRIDE + MT * GX_STRIDE + MT * 4);
-    static bool done[2] = {false, false};
     dim3 grid((w.rows + RT - 1) / RT, (m + MT - 1) / MT);
     if (resid) {
-        if (!done[1]) { SK_CUDA(cudaFuncSetAttribute(q4k_gemm_mma_kernel<NW, NT, NS, EPI_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem)); done[1] = true; }
+        SK_TRY(ensure_dynamic_smem((const void*) q4k_gemm_mma_kernel<NW, NT, NS, EPI_ADD>, (int) smem));
         SK_CUDA(launch_pdl(q4k_gemm_mma_kernel<NW, NT, NS, EPI_ADD>, grid, dim3(NW * 32), smem, s, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows,
                            w.bpr, a, m, y, resid));
     } else {
-        if (!done[0]) { SK_CUDA(cudaFuncSetAttribute(q4k_gemm_mma_kernel<NW, NT, NS, EPI_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem)); done[0] = true; }
+        SK_TRY(ensure_dynamic_smem((const void*) q4k_gemm_mma_kernel<NW, NT, NS, EPI_STORE>, (int) smem));
         SK_CUDA(launch_pdl(q4k_gemm_mma_kernel<NW, NT, NS, EPI_STORE>, grid, dim3(NW * 32), smem, s, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows,
                            w.bpr, a, m, y, resid));
     }
@@ -338,14 +337,13 @@ template <int NW, int NT, int NS>
 int32_t launch_cfg_q8(const Weight& w, ActSplit a, int m, float* y, const float* resid, cudaStream_t s) {
     constexpr int RT = NW * 16, MT = NT * 8;
     constexpr size_t smem = (size_t) NS * (RT * 272 + 2 * MT * 272);
-    static bool done[2] = {false, false};
     dim3 grid((w.rows + RT - 1) / RT, (m + MT - 1) / MT);
     if (resid) {
-        if (!done[1]) { SK_CUDA(cudaFuncSetAttribute(q8_0_gemm_mma_kernel<NW, NT, NS, EPI_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem)); done[1] = true; }
+        SK_TRY(ensure_dynamic_smem((const void*) q8_0_gemm_mma_kernel<NW, NT, NS, EPI_ADD>, (int) smem));
         SK_CUDA(launch_pdl(q8_0_gemm_mma_kernel<NW, NT, NS, EPI_ADD>, grid, dim3(NW * 32), smem, s, (const int8_t*) w.qs, (const __half*) w.hdr, w.rows, w.cols,
                            a, m, y, resid));
     } else {
-        if (!done[0]) { SK_CUDA(cudaFuncSetAttribute(q8_0_gemm_mma_kernel<NW, NT, NS, EPI_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem)); done[0] = true; }
+        SK_TRY(ensure_dynamic_smem((const void*) q8_0_gemm_mma_kernel<NW, NT, NS, EPI_STORE>, (int) smem));
         SK_CUDA(launch_pdl(q8_0_gemm_mma_kernel<NW, NT, NS, EPI_STORE>, grid, dim3(NW * 32), smem, s, (const int8_t*) w.qs, (const __half*) w.hdr, w.rows, w.cols,
                            a, m, y, resid));
     }

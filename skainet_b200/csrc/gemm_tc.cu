@@ -415,10 +415,7 @@ int32_t launch_gemm_tc(const Weight& w, ActQ8K a, int m, float* y, const float* 
     __half* xh = (__half*) base;
     __half* hs = (__half*) ((uint8_t*) base + up(xh_bytes));
     float* dxt = (float*) ((uint8_t*) base + up(xh_bytes) + up(hs_bytes));
-    static std::once_flag attr_once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(attr_once, []() { attr_err = cudaFuncSetAttribute(q4k_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM); });
-    SK_CUDA(attr_err);
+    SK_TRY(ensure_dynamic_smem((const void*) q4k_gemm_tc_kernel, TC_SMEM));
     const int64_t n16 = (int64_t) m_pad * (w.cols / 16);
     SK_CUDA(launch_pdl(act_f16_tiles_kernel, dim3((unsigned) ((n16 + 255) / 256)), dim3(256), 0, s, a, m, m_pad, w.cols, xh, hs, dxt));
     dim3 grid((w.rows + TC_M - 1) / TC_M, m_pad / TC_N);

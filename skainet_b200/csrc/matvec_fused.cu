@@ -236,15 +236,6 @@ q8_0_matvec_fused_kernel(const int8_t* __restrict__ codes, const __half* __restr
 // ================================================================================================
 // dispatch (m = 1 only). Returns 1 when the shape is outside what these kernels take.
 // ================================================================================================
-template <typename K>
-static int32_t set_smem_once(K kernel, bool* done) {
-    if (!*done) {
-        SK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) MF_SMEM_MAX + 1024));
-        *done = true;
-    }
-    return SKAINET_CUDA_OK;
-}
-
 // rows per warp: the largest tile under the budget, then halved while the grid would leave SMs short
 static int pick_rw(size_t fixed, size_t row_bytes, int rows) {
     int rw = MF_MAX_RW;
@@ -258,8 +249,7 @@ static int pick_rw(size_t fixed, size_t row_bytes, int rows) {
 template <int RW, int PREP, int EPI>
 static int32_t launch_q4k_f(const Weight& w, const MatvecIn& in, float* y, const float* resid, size_t smem, int* flag, cudaStream_t s,
                             const PeerOut& peer = PeerOut()) {
-    static bool done = false;
-    SK_TRY(set_smem_once(q4k_matvec_fused_kernel<RW, PREP, EPI>, &done));
+    SK_TRY(ensure_dynamic_smem((const void*) q4k_matvec_fused_kernel<RW, PREP, EPI>, (int) MF_SMEM_MAX + 1024));
     const int R = MF_WARPS * RW;
     SK_CUDA(launch_pdl(q4k_matvec_fused_kernel<RW, PREP, EPI>, dim3((w.rows + R - 1) / R), dim3(MF_THREADS), smem, s,
                        (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr, in, w.cols, y, resid, flag, peer));
@@ -267,8 +257,7 @@ static int32_t launch_q4k_f(const Weight& w, const MatvecIn& in, float* y, const
 }
 template <int RW, int PREP, int EPI>
 static int32_t launch_q8_f(const Weight& w, const MatvecIn& in, float* y, const float* resid, size_t smem, int* flag, cudaStream_t s) {
-    static bool done = false;
-    SK_TRY(set_smem_once(q8_0_matvec_fused_kernel<RW, PREP, EPI>, &done));
+    SK_TRY(ensure_dynamic_smem((const void*) q8_0_matvec_fused_kernel<RW, PREP, EPI>, (int) MF_SMEM_MAX + 1024));
     const int R = MF_WARPS * RW;
     SK_CUDA(launch_pdl(q8_0_matvec_fused_kernel<RW, PREP, EPI>, dim3((w.rows + R - 1) / R), dim3(MF_THREADS), smem, s,
                        (const int8_t*) w.qs, (const __half*) w.hdr, w.rows, w.cols, in, y, resid, flag));

@@ -313,19 +313,9 @@ static bool plan_ring(size_t fixed, size_t stage_bytes_per_row, RingPlan* p) {
     return false;
 }
 
-template <typename K>
-static int32_t set_smem_once(K kernel, bool* done) {
-    if (!*done) {
-        SK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) RG_SMEM_MAX + 1024));
-        *done = true;
-    }
-    return SKAINET_CUDA_OK;
-}
-
 #define SK_RG_LAUNCH(KERNEL, NCV, ...)                                                                        \
     do {                                                                                                      \
-        static bool done = false;                                                                             \
-        SK_TRY(set_smem_once(KERNEL, &done));                                                                 \
+        SK_TRY(ensure_dynamic_smem((const void*) KERNEL, (int) RG_SMEM_MAX + 1024));                          \
         const int nrg = (w.rows + NCV - 1) / NCV;                                                             \
         const int grid = std::min(sm_count() * plan.cps, nrg);                                                \
         SK_CUDA(launch_pdl(KERNEL, dim3(grid), dim3((NCV + 1) * 32), plan.smem, s, __VA_ARGS__));             \

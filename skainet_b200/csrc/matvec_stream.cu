@@ -145,11 +145,7 @@ static size_t q4k_stream_smem(int M, int RW, int bpr, int cols) {
 template <int M, int RW>
 static int32_t launch_q4k_stream(const Weight& w, ActQ8K act, float* y, int* flag, cudaStream_t s) {
     const size_t smem = q4k_stream_smem(M, RW, w.bpr, w.cols);
-    static bool attr_set = false;   // per instantiation
-    if (!attr_set) {
-        SK_CUDA(cudaFuncSetAttribute(q4k_matvec_stream_kernel<M, RW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) MS_SMEM_BUDGET + 4096));
-        attr_set = true;
-    }
+    SK_TRY(ensure_dynamic_smem((const void*) q4k_matvec_stream_kernel<M, RW>, (int) MS_SMEM_BUDGET + 4096));
     const int R = MS_WARPS * RW;
     SK_CUDA(launch_pdl(q4k_matvec_stream_kernel<M, RW>, dim3((w.rows + R - 1) / R), dim3(MS_THREADS), smem, s,
                        (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr, act, w.cols, y, flag));
@@ -263,11 +259,7 @@ static size_t q8_stream_smem(int M, int RW, int cols) {
 template <int M, int RW>
 static int32_t launch_q8_stream(const Weight& w, ActSplit act, float* y, int* flag, cudaStream_t s) {
     const size_t smem = q8_stream_smem(M, RW, w.cols);
-    static bool attr_set = false;
-    if (!attr_set) {
-        SK_CUDA(cudaFuncSetAttribute(q8_0_matvec_stream_kernel<M, RW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) MS_SMEM_BUDGET + 4096));
-        attr_set = true;
-    }
+    SK_TRY(ensure_dynamic_smem((const void*) q8_0_matvec_stream_kernel<M, RW>, (int) MS_SMEM_BUDGET + 4096));
     const int R = MS_WARPS * RW;
     SK_CUDA(launch_pdl(q8_0_matvec_stream_kernel<M, RW>, dim3((w.rows + R - 1) / R), dim3(MS_THREADS), smem, s,
                        (const int8_t*) w.qs, (const __half*) w.hdr, w.rows, w.cols, act, y, flag));

@@ -13,6 +13,7 @@
  * so that a decode call carries only its activation row across PCIe.
  */
 #include <jni.h>
+#include <stddef.h>
 #include <stdint.h>
 
 #include "skainet_cuda.h"
