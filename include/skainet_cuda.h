@@ -85,12 +85,6 @@ SKAINET_CUDA_API int32_t skainet_cuda_device_info(int64_t* out4);
  * counterpart: its kernels cannot time out. */
 SKAINET_CUDA_API int32_t skainet_cuda_device_status(void);
 
-/* Exercises that failure path without any fault: launches a kernel whose only wait is on a barrier nothing completes.
- * outcome = 2 when the kernel gave up after its poll limit and still ran to its end (the expected result; the next
- * skainet_cuda_device_status() then returns SKAINET_CUDA_ERR_TIMEOUT once), 1 if the wait unexpectedly succeeded,
- * 0 if the kernel did not finish. Takes a second or so. The reference has no counterpart. */
-SKAINET_CUDA_API int32_t skainet_cuda_selftest_bounded_wait(int32_t* outcome);
-
 /* ---- 1. drop-in twins (HOST pointers) -------------------------------------------------------- */
 
 /* Availability probe, out[i] = 2*in[i] computed on the GPU.
@@ -218,11 +212,6 @@ SKAINET_CUDA_API int32_t skainet_cuda_fused_qkv_proj_dev(skainet_weight_t w_qkv,
 SKAINET_CUDA_API int32_t skainet_cuda_fused_swiglu_ffn_dev(skainet_weight_t w_gate_up, skainet_weight_t w_down, const float* x_dev,
     const float* gamma_dev, float eps, int32_t m, const float* resid_dev, float* out_dev, skainet_stream_t stream);
 
-/* Measurement aid with no counterpart in the reference: reads every byte of a resident weight once
- * with plain vector loads and computes nothing. The bench times it over the same weights as the matvec
- * to report the floor a launch of that many bytes can reach on this GPU. */
-SKAINET_CUDA_API int32_t skainet_cuda_probe_read_dev(skainet_weight_t w, skainet_stream_t stream);
-
 /* Row kernels on the device (contracts as the twins above). */
 SKAINET_CUDA_API int32_t skainet_cuda_rms_norm_dev(const float* in, const float* gamma, float* out,
     int32_t rows, int32_t cols, float eps, skainet_stream_t stream);
@@ -321,6 +310,19 @@ SKAINET_CUDA_API int32_t skainet_cuda_kv_info(skainet_kv_t kv, int64_t* out8);
  * currentSeqLen + 1 while a token's layers are being appended (the sequence length advances only with the last layer). */
 SKAINET_CUDA_API int32_t skainet_cuda_kv_attn_decode_dev(skainet_kv_t kv, int32_t layer, const float* q_dev, float* out_dev,
     int32_t q_heads, int32_t from_pos, int32_t to_pos, float scale, skainet_stream_t stream);
+
+/* ---- 4. diagnostics (no counterpart in the reference; nothing on the product path calls these) ---- */
+
+/* Exercises the bounded-wait failure path (skainet_cuda_device_status) without any fault: launches a kernel whose only wait is on a barrier nothing completes.
+ * outcome = 2 when the kernel gave up after its poll limit and still ran to its end (the expected result; the next
+ * skainet_cuda_device_status() then returns SKAINET_CUDA_ERR_TIMEOUT once), 1 if the wait unexpectedly succeeded,
+ * 0 if the kernel did not finish. Takes a second or so. The reference has no counterpart. */
+SKAINET_CUDA_API int32_t skainet_cuda_selftest_bounded_wait(int32_t* outcome);
+
+/* Measurement aid with no counterpart in the reference: reads every byte of a resident weight once
+ * with plain vector loads and computes nothing. The bench times it over the same weights as the matvec
+ * to report the floor a launch of that many bytes can reach on this GPU. */
+SKAINET_CUDA_API int32_t skainet_cuda_probe_read_dev(skainet_weight_t w, skainet_stream_t stream);
 
 #ifdef __cplusplus
 }

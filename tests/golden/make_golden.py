@@ -70,7 +70,9 @@ def vectors() -> dict:
 
 
 if __name__ == "__main__":
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    # the reference checkout: argument, else SKAINET_REFERENCE_ROOT, else a directory `reference` beside this repository
+    ref_root = (sys.argv[1] if len(sys.argv) > 1 else
+                os.environ.get("SKAINET_REFERENCE_ROOT", os.path.abspath(os.path.join(HERE, "..", "..", "..", "reference"))))
     json.dump(digests(ref_root), open(os.path.join(HERE, "reference_digests.json"), "w"), indent=1, sort_keys=True)
     np.savez_compressed(os.path.join(HERE, "ref_vectors.npz"), **vectors())
     print("wrote", os.listdir(HERE))
