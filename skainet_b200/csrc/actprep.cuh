@@ -26,7 +26,8 @@ __device__ __forceinline__ float prep_sum(float v, float* red, int warp, int lan
     if (lane == 0) red[warp] = v;
     prep_sync<NW, BAR>();
     float t = (red[0] + red[1]) + (red[2] + red[3]);
-    if (NW == 8) t += (red[4] + red[5]) + (red[6] + red[7]);
+#pragma unroll
+    for (int i = 4; i < NW; i += 4) t += (red[i] + red[i + 1]) + (red[i + 2] + red[i + 3]);
     prep_sync<NW, BAR>();
     return t;
 }

@@ -2,6 +2,7 @@
 // the resident-weight registry, per-stream scratch, and the host-pointer twins of the reference's
 // native entry points, which are thin wrappers over the resident API (upload, run, read back).
 #include "common.cuh"
+#include <cstdlib>
 #include "matvec_fused.cuh"
 
 #include <cstdarg>

@@ -71,6 +71,7 @@ struct Weight {
 };
 Weight* weight_from_handle(skainet_weight_t h);   // nullptr (+ error set) when unknown
 
+
 // ---- per-stream scratch --------------------------------------------------------------------------
 // Device scratch reused across calls on one stream (quantized activations, split-K partials).
 // Grown on demand outside stream capture; never shrinks.

@@ -10,6 +10,7 @@
 // kernels between them turn an fp32 row into the quantized activation the next matvec consumes, which
 // is where RMSNorm and SwiGLU live. Operator contracts: see the header.
 #include "common.cuh"
+#include <cstdlib>
 #include "actquant.cuh"
 #include "matvec_fused.cuh"
 #include "tma.cuh"
@@ -28,7 +29,7 @@ namespace sk {
 // ================================================================================================
 // small kernels of the step
 // ================================================================================================
-constexpr int PROLOGUE_PREP_MAX_COLS = 4096;
+constexpr int PROLOGUE_PREP_MAX_COLS = 4096, PROLOGUE_PREP_MAX_COLS_RING = 8192;
 
 // After the merged q|k|v matvec: rotate q in place, rotate k and append it with v to the f16 cache at
 // each sequence's position. grid (rows, heads + 2*kv_heads), head_dim/2 threads. The rotation factors
@@ -200,13 +201,14 @@ static int32_t prep(Model& m, const float* in, const float* gamma, int rows, int
     return launch_prep(MODE, in, gamma, m.cfg.rms_eps, rows, n, split, m.act, s);
 }
 
-// y[rows][w.rows] = W . quantize(rmsnorm(x, gamma)). One activation row of up to 4096 elements takes a single
-// launch: the matvec kernel normalises and quantizes the row in its own prologue while its first weight tiles
-// are in flight. Wider rows keep the separate prep kernel: every CTA of the matvec would re-read the fp32 row
-// and the gains (12 bytes per element out of L2 against one for the quantized row), which measured slower
-// (70B shape, 8192 columns: 9.88 against 9.38 ms per step).
+// y[rows][w.rows] = W . quantize(rmsnorm(x, gamma)). One activation row takes a single launch where the matvec
+// kernel can normalise and quantize the row in its own prologue while its first weight tiles are in flight: up to
+// 4096 elements in the one-tile kernel (one prologue per CTA, several CTAs per SM), up to 8192 in the ring kernel
+// (one prologue per SM; 70B shape, 8192 columns: 8.26 against 8.47 ms per step). Wider rows keep the separate
+// prep kernel: every CTA would re-read the fp32 row and the gains, 12 bytes per element out of L2 against one for
+// the quantized row.
 static int32_t linear_normed(Model& m, const Weight& w, const float* x, const float* gamma, int rows, float* y, cudaStream_t s) {
-    if (rows == 1 && w.cols <= PROLOGUE_PREP_MAX_COLS) {
+    if (rows == 1 && w.cols <= (matvec_uses_ring(w) ? PROLOGUE_PREP_MAX_COLS_RING : PROLOGUE_PREP_MAX_COLS)) {
         MatvecIn in; in.x = x; in.gamma = gamma; in.eps = m.cfg.rms_eps;
         const int32_t st = launch_matvec_fused(w, in, PREP_NORM_F32, y, nullptr, s);
         if (st != 1) return st;

@@ -280,6 +280,8 @@ static int32_t launch_q8_f(const Weight& w, const MatvecIn& in, float* y, const 
         default: SK_MF_PE(FN, 1)              \
     }
 
+bool matvec_uses_ring(const Weight& w) { return w.packed_bytes >= (int64_t) RING_MIN_BYTES && (w.enc == SKAINET_ENC_Q4_K || w.enc == SKAINET_ENC_Q8_0); }
+
 int32_t launch_matvec_fused(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s,
                             const PeerOut* peer) {
     int* flag = device_timeout_flag();

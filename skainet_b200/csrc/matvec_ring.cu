@@ -1,15 +1,24 @@
-// Persistent ring matvec for LARGE weights (m = 1): when a weight is hundreds of KB per SM, a few CTAs
-// per SM each keep a ring of shared-memory stages filled by a producer warp (cp.async.bulk / TMA, one
-// "full" mbarrier per stage counted in bytes) while NC consumer warps — one output row of the stage each
-// — drain it and hand stages back through "empty" mbarriers. The rings are the SM's bytes in flight
-// (up to ~190 KB), so HBM stays busy for the whole launch and the quantized activation is staged once
-// per CTA instead of once per tile. The one-tile kernel (matvec_fused.cu) remains the choice for small
-// weights, where a CTA's prologue would not amortise.
+// Persistent ring matvec for LARGE weights (m = 1): a ring of shared-memory stages is kept filled by a producer
+// warp (cp.async.bulk / TMA, one "full" mbarrier per stage counted in bytes) while NC consumer warps — one output
+// row of the stage each — drain it and hand stages back through "empty" mbarriers. The rings are the SM's bytes in
+// flight (up to ~190 KB), so HBM stays busy for the whole launch. The one-tile kernel (matvec_fused.cu) remains
+// the choice for small weights, where a CTA's prologue would not amortise.
 //
 // Stage = NC rows x one column group (16 Q4_K super-blocks / 2048 Q8_0 codes). Consumers read stages
 // bank-conflict free with the same lane mapping and arithmetic as matvec_fused.cu. Every mbarrier wait
 // is bounded and reports through the device flag. Reference arithmetic: native/src/q4k_matmul.c:143-251,
 // native/src/q8_0_matmul.c:68-118.
+//
+// Shape of the Q4_K kernel, from measurement on B200 (57344 x 8192 and 8192 x 28672 weights, launches timed in a
+// CUDA graph over distinct weights): four independent groups of 1 producer + 4 consumer warps per SM is the
+// fastest arrangement (0.92 of the measured copy bandwidth on the first weight); 8, 12 or 16 consumer warps
+// behind one producer reach 0.49-0.54, and rings private to each warp, refilled by the warp itself (no producer,
+// no "empty" barriers), 0.65-0.79. As four CTAs per SM the groups each stage their own copy of the activation,
+// which for a 28672-column row leaves three CTAs of three stages; as four groups of ONE CTA they share one copy
+// (this kernel): 28.0 -> 25.3 us on that weight, and a fused norm + quantize prologue runs once per SM instead of
+// four times, which is what makes it pay up to 8192 columns. Asking L2 for the head of the next weight from the
+// producers' tails (prefetch.global.L2 or cp.async.bulk.prefetch.L2) made the decode step slower at every
+// budget tried and is not done.
 #include "common.cuh"
 #include "actquant.cuh"
 #include "tma.cuh"
@@ -30,6 +39,16 @@ static size_t ring_budget() { return (size_t) SK_RING_BUDGET_KB << 10; }
 
 template <int NC>
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NC * 32) : "memory"); }
+// named barriers: 1 = the consumer warps of all groups (activation staging), 2..NG+1 = the NC consumer warps of one
+// group (written as immediates: a register operand makes the compiler reserve all sixteen)
+constexpr int RG_BAR_ALL = 1;
+template <int NC, int NG>
+__device__ __forceinline__ void group_sync(int grp) {
+    if (NG == 1 || grp == 0) asm volatile("bar.sync 2, %0;" ::"n"(NC * 32) : "memory");
+    else if (grp == 1) asm volatile("bar.sync 3, %0;" ::"n"(NC * 32) : "memory");
+    else if (grp == 2) asm volatile("bar.sync 4, %0;" ::"n"(NC * 32) : "memory");
+    else asm volatile("bar.sync 5, %0;" ::"n"(NC * 32) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(skd::smem_u32(bar)) : "memory");
 }
@@ -42,28 +61,33 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // ================================================================================================
 // Q4_K. Stage: qs part [NC][16][128] then hdr part [NC][16][16].
 // ================================================================================================
-template <int NC, int PREP, int EPI>
-__global__ void __launch_bounds__((NC + 1) * 32)
+template <int NC, int NG, int PREP, int EPI>
+__global__ void __launch_bounds__(NG * (NC + 1) * 32)
 q4k_matvec_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ hdr, int rows, int bpr, MatvecIn in,
                        int cols, float* __restrict__ y, const float* __restrict__ resid, int nstages, int* __restrict__ timeout_flag, PeerOut peer) {
     constexpr int S_QS = NC * 16 * 128, S_HDR = NC * 16 * 16, S_BYTES = S_QS + S_HDR;
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: ring | q8 (swizzled) | split sub-block sums | d | reduce scratch | barriers
-    uint8_t* s_ring = smem;
-    int8_t* s_q8 = (int8_t*) (s_ring + (size_t) nstages * S_BYTES);
+    // NG independent groups (one producer warp + NC consumer warps, own ring and barriers each) share one copy of
+    // the activation: what NG CTAs per SM would do, without NG copies of a long row.
+    // layout: rings [NG] | q8 (swizzled) | split sub-block sums | d | reduce scratch | barriers [NG] | peer gather [NG]
+    const int lane = threadIdx.x & 31;
+    const int grp = NG == 1 ? 0 : (int) (threadIdx.x >> 5) / (NC + 1);
+    const int warp = (int) (threadIdx.x >> 5) - grp * (NC + 1);          // 0..NC-1 consumers, NC the producer
+    uint8_t* s_ring = smem + (size_t) grp * nstages * S_BYTES;
+    int8_t* s_q8 = (int8_t*) (smem + (size_t) NG * nstages * S_BYTES);
     uint8_t* s_bs = (uint8_t*) (s_q8 + cols);                      // 16 bytes per block
     float* s_d = (float*) (s_bs + cols / 16);
-    float* s_red = (float*) ((uint8_t*) s_d + ((bpr * 4 + 15) & ~15));
-    uint64_t* full = (uint64_t*) (s_red + 8);
+    float* s_red = (float*) ((uint8_t*) s_d + ((bpr * 4 + 15) & ~15));      // NG * NC floats (at most 16)
+    uint64_t* full = (uint64_t*) (s_red + 16) + grp * 2 * RG_MAX_STAGES;
     uint64_t* empty = full + RG_MAX_STAGES;
-    float* s_out = (float*) (empty + RG_MAX_STAGES);          // [2][NC]: a row group's results, gathered for the peer stores
+    float* s_out = (float*) ((uint64_t*) (s_red + 16) + NG * 2 * RG_MAX_STAGES) + grp * 2 * NC;   // [2][NC]: a row group's results, gathered for the peer stores
 
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int vcta = (int) blockIdx.x * NG + grp, vgrid = (int) gridDim.x * NG;   // row group g belongs to group g mod vgrid
     const int nrg = (rows + NC - 1) / NC;                     // row groups in the matrix
     const int ncg = (bpr + 15) >> 4;                          // column groups per row
-    const int my_rgs = (int) blockIdx.x < nrg ? (nrg - 1 - (int) blockIdx.x) / (int) gridDim.x + 1 : 0;
+    const int my_rgs = vcta < nrg ? (nrg - 1 - vcta) / vgrid + 1 : 0;
 
-    if (threadIdx.x == 0) {
+    if (warp == NC && lane == 0) {
         for (int s = 0; s < nstages; ++s) { skd::mbar_init(full + s, 1); skd::mbar_init(empty + s, NC); }
         skd::mbar_fence_init();
     }
@@ -74,7 +98,7 @@ q4k_matvec_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict
         // ---------------- producer: the weights depend on no predecessor ----------------
         int stage = 0, round = 0;
         for (int rgi = 0; rgi < my_rgs; ++rgi) {
-            const int row0 = ((int) blockIdx.x + rgi * (int) gridDim.x) * NC, nr = min(NC, rows - row0);
+            const int row0 = (vcta + rgi * vgrid) * NC, nr = min(NC, rows - row0);
             for (int cg = 0; cg < ncg; ++cg) {
                 if (round > 0 && !skd::mbar_wait_bounded(empty + stage, (round - 1) & 1, timeout_flag)) return;
                 const int b0 = cg * 16, nb = min(16, bpr - b0);
@@ -100,8 +124,8 @@ q4k_matvec_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict
     // ---------------- consumers ----------------
     skd::pdl_wait();                                   // the activation is the predecessor's output
     // taken as already quantized, or quantized here (optionally RMS-normalised first) while the ring fills
-    q8k_prep_to_smem<PREP, NC, 1>(in, cols, bpr, s_q8, s_bs, s_d, s_red, warp, lane, threadIdx.x);
-    consumer_sync<NC>();
+    q8k_prep_to_smem<PREP, NG * NC, RG_BAR_ALL>(in, cols, bpr, s_q8, s_bs, s_d, s_red, grp * NC + warp, lane, (grp * NC + warp) * 32 + lane);
+    prep_sync<NG * NC, RG_BAR_ALL>();
 
     const int h = lane & 1, slot = lane >> 1, s1 = (slot >> 1) & 1;
     const int off_lo = (h ^ (s1 << 1)) * 16, off_hi = ((2 + h) ^ (s1 << 1)) * 16;
@@ -123,7 +147,7 @@ q4k_matvec_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict
     // Rows past the end of the matrix (last group only) are computed on whatever the stage holds and never written.
     for (int rgi = 0; rgi < my_rgs; ++rgi) {
         const bool first = rgi == 0;
-        const int rg = (int) blockIdx.x + rgi * (int) gridDim.x;
+        const int rg = vcta + rgi * vgrid;
         float acc = 0.0f;
         for (int cg = 0; cg < ncg; ++cg) {
             const int b = cg * 16 + slot;
@@ -177,7 +201,7 @@ q4k_matvec_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict
             // the group's NC rows, four at a time, into this rank's slot of every rank's inbox: the exchange of the
             // group sum rides on the matvec instead of following it (two result buffers: one barrier per group)
             if (lane == 0) s_out[obuf * NC + warp] = row < rows ? (resid ? resid[row] + v : v) : 0.0f;
-            consumer_sync<NC>();
+            group_sync<NC, NG>(grp);
             if (warp == 0 && lane < (NC / 4) * peer.world) {
                 const int g = lane % (NC / 4), p = lane / (NC / 4), base = rg * NC + 4 * g;
                 const float* o = s_out + obuf * NC + 4 * g;
@@ -300,7 +324,7 @@ q8_0_matvec_ring_kernel(const int8_t* __restrict__ codes, const __half* __restri
 // ================================================================================================
 struct RingPlan { int nc, cps, nstages; size_t smem; };
 
-// As many consumer warps per SM as the shared-memory budget allows with at least three stages per ring.
+// Q8_0: as many consumer warps per SM as the shared-memory budget allows with at least three stages per ring.
 static bool plan_ring(size_t fixed, size_t stage_bytes_per_row, RingPlan* p) {
     const int ncs[4] = {4, 4, 8, 8}, cpss[4] = {4, 3, 2, 1};
     for (int i = 0; i < 4; ++i) {
@@ -322,12 +346,22 @@ static bool plan_ring(size_t fixed, size_t stage_bytes_per_row, RingPlan* p) {
         return SKAINET_CUDA_OK;                                                                               \
     } while (0)
 
+// Q4_K: one CTA per SM of RG_GROUPS groups; the ring depth is what the activation leaves of the budget.
+constexpr int RG_GROUPS = 4, RG_GROUP_ROWS = 4;
 template <int PREP, int EPI>
-static int32_t launch_q4k_ring(const Weight& w, const MatvecIn& in, float* y, const float* resid, const RingPlan& plan, int* flag, cudaStream_t s,
+static int32_t launch_q4k_ring(const Weight& w, const MatvecIn& in, float* y, const float* resid, int* flag, cudaStream_t s,
                                const PeerOut& peer = PeerOut()) {
-    if (plan.nc == 4)
-        SK_RG_LAUNCH((q4k_matvec_ring_kernel<4, PREP, EPI>), 4, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr, in, w.cols, y, resid, plan.nstages, flag, peer);
-    SK_RG_LAUNCH((q4k_matvec_ring_kernel<8, PREP, EPI>), 8, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr, in, w.cols, y, resid, plan.nstages, flag, peer);
+    constexpr size_t STAGE = (size_t) RG_GROUPS * RG_GROUP_ROWS * 16 * 144;
+    const size_t fixed = (size_t) w.cols + w.cols / 16 + ((w.bpr * 4 + 15) & ~15) + 64 + RG_GROUPS * (2 * RG_MAX_STAGES * 8 + 2 * RG_GROUP_ROWS * 4) + 256;
+    if (ring_budget() <= fixed) return 1;
+    const int ns = (int) std::min<size_t>(RG_MAX_STAGES, (ring_budget() - fixed) / STAGE);
+    if (ns < 3) return 1;
+    auto kernel = q4k_matvec_ring_kernel<RG_GROUP_ROWS, RG_GROUPS, PREP, EPI>;
+    SK_TRY(ensure_dynamic_smem((const void*) kernel, (int) RG_SMEM_MAX + 1024));
+    const int nrg = (w.rows + RG_GROUP_ROWS - 1) / RG_GROUP_ROWS, grid = std::min(sm_count(), (nrg + RG_GROUPS - 1) / RG_GROUPS);
+    SK_CUDA(launch_pdl(kernel, dim3(grid), dim3(RG_GROUPS * (RG_GROUP_ROWS + 1) * 32), fixed + ns * STAGE, s, (const uint8_t*) w.qs,
+                       (const uint8_t*) w.hdr, w.rows, w.bpr, in, w.cols, y, resid, ns, flag, peer));
+    return SKAINET_CUDA_OK;
 }
 template <int PREP, int EPI>
 static int32_t launch_q8_ring(const Weight& w, const MatvecIn& in, float* y, const float* resid, const RingPlan& plan, int* flag, cudaStream_t s) {
@@ -352,10 +386,15 @@ int32_t launch_matvec_ring(const Weight& w, const MatvecIn& in, int prep, float*
     if (peer && (w.enc != SKAINET_ENC_Q4_K || prep != PREP_QUANTIZED)) return 1;
     RingPlan plan;
     if (w.enc == SKAINET_ENC_Q4_K) {
-        const size_t fixed = (size_t) w.cols + w.cols / 16 + ((w.bpr * 4 + 15) & ~15) + 32 + 2 * RG_MAX_STAGES * 8 + 64;
-        if (!plan_ring(fixed, 16 * 144, &plan)) return 1;
-        if (peer) return launch_q4k_ring<PREP_QUANTIZED, EPI_PEER>(w, in, y, resid, plan, flag, s, *peer);
-        SK_RG_PE(launch_q4k_ring)
+        if (peer) return launch_q4k_ring<PREP_QUANTIZED, EPI_PEER>(w, in, y, resid, flag, s, *peer);
+        switch (prep * 2 + (resid ? EPI_ADD : EPI_STORE)) {
+            case PREP_QUANTIZED * 2 + EPI_STORE: return launch_q4k_ring<PREP_QUANTIZED, EPI_STORE>(w, in, y, resid, flag, s);
+            case PREP_QUANTIZED * 2 + EPI_ADD:   return launch_q4k_ring<PREP_QUANTIZED, EPI_ADD>(w, in, y, resid, flag, s);
+            case PREP_F32 * 2 + EPI_STORE:       return launch_q4k_ring<PREP_F32, EPI_STORE>(w, in, y, resid, flag, s);
+            case PREP_F32 * 2 + EPI_ADD:         return launch_q4k_ring<PREP_F32, EPI_ADD>(w, in, y, resid, flag, s);
+            case PREP_NORM_F32 * 2 + EPI_STORE:  return launch_q4k_ring<PREP_NORM_F32, EPI_STORE>(w, in, y, resid, flag, s);
+            default:                             return launch_q4k_ring<PREP_NORM_F32, EPI_ADD>(w, in, y, resid, flag, s);
+        }
     }
     if (w.enc == SKAINET_ENC_Q8_0) {
         if (w.cols % 256 != 0) return 1;
