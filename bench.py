@@ -334,6 +334,13 @@ def read_floor_ms(torch, L, weights_flat, stream, steps: int) -> float:
     return e0.elapsed_time(e1) / steps
 
 
+def matmul_launches(w) -> int:
+    """Kernels one skainet_cuda_matmul_dev call of one activation row launches: a Q4_K weight of 20 MiB or more with at
+    most 12288 columns takes the ring kernel with the quantizer in its prologue (one launch); everything else is a quantizer
+    launch followed by the matvec (csrc/api.cu)."""
+    return 1 if (w.encoding == "Q4_K" and w.packed_bytes >= (20 << 20) and w.cols <= 12288) else 2
+
+
 def matvec_sweep_rate(torch, device, L, weights_flat, stream, steps: int, warmup: int):
     """Times `steps` sweeps of one fused-path matvec per weight (fp32 activation in HBM), one CUDA graph
     per sweep, on `stream`. Returns (ms per sweep, launches per sweep)."""
@@ -364,7 +371,7 @@ def matvec_sweep_rate(torch, device, L, weights_flat, stream, steps: int, warmup
             graph.replay()
         e1.record(stream)
         stream.synchronize()
-    return e0.elapsed_time(e1) / steps, 2 * len(weights_flat), graph, (xs, ys)
+    return e0.elapsed_time(e1) / steps, sum(matmul_launches(w) for w in weights_flat), graph, (xs, ys)
 
 
 def matvec_configs_summary(torch, device, L, steps: int = 10) -> dict:
@@ -466,7 +473,8 @@ def run_matvec(args) -> None:
                          "peak_kind": peak_kind, "kernel": "q4k_matvec_ring_kernel" if enc == "Q4_K" else "q8_0_matvec_fused_kernel",
                          "avg_launch_us": per_launch_us,
                          "read_floor_us": floor_ms * 1e3 / len(weights), "read_floor_gbs": bytes_per_step / (floor_ms * 1e-3) / 1e9,
-                         "note": "avg launch = timed region / matvec launches; the activation quantizer and launch gaps are inside it. "
+                         "note": "avg launch = timed region / matvec calls; the activation quantizer (its own launch for Q8_0 and small weights, the "
+                                 "matvec's prologue otherwise) and launch gaps are inside it. "
                                  "read_floor = a kernel that only reads the same weights, same launch count, same graph protocol"},
             "e2e": {"value": (bytes_per_step * world * e2e_steps / (e2e_ms * 1e-3) / 1e9) if e2e_steps else None, "unit": "GB/s",
                     "h2d_bytes_per_step": int(sum(4 * w.cols for w in weights)), "d2h_bytes_per_step": int(sum(4 * w.rows for w in weights)),

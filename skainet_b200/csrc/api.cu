@@ -456,6 +456,8 @@ int32_t skainet_cuda_weight_dequant(skainet_weight_t h, float* dev_out, skainet_
     return launch_dequant_weight(*w, dev_out, as_stream(stream));
 }
 
+constexpr int MATMUL_PROLOGUE_MAX_COLS = 12288;
+
 int32_t skainet_cuda_matmul_dev(skainet_weight_t h, const float* x_dev, int32_t m, float* y_dev, int32_t act_mode,
                                 skainet_stream_t stream) {
     Weight* w = weight_from_handle(h);
@@ -468,13 +470,21 @@ int32_t skainet_cuda_matmul_dev(skainet_weight_t h, const float* x_dev, int32_t 
     SK_TRY(ensure_device());
     cudaStream_t s = as_stream(stream);
     if (w->cols == 0) { SK_CUDA(cudaMemsetAsync(y_dev, 0, sizeof(float) * (size_t) m * w->rows, s)); return SKAINET_CUDA_OK; }
+    // One activation row of a ring-sized Q4_K weight: a single launch, the ring kernel quantizes the row in its own
+    // prologue (once per SM) while the first weight stages are in flight (config 2: 5.7 / 7.2 us per matvec against
+    // 8.0 / 8.4 us for a quantizer launch followed by the matvec).
+    if (m == 1 && act_mode == SKAINET_ACT_NATIVE && w->enc == SKAINET_ENC_Q4_K && w->cols <= MATMUL_PROLOGUE_MAX_COLS && matvec_uses_ring(*w)) {
+        MatvecIn in; in.x = x_dev;
+        const int32_t st = launch_matvec_fused(*w, in, PREP_F32, y_dev, nullptr, s);
+        if (st != 1) return st;
+    }
     void* scratch = nullptr;
     const size_t need = act_scratch_bytes(w->enc, act_mode, m, w->cols);
     if (need) SK_TRY(scratch_get(s, SCRATCH_ACT, need, &scratch));
     SK_TRY(launch_act_quant(w->enc, act_mode, x_dev, m, w->cols, scratch, s));
-    // One activation row: quantizer launch, then the streaming matvec over the quantized row (one-tile kernel, or the
-    // ring kernel for large weights). Quantizing in every CTA's prologue instead measured slower at these widths
-    // (config 2: 9.9 against 9.0 us per matvec): each CTA would pull the fp32 row out of L2 again.
+    // Otherwise one row = quantizer launch, then the streaming matvec over the quantized row. In the one-tile kernel
+    // (small weights, Q8_0) quantizing in every CTA's prologue measured slower (Q8_0 4096 x 4096: 7.2 against 6.8 us):
+    // every CTA pulls the fp32 row out of L2 again.
     if (m == 1 && act_mode == SKAINET_ACT_NATIVE && (w->enc == SKAINET_ENC_Q4_K || w->enc == SKAINET_ENC_Q8_0)) {
         MatvecIn in;
         if (w->enc == SKAINET_ENC_Q8_0) in.split = act_split_layout(scratch, 1, w->cols); else in.q8 = act_q8k_layout(scratch, 1, w->cols);

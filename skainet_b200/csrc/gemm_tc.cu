@@ -149,8 +149,9 @@ act_f16_tiles_kernel(ActQ8K act, int m, int m_pad, int cols, __half* __restrict_
     if (j == 0) dxt[(size_t) kb * m_pad + n] = n < m ? act.d[(size_t) n * (cols >> 8) + kb] : 0.0f;
 }
 
-constexpr int TC_SPLIT = 4;          // threads per weight row: each converts 1/4 of a stage and folds 1/4 of the columns
-constexpr int TC_WORKERS = 128 * TC_SPLIT;
+constexpr int TC_PROD_WARPS = 8;     // two threads per weight row convert the A stages
+constexpr int TC_EPI_WARPS = 16;     // four threads per weight row (= TMEM lane) fold a quarter of the columns each
+constexpr int TC_WORKERS = (TC_PROD_WARPS + TC_EPI_WARPS) * 32;
 
 __global__ void __launch_bounds__(TC_WORKERS + 64, 1)
 q4k_gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ hdr, int rows, int bpr, const __half* __restrict__ xh,
@@ -173,9 +174,9 @@ q4k_gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ h
 
     if (warp == MMA_WARP) {
         if (lane == 0) {
-            for (int s = 0; s < TC_STAGES; ++s) { skd::mbar_init(full + s, TC_WORKERS / 32 + 1); skd::mbar_init(empty + s, 1); }
+            for (int s = 0; s < TC_STAGES; ++s) { skd::mbar_init(full + s, TC_PROD_WARPS + 1); skd::mbar_init(empty + s, 1); }
             for (int b = 0; b < 2; ++b) {
-                skd::mbar_init(s2_full + b, TC_WORKERS / 32 + 1); skd::mbar_init(acc_full + b, 1); skd::mbar_init(acc_empty + b, TC_WORKERS / 32);
+                skd::mbar_init(s2_full + b, TC_PROD_WARPS + 1); skd::mbar_init(acc_full + b, 1); skd::mbar_init(acc_empty + b, TC_EPI_WARPS);
             }
             skd::mbar_fence_init();
         }
@@ -249,23 +250,119 @@ q4k_gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ h
             }
         }
         __syncwarp();
-    } else {
-        // ------------------------------------- producers of A, then epilogue -------------------------------------
-        const int r = tid & 127, part = tid >> 7;       // weight row of the tile; which quarter of a group / of the columns
+    } else if (warp < TC_PROD_WARPS) {
+        // ------------------------------------------- producers of the A operand -------------------------------------------
+        // Never touch TMEM: they run ahead of the MMAs by the depth of the stage ring while the epilogue warps fold.
+        const int r = tid & 127, half = tid >> 7;       // weight row of the tile; which 16 bytes of each 32-byte group
         const int grow = min(row0 + r, rows - 1);
-        constexpr int NC = TC_N / TC_SPLIT;
+        bool ok = true;
+        // this thread's 16 bytes of each 32-byte group of the row's super-block, and the header; one block ahead
+        uint4 q[4], qn[4];
+        uint4 hd, hdn;
+        {
+            const size_t blk = (size_t) grow * bpr;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) qn[i] = ld_nc_v4(qs + blk * 128 + i * 32 + half * 16);
+            hdn = ld_nc_v4(hdr + blk * 16);
+        }
+        int s = 0, round = 0;
+        for (int kb = 0; kb < bpr && ok; ++kb) {
+            const int set = kb & 1;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) q[i] = qn[i];
+            hd = hdn;
+            if (kb + 1 < bpr) {
+                const size_t blk = (size_t) grow * bpr + kb + 1;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) qn[i] = ld_nc_v4(qs + blk * 128 + i * 32 + half * 16);
+                hdn = ld_nc_v4(hdr + blk * 16);
+            }
+            uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
+            skd::k4_unpack(hd.y, hd.z, hd.w, sc_lo, sc_hi, mn_lo, mn_hi);
+
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {              // stage = groups 2j, 2j+1 of the super-block
+                if (round > 0 && !__all_sync(0xffffffffu, wait_backoff(empty + s, (round - 1) & 1, timeout_flag))) { ok = false; break; }
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int gq = 2 * j + h;
+                    // 64-k half: k 0..31 = low nibbles x sc[2gq], k 32..63 = high nibbles x sc[2gq+1]; this thread's four
+                    // words are bytes 16*half.. of the group: chunks 2*half, 2*half+1 of each nibble half. High nibbles
+                    // stay in place (f16 1024 + 16 n) and take scale/16, so only the odd bytes need a shift.
+                    const uint32_t scw = gq < 2 ? sc_lo : sc_hi;
+                    const int i_lo = (int) ((scw >> (16 * (gq & 1))) & 0xff), i_hi = (int) ((scw >> (16 * (gq & 1) + 8)) & 0xff);
+                    const __half2 ml = __half2half2(__int2half_rn(i_lo)), mh = __half2half2(__hmul(__int2half_rn(i_hi), __float2half_rn(0.0625f)));
+                    const __half2 nl = __hmul2(ml, __float2half2_rn(-1024.0f)), nh = __hmul2(mh, __float2half2_rn(-1024.0f));
+                    const uint32_t wv[4] = {q[gq].x, q[gq].y, q[gq].z, q[gq].w};
+                    // 128-byte rows, chunk index XOR row (128B swizzle)
+                    uint8_t* arow = smem + s * TC_STAGE_BYTES + h * (TC_A_BYTES / 2) + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+                    for (int p2 = 0; p2 < 2; ++p2) {
+                        const int part = 2 * half + p2;
+                        uint32_t lo4[4], hi4[4];
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const uint32_t w = wv[2 * p2 + e], w8 = w >> 8;
+                            const uint32_t x02 = (w & 0x000f000fu) | 0x64006400u, x13 = (w8 & 0x000f000fu) | 0x64006400u;
+                            const uint32_t y02 = (w & 0x00f000f0u) | 0x64006400u, y13 = (w8 & 0x00f000f0u) | 0x64006400u;
+                            __half2 v;
+                            v = __hfma2(*reinterpret_cast<const __half2*>(&x02), ml, nl); lo4[2 * e] = *reinterpret_cast<uint32_t*>(&v);
+                            v = __hfma2(*reinterpret_cast<const __half2*>(&x13), ml, nl); lo4[2 * e + 1] = *reinterpret_cast<uint32_t*>(&v);
+                            v = __hfma2(*reinterpret_cast<const __half2*>(&y02), mh, nh); hi4[2 * e] = *reinterpret_cast<uint32_t*>(&v);
+                            v = __hfma2(*reinterpret_cast<const __half2*>(&y13), mh, nh); hi4[2 * e + 1] = *reinterpret_cast<uint32_t*>(&v);
+                        }
+                        *reinterpret_cast<uint4*>(arow + ((part ^ (r & 7)) << 4)) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
+                        *reinterpret_cast<uint4*>(arow + (((4 + part) ^ (r & 7)) << 4)) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
+                    }
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive1(full + s);
+                if (++s == TC_STAGES) { s = 0; ++round; }
+            }
+            if (!ok) break;
+            // S2 operand of this super-block: mins (each twice) against the sums of 16 codes. Its buffer was last read by
+            // the S2 MMA of super-block kb-2, whose completion acc_full[set] reported (observed here, not consumed).
+            {
+                if (kb >= 2 && !__all_sync(0xffffffffu, wait_backoff(acc_full + set, ((kb >> 1) - 1) & 1, timeout_flag))) { ok = false; break; }
+                uint8_t* s2 = smem + TC_OFF_S2 + set * TC_S2_BYTES;
+                const uint32_t mnw = half ? mn_hi : mn_lo;           // half 0 / 1 writes the chunks of sub-blocks 0..3 / 4..7
+                uint32_t mm[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const __half2 vv = __half2half2(__int2half_rn((int) ((mnw >> (8 * i)) & 0xff)));
+                    mm[i] = *reinterpret_cast<const uint32_t*>(&vv);
+                }
+                *reinterpret_cast<uint4*>(s2 + (r >> 3) * 256 + half * 128 + (r & 7) * 16) = make_uint4(mm[0], mm[1], mm[2], mm[3]);
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive1(s2_full + set);
+            }
+        }
+        if (!ok) {                                      // give copies in flight time to land before the CTA leaves
+            for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        }
+    } else {
+        // ------------------------------- epilogue: fold every super-block out of TMEM -------------------------------
+        const int e = tid - TC_PROD_WARPS * 32;
+        const int r = e & 127, part = e >> 7;           // TMEM lane = weight row (warp % 4 is its 32-lane quarter); which share of the columns
+        const int grow = min(row0 + r, rows - 1);
+        constexpr int NC = TC_N / (TC_EPI_WARPS / 4);
         float yacc[NC];
 #pragma unroll
         for (int i = 0; i < NC; ++i) yacc[i] = 0.0f;
-        float d_prev = 0.0f, dmin_prev = 0.0f;
         bool ok = true;
-
-        auto fold = [&](int kb, float dw, float dminw) {        // super-block kb out of TMEM into yacc
+        uint32_t ddn = *reinterpret_cast<const uint32_t*>(hdr + (size_t) grow * bpr * 16);      // (d, dmin) of the row's block, one ahead
+        for (int kb = 0; kb < bpr && ok; ++kb) {
             const int set = kb & 1;
+            const uint32_t dd = ddn;
+            if (kb + 1 < bpr) ddn = *reinterpret_cast<const uint32_t*>(hdr + ((size_t) grow * bpr + kb + 1) * 16);
+            const float dw = __half2float(__ushort_as_half((unsigned short) (dd & 0xffff)));
+            const float dminw = __half2float(__ushort_as_half((unsigned short) (dd >> 16)));
             // the verdict of a wait is made warp-uniform: the lanes meet again at the __syncwarp before the arrive
-            if (!__all_sync(0xffffffffu, wait_backoff(acc_full + set, (kb >> 1) & 1, timeout_flag))) { ok = false; return; }
+            if (!__all_sync(0xffffffffu, wait_backoff(acc_full + set, (kb >> 1) & 1, timeout_flag))) { ok = false; break; }
             // the block scales below were written by a bulk copy: observe the barrier that tracked it (long complete)
-            if (!__all_sync(0xffffffffu, wait_backoff(s2_full + set, (kb >> 1) & 1, timeout_flag))) { ok = false; return; }
+            if (!__all_sync(0xffffffffu, wait_backoff(s2_full + set, (kb >> 1) & 1, timeout_flag))) { ok = false; break; }
             tc_fence_after();
             const float* dx = (const float*) (smem + TC_OFF_DX) + (kb % TC_DX_SLOTS) * TC_N + part * NC;
             const uint32_t t0 = tmem + ((uint32_t) ((warp & 3) * 32) << 16) + set * 256 + part * NC;
@@ -286,93 +383,7 @@ q4k_gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ h
             fence_async_smem();                        // the scales just read will be overwritten through the async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive1(acc_empty + set);
-        };
-
-        // this thread's 8 bytes of each 32-byte group of the row's super-block, and the header; one block ahead
-        uint2 q[4], qn[4];
-        uint4 hd, hdn;
-        {
-            const size_t blk = (size_t) grow * bpr;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) qn[i] = ld_nc_v2(qs + blk * 128 + i * 32 + part * 8);
-            hdn = ld_nc_v4(hdr + blk * 16);
         }
-        int s = 0, round = 0;
-        for (int kb = 0; kb < bpr && ok; ++kb) {
-            const int set = kb & 1;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) q[i] = qn[i];
-            hd = hdn;
-            if (kb + 1 < bpr) {
-                const size_t blk = (size_t) grow * bpr + kb + 1;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) qn[i] = ld_nc_v2(qs + blk * 128 + i * 32 + part * 8);
-                hdn = ld_nc_v4(hdr + blk * 16);
-            }
-            const float dw = __half2float(__ushort_as_half((unsigned short) (hd.x & 0xffff)));
-            const float dminw = __half2float(__ushort_as_half((unsigned short) (hd.x >> 16)));
-            uint32_t sc_lo, sc_hi, mn_lo, mn_hi;
-            skd::k4_unpack(hd.y, hd.z, hd.w, sc_lo, sc_hi, mn_lo, mn_hi);
-
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {              // stage = groups 2j, 2j+1 of the super-block
-                if (round > 0 && !__all_sync(0xffffffffu, wait_backoff(empty + s, (round - 1) & 1, timeout_flag))) { ok = false; break; }
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int gq = 2 * j + h;
-                    // 64-k half: k 0..31 = low nibbles x sc[2gq], k 32..63 = high nibbles x sc[2gq+1]; this thread's two
-                    // words are bytes 8*part.. of the group: chunk `part` of each nibble half. High nibbles stay in
-                    // place (f16 1024 + 16 n) and take scale/16, so only the odd bytes need a shift.
-                    const uint32_t scw = gq < 2 ? sc_lo : sc_hi;
-                    const int i_lo = (int) ((scw >> (16 * (gq & 1))) & 0xff), i_hi = (int) ((scw >> (16 * (gq & 1) + 8)) & 0xff);
-                    const __half2 ml = __half2half2(__int2half_rn(i_lo)), mh = __half2half2(__hmul(__int2half_rn(i_hi), __float2half_rn(0.0625f)));
-                    const __half2 nl = __hmul2(ml, __float2half2_rn(-1024.0f)), nh = __hmul2(mh, __float2half2_rn(-1024.0f));
-                    const uint32_t wv[2] = {q[gq].x, q[gq].y};
-                    // 128-byte rows, chunk index XOR row (128B swizzle)
-                    uint8_t* arow = smem + s * TC_STAGE_BYTES + h * (TC_A_BYTES / 2) + (r >> 3) * 1024 + (r & 7) * 128;
-                    uint32_t lo4[4], hi4[4];
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const uint32_t w = wv[e], w8 = w >> 8;
-                        const uint32_t x02 = (w & 0x000f000fu) | 0x64006400u, x13 = (w8 & 0x000f000fu) | 0x64006400u;
-                        const uint32_t y02 = (w & 0x00f000f0u) | 0x64006400u, y13 = (w8 & 0x00f000f0u) | 0x64006400u;
-                        __half2 v;
-                        v = __hfma2(*reinterpret_cast<const __half2*>(&x02), ml, nl); lo4[2 * e] = *reinterpret_cast<uint32_t*>(&v);
-                        v = __hfma2(*reinterpret_cast<const __half2*>(&x13), ml, nl); lo4[2 * e + 1] = *reinterpret_cast<uint32_t*>(&v);
-                        v = __hfma2(*reinterpret_cast<const __half2*>(&y02), mh, nh); hi4[2 * e] = *reinterpret_cast<uint32_t*>(&v);
-                        v = __hfma2(*reinterpret_cast<const __half2*>(&y13), mh, nh); hi4[2 * e + 1] = *reinterpret_cast<uint32_t*>(&v);
-                    }
-                    *reinterpret_cast<uint4*>(arow + ((part ^ (r & 7)) << 4)) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
-                    *reinterpret_cast<uint4*>(arow + (((4 + part) ^ (r & 7)) << 4)) = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
-                }
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive1(full + s);
-                if (++s == TC_STAGES) { s = 0; ++round; }
-            }
-            if (!ok) break;
-            // S2 operand of this super-block: mins (each twice) against the sums of 16 codes. The buffer is free:
-            // this thread folded super-block kb-2, so the MMA that read it has completed.
-            {
-                uint8_t* s2 = smem + TC_OFF_S2 + set * TC_S2_BYTES;
-                if (part < 2) {                                  // parts 0, 1 write the chunks of sub-blocks 0..3 and 4..7
-                    const uint32_t mnw = part ? mn_hi : mn_lo;
-                    uint32_t mm[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const __half2 vv = __half2half2(__int2half_rn((int) ((mnw >> (8 * i)) & 0xff)));
-                        mm[i] = *reinterpret_cast<const uint32_t*>(&vv);
-                    }
-                    *reinterpret_cast<uint4*>(s2 + (r >> 3) * 256 + part * 128 + (r & 7) * 16) = make_uint4(mm[0], mm[1], mm[2], mm[3]);
-                }
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive1(s2_full + set);
-            }
-            if (kb > 0) fold(kb - 1, d_prev, dmin_prev);
-            d_prev = dw; dmin_prev = dminw;
-        }
-        if (ok && bpr > 0) fold(bpr - 1, d_prev, dmin_prev);
         skd::pdl_wait();                               // y and resid may still be in use by kernels launched before this one
         if (ok && row0 + r < rows) {
 #pragma unroll
@@ -382,7 +393,7 @@ q4k_gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ h
                     y[o] = resid ? resid[o] + yacc[c] : yacc[c];
                 }
         }
-        if (!ok) {                                      // give copies in flight time to land before the CTA leaves
+        if (!ok) {
             for (int i = 0; i < 64; ++i) __nanosleep(1000);
         }
     }

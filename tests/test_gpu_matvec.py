@@ -170,11 +170,13 @@ def test_fused_norm_quant_matvec_residual(gpu, oracle, enc, n, k):
     w.free()
 
 
-def test_tcgen05_rows_tile_kernel_is_exact_and_repeatable(gpu, oracle):
+@pytest.mark.parametrize("n,k,m,runs", [(300, 2048, 290, 10), (129, 4096, 130, 30), (260, 2816, 130, 30), (140, 256, 130, 10)])
+def test_tcgen05_rows_tile_kernel_is_exact_and_repeatable(gpu, oracle, n, k, m, runs):
     """m >= 128 rows take the tcgen05 kernel: several row and column tiles, ragged on both sides. The integer sums
-    are exact in f16 x f16 -> f32, so the result equals the reference's to fp32 rounding, and ten runs are
-    bit-identical (a race between the roles of the kernel shows up as a run that differs)."""
-    n, k, m = 300, 2048, 290
+    are exact in f16 x f16 -> f32, so the result equals the reference's to fp32 rounding, and repeated runs are
+    bit-identical (a race between the roles of the kernel shows up as a run that differs). Shapes: an even and an odd
+    number of super-blocks per row (8, 16, 11) and a single one, where the two accumulator sets and the two block-scale
+    slots are reused with and without a parity change."""
     rng = np.random.default_rng(77)
     wf = (0.02 * rng.standard_normal((n, k))).astype(np.float32)
     packed = oracle.quantize_q4k(wf)
@@ -183,7 +185,7 @@ def test_tcgen05_rows_tile_kernel_is_exact_and_repeatable(gpu, oracle):
     ref = oracle.matmul("Q4_K", x, packed, k, n, "rm", use_ref=oracle.ref() is not None)
     first = gpu.matmul_host(w, x)
     rel_err_ok(first, ref, 1e-5)
-    for _ in range(9):
+    for _ in range(runs - 1):
         np.testing.assert_array_equal(gpu.matmul_host(w, x), first)
     from skainet_b200 import _lib
     assert _lib.lib().skainet_cuda_device_status() == 0
