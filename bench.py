@@ -22,12 +22,17 @@ Prints ONE JSON line (rank 0). Workloads (all inputs synthetic and seeded):
       tokens; metric = generated tokens per second of request time, with the two phases reported apart.
   q4k_gemm — benchmark config 2 at M = --batch rows (default 512) through the tensor-core tile kernels (tcgen05 from 128 rows);
       metric = 2*M*rows*cols operations per second, roofline against the measured cuBLAS bf16 burst.
+  tp_collective — N >= 2 ranks: nothing but the group exchanges of a decode step (one [8192] fp32 row), timed on their own
+      in a CUDA graph: the peer-memory sum, the store + gather + sum + RMSNorm + quantize kernel, and ncclAllReduce of the
+      same row; metric = microseconds per exchange (lower is better). The N > 1 decode lines carry the same three numbers
+      under `tp_exchange`.
 
 `value` is timed on the device with everything resident in HBM (decode: one CUDA-graph replay per
 step, tokens fed back on the device). `e2e` is the same metric through the C ABI with HOST buffers
 (decode: one `skainet_cuda_llama_decode` call per step, token ids host -> device and back, host
 synchronisation every step; matvec: activation in, output out per call, weights resident).
-`roofline` is the dequant-fused matvec kernel measured live over the workload's own weights.
+`roofline.frac` is the whole step (bytes a step must read / step time); `roofline.kernel_*` is the dequant-fused matvec
+path measured live over the workload's own weights.
 `--impl reference` times the reference's own C kernels (oracle/_ref; the port if absent) on the host:
 for decode a CPU composer built from those kernels, measured on a bounded number of layers and scaled.
 PyTorch is used here for events, pinned memory and the process group only.
@@ -376,7 +381,7 @@ def matvec_sweep_rate(torch, device, L, weights_flat, stream, steps: int, warmup
 
 def matvec_configs_summary(torch, device, L, steps: int = 10) -> dict:
     """Benchmark configs 1 (Q8_0 4096x4096) and 2 (Q4_K 11008x4096 + 4096x11008) at M = 1, measured in the same process as the
-    decode line: algorithmic GB/s of the quantizer + matvec pair over a rotation of distinct weights larger than 2x L2, the
+    decode line: algorithmic GB/s of the whole matvec call (activation quantization included) over a rotation of distinct weights larger than 2x L2, the
     fraction of the measured copy bandwidth, and the time a kernel that only reads the same bytes takes."""
     info = device.device_info()
     peak, _ = load_peaks()
@@ -387,15 +392,16 @@ def matvec_configs_summary(torch, device, L, steps: int = 10) -> dict:
         copies = max(2, int(np.ceil(2.2 * info["l2_bytes"] / min(r * (c // be) * bb for r, c in shapes))))
         ws = [device.Weight.synth(enc, r, c, seed=50 + 10 * si + ci, std=0.02) for ci in range(copies) for si, (r, c) in enumerate(shapes)]
         nbytes = sum(algorithmic_bytes(bb, be, w.rows, w.cols) for w in ws)
-        ms, _, graph, keep = matvec_sweep_rate(torch, device, L, ws, stream, steps, 3)
+        ms, launches, graph, keep = matvec_sweep_rate(torch, device, L, ws, stream, steps, 3)
         floor = read_floor_ms(torch, L, ws, stream, steps)
         gbs = nbytes / (ms * 1e-3) / 1e9
         out[key] = {"gbs": gbs, "frac": gbs / peak, "avg_launch_us": ms * 1e3 / len(ws), "read_floor_us": floor * 1e3 / len(ws),
-                    "weights": len(ws), "launches_per_matvec": 2}
+                    "weights": len(ws), "launches_per_matvec": launches / len(ws)}
         del graph, keep
         for w in ws:
             w.free()
-    out["note"] = "M = 1; each matvec = activation quantizer launch + streaming matvec launch, one CUDA graph per sweep; frac of the measured copy bandwidth"
+    out["note"] = ("M = 1 through skainet_cuda_matmul_dev, one CUDA graph per sweep; config 1 = activation quantizer launch + matvec launch, config 2 = one "
+                   "launch (the ring kernel quantizes the row in its prologue); avg_launch_us is per matvec; frac of the measured copy bandwidth")
     return out
 
 
@@ -806,6 +812,66 @@ def tp_parity_check(torch, dist, m, cfg, model_name: str, ctx: int, batch: int, 
     return out
 
 
+def tp_exchange_times(m, torch, dist, rounds: int = 64, reps: int = 20) -> dict:
+    """The group exchanges of a decode step timed on their own (every rank calls; the max over ranks is reported):
+    device microseconds per exchange of one [d_model] fp32 row, `rounds` launches back to back in one CUDA graph."""
+    out = {}
+    for key, mode in (("peer_sum_us", 0), ("send_gather_norm_quant_us", 1), ("nccl_sum_us", 2)):
+        t = torch.tensor([m.tp_exchange_time(mode, rounds, reps)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out[key] = float(t[0])
+    out["note"] = (f"{rounds} exchanges of one [d_model] fp32 row per CUDA graph, {reps} replays between two events, max over ranks. peer_sum: in-place "
+                   "sum through peer memory; send_gather_norm_quant: store + gather + sum + RMSNorm + quantize in one kernel (the decode step's "
+                   "matvec epilogue does the store part itself); nccl_sum: ncclAllReduce of the same row")
+    return out
+
+
+def run_collective(args) -> None:
+    """tp_collective: nothing but the exchanges, on a one-layer model of the 70B width."""
+    import torch
+    import torch.distributed as dist
+    from skainet_b200 import _lib as L, device
+    from skainet_b200.llama import Llama, LlamaConfig
+    rank, world, local = dist_env()
+    if world < 2:
+        raise SystemExit("tp_collective needs 2 or more ranks (launch under torch.distributed.run with --gpus N)")
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local); device.set_device(local)
+    cfg = LlamaConfig(1, 8192, 64, 8, 128, 2048 * world, 256 * world, table_enc="Q4_K", max_seq=512, max_batch=1, tp_rank=rank, tp_world=world)
+    m = Llama(cfg)
+    m.synth(seed=3, std=0.02); m.finalize()
+    ids = [Llama.tp_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(ids, src=0)
+    m.tp_init(ids[0])
+    sampler = ClockSampler(local)
+    dist.barrier(); torch.cuda.synchronize()
+    if rank == 0:
+        sampler.start()
+    for _ in range(max(3, args.warmup)):
+        m.tp_exchange_time(1, 8, 1)
+    times = tp_exchange_times(m, torch, dist, rounds=64, reps=max(1, args.steps))
+    clocks = sampler.stop() if rank == 0 else None
+    status = L.lib().skainet_cuda_device_status()
+    ok = torch.tensor([1 if status == 0 else 0], device="cuda", dtype=torch.int32)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if int(ok[0]) != 1:
+        raise SystemExit(f"rank {rank}: device status {status} ({L.last_error() if status else 'ok'})")
+    if rank == 0:
+        us = times["send_gather_norm_quant_us"]
+        nbytes = 4 * cfg.d_model * (world - 1)          # what one rank stores into its peers per exchange
+        print(json.dumps({
+            "metric": "tp_exchange_us", "value": us, "unit": "us", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": us * 64 * 1e-3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": "tp_collective", "d_model": cfg.d_model, "row_bytes": 4 * cfg.d_model,
+                                            "parallelism": f"tp{world}", "l2": "32 KB rows: latency, not bandwidth, is measured"},
+            "tp_exchange": times,
+            "roofline": {"bound": "nvlink", "achieved": nbytes / (us * 1e-6) / 1e9, "peak": 770.0, "unit": "GB/s", "frac": nbytes / (us * 1e-6) / 1e9 / 770.0,
+                         "traffic": None, "note": "bytes one rank stores to its peers per exchange / time; a 32 KB exchange is bound by one NVLink store latency"},
+            "gpu_launches": 64 * max(1, args.steps) * 3, "clocks": clocks}), flush=True)
+    m.free()
+    dist.destroy_process_group()
+
+
 def run_decode(args) -> None:
     import torch
     import torch.distributed as dist
@@ -904,6 +970,7 @@ def run_decode(args) -> None:
     if int(ok[0]) != 1:
         raise SystemExit(f"rank {rank}: device status {status} ({L.last_error() if status else 'ok'}), logits finite {logits_ok}, tokens in range {tokens_ok}")
     matvec_summary = matvec_configs_summary(torch, device, L) if (world == 1 and not args.skip_cpu) else None
+    tp_exchange = tp_exchange_times(m, torch, dist) if (world > 1 and batch == 1) else None
     if rank == 0:
         peak, peak_kind = load_peaks()
         achieved = mv_bytes / (mv_ms * 1e-3) / 1e9
@@ -933,6 +1000,8 @@ def run_decode(args) -> None:
         }
         if tp_parity is not None:
             line["tp_parity"] = tp_parity
+        if tp_exchange is not None:
+            line["tp_exchange"] = tp_exchange
         if matvec_summary is not None:
             line["matvec"] = matvec_summary
         if world == 1 and not args.skip_cpu:
@@ -949,7 +1018,7 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="decode_70b", choices=sorted(MATVEC_WORKLOADS) + sorted(DECODE_WORKLOADS) + sorted(ATTN_WORKLOADS) + sorted(GEMM_WORKLOADS) + sorted(REQUEST_WORKLOADS))
+    ap.add_argument("--workload", default="decode_70b", choices=sorted(MATVEC_WORKLOADS) + sorted(DECODE_WORKLOADS) + sorted(ATTN_WORKLOADS) + sorted(GEMM_WORKLOADS) + sorted(REQUEST_WORKLOADS) + ["tp_collective"])
     ap.add_argument("--context", type=int, default=4096, help="keys per sequence (attn_decode workload)")
     ap.add_argument("--batch", type=int, default=1, help="sequences decoded together (decode workloads)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -966,6 +1035,8 @@ def main() -> None:
         run_gemm(args)
     elif args.workload in REQUEST_WORKLOADS:
         run_request(args)
+    elif args.workload == "tp_collective":
+        run_collective(args)
     else:
         run_decode(args)
 

@@ -103,6 +103,12 @@ SKAINET_CUDA_API int32_t skainet_cuda_llama_step_cost(skainet_model_t m, int32_t
  * (0 residual stream, 1 merged q|k|v as projected — a decode step rotates q and k inside its attention kernel, a prompt
  * chunk rotates q in place —, 2 attention output, 3 gate|up, 4 q). */
 SKAINET_CUDA_API int32_t skainet_cuda_llama_peek(skainet_model_t m, int32_t which, float* host_out, int64_t n);
+/* Measurement aid (no reference counterpart): the group exchanges of a decode step timed on their own. `rounds` launches
+ * are captured back to back in one CUDA graph and replayed `reps` times between two events; *us_per_round = device time of
+ * one exchange of a [d_model] fp32 row. mode 0: in-place sum through peer memory; 1: store + gather + sum + RMSNorm +
+ * quantize in one kernel (what follows a row-parallel projection); 2: the same sum through NCCL. Collective: every rank
+ * of the group calls it with the same arguments. */
+SKAINET_CUDA_API int32_t skainet_cuda_llama_tp_exchange_time(skainet_model_t m, int32_t mode, int32_t rounds, int32_t reps, float* us_per_round);
 /* The stream the model runs on (for event timing by the caller). */
 SKAINET_CUDA_API int32_t skainet_cuda_llama_stream(skainet_model_t m, skainet_stream_t* out);
 

@@ -107,6 +107,7 @@ SIGNATURES = {
     "skainet_cuda_llama_logits": [i64, i32, f32p],
     "skainet_cuda_llama_step_cost": [i64, i32, i64p],
     "skainet_cuda_llama_peek": [i64, i32, f32p, i64],
+    "skainet_cuda_llama_tp_exchange_time": [i64, i32, i32, i32, f32p],
     "skainet_cuda_llama_stream": [i64, C.POINTER(vp)],
 }
 _RESTYPE = {"skainet_cuda_last_error": C.c_char_p, "skainet_cuda_version": C.c_char_p}

@@ -342,6 +342,12 @@ int32_t comm_all_reduce_sum(Comm* c, float* buf, int64_t n, cudaStream_t s) {
     return r == 0 ? SKAINET_CUDA_OK : nccl_fail(r, "ncclAllReduce");
 }
 
+int32_t comm_all_reduce_sum_nccl(Comm* c, float* buf, int64_t n, cudaStream_t s) {
+    if (!c) { set_error("tensor-parallel model without a communicator (call llama_tp_init)"); return SKAINET_CUDA_ERR_COMM; }
+    const ncclResult_t r = g_nccl.AllReduce(buf, buf, (size_t) n, ncclFloat32, ncclSum, c->comm, s);
+    return r == 0 ? SKAINET_CUDA_OK : nccl_fail(r, "ncclAllReduce");
+}
+
 static bool fused_shape_ok(const Comm* c, const float* x, int rows, int n) {
     if (!c || !c->p2p || n % P2P_FUSED_CTA_ELEMS != 0) return false;
     const int cs = n / P2P_FUSED_CTA_ELEMS;

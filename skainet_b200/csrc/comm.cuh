@@ -25,6 +25,8 @@ int32_t comm_create(int rank, int world, const uint8_t* id128, Comm** out);
 void comm_destroy(Comm* c);
 // in place, fp32, sum over the group
 int32_t comm_all_reduce_sum(Comm* c, float* buf, int64_t n, cudaStream_t s);
+// the same sum through NCCL whatever the size (the measurement entry compares the two)
+int32_t comm_all_reduce_sum_nccl(Comm* c, float* buf, int64_t n, cudaStream_t s);
 // x[rows][n] <- group sum; act <- int8-per-256 quantization of rmsnorm(x, gamma). 1 = not applicable (do it in two steps)
 struct ActQ8K;
 int32_t comm_all_reduce_norm_quant(Comm* c, float* x, int rows, int n, const float* gamma, float eps, ActQ8K act, cudaStream_t s);

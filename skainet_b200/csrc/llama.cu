@@ -723,6 +723,58 @@ int32_t skainet_cuda_llama_tp_init(skainet_model_t h, const uint8_t* id128) {
     return comm_create(m->cfg.tp_rank, m->cfg.tp_world, id128, &m->comm);
 }
 
+// Times the group exchanges of a decode step on their own: `rounds` back-to-back launches captured in one CUDA graph,
+// replayed `reps` times between two events on the model's stream. Collective: every rank calls it with the same arguments.
+int32_t skainet_cuda_llama_tp_exchange_time(skainet_model_t h, int32_t mode, int32_t rounds, int32_t reps, float* us_per_round) {
+    Model* m = model_from_handle(h);
+    if (!m) return SKAINET_CUDA_ERR_HANDLE;
+    SK_REQUIRE(us_per_round != nullptr && rounds >= 1 && rounds <= 1024 && reps >= 1, "llama_tp_exchange_time: bad arguments");
+    SK_REQUIRE(m->cfg.tp_world > 1 && m->comm != nullptr, "llama_tp_exchange_time: not a tensor-parallel model with a communicator");
+    SK_REQUIRE(mode >= 0 && mode <= 2, "llama_tp_exchange_time: unknown mode %d", mode);
+    SK_TRY(set_device_of(*m));
+    const auto& c = m->cfg;
+    cudaStream_t s = m->stream;
+    SK_CUDA(cudaMemsetAsync(m->x, 0, sizeof(float) * c.d_model, s));         // sums of zeros stay finite however many rounds run
+    auto one = [&]() -> int32_t {
+        if (mode == 0) return comm_all_reduce_sum(m->comm, m->x, c.d_model, s);
+        if (mode == 2) return comm_all_reduce_sum_nccl(m->comm, m->x, c.d_model, s);
+        const int32_t st = comm_all_reduce_norm_quant(m->comm, m->x, 1, c.d_model, m->layers[0].g_attn, c.rms_eps, act_q8k_layout(m->act, 1, c.d_model), s);
+        if (st == 1) { set_error("llama_tp_exchange_time: the fused exchange does not apply to this model (no peer mapping or d_model outside its slots)"); return SKAINET_CUDA_ERR_INVALID; }
+        return st;
+    };
+    SK_TRY(one());                                                              // outside capture once: lazy initialisation
+    SK_CUDA(cudaStreamSynchronize(s));
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    SK_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+    int32_t st = SKAINET_CUDA_OK;
+    for (int i = 0; i < rounds && st == SKAINET_CUDA_OK; ++i) st = one();
+    const cudaError_t ce = cudaStreamEndCapture(s, &graph);
+    if (st != SKAINET_CUDA_OK) { if (graph) cudaGraphDestroy(graph); return st; }
+    SK_CUDA(ce);
+    cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    SK_CUDA(e);
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    float ms = 0.0f;
+    e = cudaEventCreate(&e0);
+    if (e == cudaSuccess) e = cudaEventCreate(&e1);
+    for (int i = 0; i < 2 && e == cudaSuccess; ++i) e = cudaGraphLaunch(exec, s);
+    if (e == cudaSuccess) e = cudaEventRecord(e0, s);
+    for (int i = 0; i < reps && e == cudaSuccess; ++i) e = cudaGraphLaunch(exec, s);
+    if (e == cudaSuccess) e = cudaEventRecord(e1, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    cudaGraphExecDestroy(exec);
+    SK_CUDA(e);
+    *us_per_round = ms * 1000.0f / ((float) rounds * (float) reps);
+    SK_TRY(flag_fetch(*m, s));
+    SK_CUDA(cudaStreamSynchronize(s));
+    return flag_check(*m);
+}
+
 int32_t skainet_cuda_llama_reset(skainet_model_t h) {
     Model* m = model_from_handle(h);
     if (!m) return SKAINET_CUDA_ERR_HANDLE;

@@ -218,27 +218,31 @@ q4k_matvec_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict
 // ================================================================================================
 constexpr int RG8_COLS = 2048;
 
-template <int NC, int PREP, int EPI>
-__global__ void __launch_bounds__((NC + 1) * 32)
+template <int NC, int NG, int PREP, int EPI>
+__global__ void __launch_bounds__(NG * (NC + 1) * 32)
 q8_0_matvec_ring_kernel(const int8_t* __restrict__ codes, const __half* __restrict__ scales, int rows, int cols, MatvecIn in,
                         float* __restrict__ y, const float* __restrict__ resid, int nstages, int* __restrict__ timeout_flag) {
     constexpr int S_CODES = NC * RG8_COLS, S_SC = NC * (RG8_COLS / 32) * 2, S_BYTES = S_CODES + S_SC;
     extern __shared__ __align__(128) uint8_t smem[];
+    // NG groups (producer warp + NC consumer warps, own ring and barriers) around one staged activation, as in the Q4_K kernel
     const int bpr = cols >> 5;
-    uint8_t* s_ring = smem;
-    int8_t* s_hi = (int8_t*) (s_ring + (size_t) nstages * S_BYTES);
+    const int lane = threadIdx.x & 31;
+    const int grp = NG == 1 ? 0 : (int) (threadIdx.x >> 5) / (NC + 1);
+    const int warp = (int) (threadIdx.x >> 5) - grp * (NC + 1);
+    uint8_t* s_ring = smem + (size_t) grp * nstages * S_BYTES;
+    int8_t* s_hi = (int8_t*) (smem + (size_t) NG * nstages * S_BYTES);
     int8_t* s_lo = s_hi + cols;
     float* s_dx = (float*) (s_lo + cols);
-    float* s_red = (float*) ((uint8_t*) s_dx + ((bpr * 4 + 15) & ~15));
-    uint64_t* full = (uint64_t*) (s_red + 8);
+    float* s_red = (float*) ((uint8_t*) s_dx + ((bpr * 4 + 15) & ~15));     // NG * NC floats (at most 16)
+    uint64_t* full = (uint64_t*) (s_red + 16) + grp * 2 * RG_MAX_STAGES;
     uint64_t* empty = full + RG_MAX_STAGES;
 
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int vcta = (int) blockIdx.x * NG + grp, vgrid = (int) gridDim.x * NG;
     const int nrg = (rows + NC - 1) / NC;
     const int ncg = (cols + RG8_COLS - 1) / RG8_COLS;
-    const int my_rgs = (int) blockIdx.x < nrg ? (nrg - 1 - (int) blockIdx.x) / (int) gridDim.x + 1 : 0;
+    const int my_rgs = vcta < nrg ? (nrg - 1 - vcta) / vgrid + 1 : 0;
 
-    if (threadIdx.x == 0) {
+    if (warp == NC && lane == 0) {
         for (int s = 0; s < nstages; ++s) { skd::mbar_init(full + s, 1); skd::mbar_init(empty + s, NC); }
         skd::mbar_fence_init();
     }
@@ -248,7 +252,7 @@ q8_0_matvec_ring_kernel(const int8_t* __restrict__ codes, const __half* __restri
     if (warp == NC) {
         int stage = 0, round = 0;
         for (int rgi = 0; rgi < my_rgs; ++rgi) {
-            const int row0 = ((int) blockIdx.x + rgi * (int) gridDim.x) * NC, nr = min(NC, rows - row0);
+            const int row0 = (vcta + rgi * vgrid) * NC, nr = min(NC, rows - row0);
             for (int cg = 0; cg < ncg; ++cg) {
                 if (round > 0 && !skd::mbar_wait_bounded(empty + stage, (round - 1) & 1, timeout_flag)) return;
                 const int c0 = cg * RG8_COLS, nc = min(RG8_COLS, cols - c0);
@@ -268,15 +272,15 @@ q8_0_matvec_ring_kernel(const int8_t* __restrict__ codes, const __half* __restri
     }
 
     skd::pdl_wait();
-    split_prep_to_smem<PREP, NC, 1>(in, cols, bpr, s_hi, s_lo, s_dx, s_red, warp, lane, threadIdx.x);
-    consumer_sync<NC>();
+    split_prep_to_smem<PREP, NG * NC, RG_BAR_ALL>(in, cols, bpr, s_hi, s_lo, s_dx, s_red, grp * NC + warp, lane, (grp * NC + warp) * 32 + lane);
+    prep_sync<NG * NC, RG_BAR_ALL>();
 
     uint4 ah[4], al[4];
     float dx[4];
     int stage = 0, phase = 0;
     for (int rgi = 0; rgi < my_rgs; ++rgi) {
         const bool first = rgi == 0;
-        const int rg = (int) blockIdx.x + rgi * (int) gridDim.x;
+        const int rg = vcta + rgi * vgrid;
         float acc = 0.0f;
         for (int cg = 0; cg < ncg; ++cg) {
             const int c0 = cg * RG8_COLS, nc = min(RG8_COLS, cols - c0);
@@ -322,31 +326,7 @@ q8_0_matvec_ring_kernel(const int8_t* __restrict__ codes, const __half* __restri
 // ================================================================================================
 // dispatch (m = 1). Returns 1 when the shape is outside what these take.
 // ================================================================================================
-struct RingPlan { int nc, cps, nstages; size_t smem; };
-
-// Q8_0: as many consumer warps per SM as the shared-memory budget allows with at least three stages per ring.
-static bool plan_ring(size_t fixed, size_t stage_bytes_per_row, RingPlan* p) {
-    const int ncs[4] = {4, 4, 8, 8}, cpss[4] = {4, 3, 2, 1};
-    for (int i = 0; i < 4; ++i) {
-        const size_t per_cta = ring_budget() / cpss[i];
-        const size_t sb = stage_bytes_per_row * ncs[i];
-        if (per_cta <= fixed + 256) continue;
-        const int ns = (int) std::min<size_t>(RG_MAX_STAGES, (per_cta - fixed - 256) / sb);
-        if (ns >= 3) { p->nc = ncs[i]; p->cps = cpss[i]; p->nstages = ns; p->smem = fixed + 256 + ns * sb; return true; }
-    }
-    return false;
-}
-
-#define SK_RG_LAUNCH(KERNEL, NCV, ...)                                                                        \
-    do {                                                                                                      \
-        SK_TRY(ensure_dynamic_smem((const void*) KERNEL, (int) RG_SMEM_MAX + 1024));                          \
-        const int nrg = (w.rows + NCV - 1) / NCV;                                                             \
-        const int grid = std::min(sm_count() * plan.cps, nrg);                                                \
-        SK_CUDA(launch_pdl(KERNEL, dim3(grid), dim3((NCV + 1) * 32), plan.smem, s, __VA_ARGS__));             \
-        return SKAINET_CUDA_OK;                                                                               \
-    } while (0)
-
-// Q4_K: one CTA per SM of RG_GROUPS groups; the ring depth is what the activation leaves of the budget.
+// One CTA per SM of RG_GROUPS groups; the ring depth is what the activation leaves of the budget.
 constexpr int RG_GROUPS = 4, RG_GROUP_ROWS = 4;
 template <int PREP, int EPI>
 static int32_t launch_q4k_ring(const Weight& w, const MatvecIn& in, float* y, const float* resid, int* flag, cudaStream_t s,
@@ -364,27 +344,24 @@ static int32_t launch_q4k_ring(const Weight& w, const MatvecIn& in, float* y, co
     return SKAINET_CUDA_OK;
 }
 template <int PREP, int EPI>
-static int32_t launch_q8_ring(const Weight& w, const MatvecIn& in, float* y, const float* resid, const RingPlan& plan, int* flag, cudaStream_t s) {
-    if (plan.nc == 4)
-        SK_RG_LAUNCH((q8_0_matvec_ring_kernel<4, PREP, EPI>), 4, (const int8_t*) w.qs, (const __half*) w.hdr, w.rows, w.cols, in, y, resid, plan.nstages, flag);
-    SK_RG_LAUNCH((q8_0_matvec_ring_kernel<8, PREP, EPI>), 8, (const int8_t*) w.qs, (const __half*) w.hdr, w.rows, w.cols, in, y, resid, plan.nstages, flag);
+static int32_t launch_q8_ring(const Weight& w, const MatvecIn& in, float* y, const float* resid, int* flag, cudaStream_t s) {
+    constexpr size_t STAGE = (size_t) RG_GROUPS * RG_GROUP_ROWS * (RG8_COLS + RG8_COLS / 16);
+    const size_t fixed = (size_t) 2 * w.cols + ((w.bpr * 4 + 15) & ~15) + 64 + RG_GROUPS * 2 * RG_MAX_STAGES * 8 + 256;
+    if (ring_budget() <= fixed) return 1;
+    const int ns = (int) std::min<size_t>(RG_MAX_STAGES, (ring_budget() - fixed) / STAGE);
+    if (ns < 3) return 1;
+    auto kernel = q8_0_matvec_ring_kernel<RG_GROUP_ROWS, RG_GROUPS, PREP, EPI>;
+    SK_TRY(ensure_dynamic_smem((const void*) kernel, (int) RG_SMEM_MAX + 1024));
+    const int nrg = (w.rows + RG_GROUP_ROWS - 1) / RG_GROUP_ROWS, grid = std::min(sm_count(), (nrg + RG_GROUPS - 1) / RG_GROUPS);
+    SK_CUDA(launch_pdl(kernel, dim3(grid), dim3(RG_GROUPS * (RG_GROUP_ROWS + 1) * 32), fixed + ns * STAGE, s, (const int8_t*) w.qs,
+                       (const __half*) w.hdr, w.rows, w.cols, in, y, resid, ns, flag));
+    return SKAINET_CUDA_OK;
 }
-
-#define SK_RG_PE(FN)                                                                                              \
-    switch (prep * 2 + (resid ? EPI_ADD : EPI_STORE)) {                                                           \
-        case PREP_QUANTIZED * 2 + EPI_STORE: return FN<PREP_QUANTIZED, EPI_STORE>(w, in, y, resid, plan, flag, s); \
-        case PREP_QUANTIZED * 2 + EPI_ADD:   return FN<PREP_QUANTIZED, EPI_ADD>(w, in, y, resid, plan, flag, s);   \
-        case PREP_F32 * 2 + EPI_STORE:       return FN<PREP_F32, EPI_STORE>(w, in, y, resid, plan, flag, s);       \
-        case PREP_F32 * 2 + EPI_ADD:         return FN<PREP_F32, EPI_ADD>(w, in, y, resid, plan, flag, s);         \
-        case PREP_NORM_F32 * 2 + EPI_STORE:  return FN<PREP_NORM_F32, EPI_STORE>(w, in, y, resid, plan, flag, s);  \
-        default:                             return FN<PREP_NORM_F32, EPI_ADD>(w, in, y, resid, plan, flag, s);    \
-    }
 
 int32_t launch_matvec_ring(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s, const PeerOut* peer) {
     int* flag = device_timeout_flag();
     if (w.rows <= 0) return 1;
     if (peer && (w.enc != SKAINET_ENC_Q4_K || prep != PREP_QUANTIZED)) return 1;
-    RingPlan plan;
     if (w.enc == SKAINET_ENC_Q4_K) {
         if (peer) return launch_q4k_ring<PREP_QUANTIZED, EPI_PEER>(w, in, y, resid, flag, s, *peer);
         switch (prep * 2 + (resid ? EPI_ADD : EPI_STORE)) {
@@ -398,9 +375,14 @@ int32_t launch_matvec_ring(const Weight& w, const MatvecIn& in, int prep, float*
     }
     if (w.enc == SKAINET_ENC_Q8_0) {
         if (w.cols % 256 != 0) return 1;
-        const size_t fixed = (size_t) 2 * w.cols + ((w.bpr * 4 + 15) & ~15) + 32 + 2 * RG_MAX_STAGES * 8 + 64;
-        if (!plan_ring(fixed, RG8_COLS + RG8_COLS / 16, &plan)) return 1;
-        SK_RG_PE(launch_q8_ring)
+        switch (prep * 2 + (resid ? EPI_ADD : EPI_STORE)) {
+            case PREP_QUANTIZED * 2 + EPI_STORE: return launch_q8_ring<PREP_QUANTIZED, EPI_STORE>(w, in, y, resid, flag, s);
+            case PREP_QUANTIZED * 2 + EPI_ADD:   return launch_q8_ring<PREP_QUANTIZED, EPI_ADD>(w, in, y, resid, flag, s);
+            case PREP_F32 * 2 + EPI_STORE:       return launch_q8_ring<PREP_F32, EPI_STORE>(w, in, y, resid, flag, s);
+            case PREP_F32 * 2 + EPI_ADD:         return launch_q8_ring<PREP_F32, EPI_ADD>(w, in, y, resid, flag, s);
+            case PREP_NORM_F32 * 2 + EPI_STORE:  return launch_q8_ring<PREP_NORM_F32, EPI_STORE>(w, in, y, resid, flag, s);
+            default:                             return launch_q8_ring<PREP_NORM_F32, EPI_ADD>(w, in, y, resid, flag, s);
+        }
     }
     return 1;
 }

@@ -145,6 +145,13 @@ class Llama:
         L.check(L.lib().skainet_cuda_llama_peek(self.handle, which, out.ctypes.data_as(L.f32p), n))
         return out
 
+    def tp_exchange_time(self, mode: int, rounds: int = 64, reps: int = 20) -> float:
+        """Device microseconds of one group exchange of a [d_model] row, timed on its own (collective: all ranks call it).
+        mode 0 peer-memory sum, 1 store + gather + sum + RMSNorm + quantize, 2 NCCL sum."""
+        out = C.c_float()
+        L.check(L.lib().skainet_cuda_llama_tp_exchange_time(self.handle, mode, rounds, reps, C.byref(out)))
+        return float(out.value)
+
     def step_cost(self, batch: int = 1) -> tuple[int, int]:
         out = (C.c_int64 * 2)()
         L.check(L.lib().skainet_cuda_llama_step_cost(self.handle, batch, out))

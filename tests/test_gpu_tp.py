@@ -66,6 +66,17 @@ def test_tp2_matches_single_gpu(gpu, d_model, env):
     check_against_single(single(d_model), run_world(2, d_model, env), f"TP2 {env}")
 
 
+def test_tp2_exchange_timing_entry_leaves_the_group_consistent(gpu):
+    """skainet_cuda_llama_tp_exchange_time (what the bench's tp_collective workload and `tp_exchange` key call) returns a
+    positive device time for the peer-memory sum, the fused store + gather + norm + quantize kernel and the NCCL sum, and a
+    decode after those exchange rounds still matches the single-GPU run."""
+    if gpu.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    out = run_world(2, 4096, {"SKAINET_TEST_EXCHANGE": "1"})
+    assert (out["exchange_us"] > 0).all() and (out["exchange_us"] < 1e4).all(), out["exchange_us"]
+    check_against_single(single(4096), out, "TP2 after exchange timing")
+
+
 def test_tp4_matches_single_gpu(gpu):
     if gpu.device_count() < 4:
         pytest.skip("needs 4 GPUs")

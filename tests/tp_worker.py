@@ -40,13 +40,17 @@ def main():
                 time.sleep(0.05)
             uid = open(idf, "rb").read()
         m.tp_init(uid)
+    # The exchange timing entry runs real exchange rounds on both inbox channels: the decode that follows must be unaffected.
+    xt = np.zeros(3, np.float32)
+    if world > 1 and os.environ.get("SKAINET_TEST_EXCHANGE") == "1":
+        xt = np.array([m.tp_exchange_time(mode, 7, 3) for mode in (0, 1, 2)], np.float32)
     prompts = [[5, 17, 900, 33, 2, 640], [7, 7, 123]]
     firsts = [m.prefill(p, seq=i) for i, p in enumerate(prompts)]
     logits0 = m.logits(1)
     toks = m.generate(firsts, 6)
     logits = m.logits(2)
     if rank == 0:
-        np.savez(os.path.join(work, "out.npz"), firsts=np.array(firsts), toks=toks, logits=logits, logits0=logits0)
+        np.savez(os.path.join(work, "out.npz"), firsts=np.array(firsts), toks=toks, logits=logits, logits0=logits0, exchange_us=xt)
     m.free()
 
 
