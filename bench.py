@@ -340,10 +340,10 @@ def read_floor_ms(torch, L, weights_flat, stream, steps: int) -> float:
 
 
 def matmul_launches(w) -> int:
-    """Kernels one skainet_cuda_matmul_dev call of one activation row launches: a Q4_K weight of 20 MiB or more with at
+    """Kernels one skainet_cuda_matmul_dev call of one activation row launches: a Q4_K weight of 4 MiB or more with at
     most 12288 columns takes the ring kernel with the quantizer in its prologue (one launch); everything else is a quantizer
     launch followed by the matvec (csrc/api.cu)."""
-    return 1 if (w.encoding == "Q4_K" and w.packed_bytes >= (20 << 20) and w.cols <= 12288) else 2
+    return 1 if (w.encoding == "Q4_K" and w.packed_bytes >= (4 << 20) and w.cols <= 12288) else 2
 
 
 def matvec_sweep_rate(torch, device, L, weights_flat, stream, steps: int, warmup: int):

@@ -470,10 +470,10 @@ int32_t skainet_cuda_matmul_dev(skainet_weight_t h, const float* x_dev, int32_t 
     SK_TRY(ensure_device());
     cudaStream_t s = as_stream(stream);
     if (w->cols == 0) { SK_CUDA(cudaMemsetAsync(y_dev, 0, sizeof(float) * (size_t) m * w->rows, s)); return SKAINET_CUDA_OK; }
-    // One activation row of a ring-sized Q4_K weight: a single launch, the ring kernel quantizes the row in its own
+    // One activation row of a Q4_K weight of 4 MB or more: a single launch, the ring kernel quantizes the row in its own
     // prologue (once per SM) while the first weight stages are in flight (config 2: 5.7 / 7.2 us per matvec against
     // 8.0 / 8.4 us for a quantizer launch followed by the matvec).
-    if (m == 1 && act_mode == SKAINET_ACT_NATIVE && w->enc == SKAINET_ENC_Q4_K && w->cols <= MATMUL_PROLOGUE_MAX_COLS && matvec_uses_ring(*w)) {
+    if (m == 1 && act_mode == SKAINET_ACT_NATIVE && w->enc == SKAINET_ENC_Q4_K && w->cols <= MATMUL_PROLOGUE_MAX_COLS && matvec_uses_ring(*w, PREP_F32)) {
         MatvecIn in; in.x = x_dev;
         const int32_t st = launch_matvec_fused(*w, in, PREP_F32, y_dev, nullptr, s);
         if (st != 1) return st;

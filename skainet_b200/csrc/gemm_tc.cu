@@ -106,9 +106,7 @@ __device__ __forceinline__ void tmem_ld16x2(uint32_t ta, uint32_t tb, float (&u)
 __device__ __forceinline__ bool wait_backoff(uint64_t* bar, uint32_t parity, int* timeout_flag) {
     for (int i = 0; i < (1 << 21); ++i) {
         if (skd::mbar_try_wait(bar, parity)) return true;
-#ifndef SK_TC_NOSLEEP
         __nanosleep(64);
-#endif
     }
     if (timeout_flag) *timeout_flag = 1;
     return false;

@@ -208,7 +208,7 @@ static int32_t prep(Model& m, const float* in, const float* gamma, int rows, int
 // prep kernel: every CTA would re-read the fp32 row and the gains, 12 bytes per element out of L2 against one for
 // the quantized row.
 static int32_t linear_normed(Model& m, const Weight& w, const float* x, const float* gamma, int rows, float* y, cudaStream_t s) {
-    if (rows == 1 && w.cols <= (matvec_uses_ring(w) ? PROLOGUE_PREP_MAX_COLS_RING : PROLOGUE_PREP_MAX_COLS)) {
+    if (rows == 1 && w.cols <= (matvec_uses_ring(w, PREP_NORM_F32) ? PROLOGUE_PREP_MAX_COLS_RING : PROLOGUE_PREP_MAX_COLS)) {
         MatvecIn in; in.x = x; in.gamma = gamma; in.eps = m.cfg.rms_eps;
         const int32_t st = launch_matvec_fused(w, in, PREP_NORM_F32, y, nullptr, s);
         if (st != 1) return st;

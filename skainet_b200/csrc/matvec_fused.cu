@@ -29,10 +29,11 @@ constexpr int MF_WARPS = 4;
 constexpr int MF_THREADS = MF_WARPS * 32;
 constexpr int MF_MAX_RW = 4;
 constexpr size_t MF_SMEM_MAX = 100 * 1024;
-#ifndef SK_RING_MIN_MB
-#define SK_RING_MIN_MB 20
-#endif
-constexpr size_t RING_MIN_BYTES = (size_t) SK_RING_MIN_MB << 20;   // measured crossover between the one-tile and the ring kernel
+// Measured crossover between the one-tile and the ring kernel. With the activation already quantized (the decoder's o
+// and down projections, everything under tensor parallelism) the two trade places shape by shape below 20 MB. When the
+// kernel itself quantizes an fp32 row, the ring kernel does so once per SM and the one-tile kernel once per CTA, and the
+// ring kernel wins down to a few MB (Q4_K 4096 x 4096: 3.3 against 5.2 us; 8192 x 1024: 4.1 against 4.6-5.7 us).
+constexpr size_t RING_MIN_BYTES = (size_t) 20 << 20, RING_MIN_BYTES_F32_ROW = (size_t) 4 << 20;
 
 // ================================================================================================
 // Q4_K (activation preparation: actprep.cuh)
@@ -280,7 +281,10 @@ static int32_t launch_q8_f(const Weight& w, const MatvecIn& in, float* y, const 
         default: SK_MF_PE(FN, 1)              \
     }
 
-bool matvec_uses_ring(const Weight& w) { return w.packed_bytes >= (int64_t) RING_MIN_BYTES && (w.enc == SKAINET_ENC_Q4_K || w.enc == SKAINET_ENC_Q8_0); }
+bool matvec_uses_ring(const Weight& w, int prep) {
+    const size_t lim = (prep != PREP_QUANTIZED && w.enc == SKAINET_ENC_Q4_K) ? RING_MIN_BYTES_F32_ROW : RING_MIN_BYTES;
+    return w.packed_bytes >= (int64_t) lim && (w.enc == SKAINET_ENC_Q4_K || w.enc == SKAINET_ENC_Q8_0);
+}
 
 int32_t launch_matvec_fused(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s,
                             const PeerOut* peer) {
@@ -288,8 +292,7 @@ int32_t launch_matvec_fused(const Weight& w, const MatvecIn& in, int prep, float
     if (w.rows <= 0) return 1;
     if (peer && (w.enc != SKAINET_ENC_Q4_K || prep != PREP_QUANTIZED)) return 1;
     // Large weights go to the persistent ring kernel.
-    const int64_t ring_min = (int64_t) RING_MIN_BYTES;
-    if (w.packed_bytes >= ring_min) {
+    if (matvec_uses_ring(w, prep)) {
         const int32_t st = launch_matvec_ring(w, in, prep, y, resid, s, peer);
         if (st != 1) return st;
     }

@@ -28,8 +28,8 @@ struct MatvecIn {
 int32_t launch_matvec_fused(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s,
                             const PeerOut* peer = nullptr);
 
-// Whether launch_matvec_fused hands this weight to the ring kernel (by size).
-bool matvec_uses_ring(const Weight& w);
+// Whether launch_matvec_fused hands this weight to the ring kernel (by size and by the form the activation arrives in).
+bool matvec_uses_ring(const Weight& w, int prep);
 
 // matvec_ring.cu: the persistent ring kernel for large weights, same activation forms and return convention.
 int32_t launch_matvec_ring(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s,
