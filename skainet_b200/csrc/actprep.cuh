@@ -87,6 +87,10 @@ __device__ __forceinline__ void q8k_prep_to_smem(const MatvecIn& in, int cols, i
                     g[2 * j] = __ldg(reinterpret_cast<const float4*>(in.gamma + (size_t) blk * 256) + lane);
                     g[2 * j + 1] = __ldg(reinterpret_cast<const float4*>(in.gamma + (size_t) blk * 256) + 32 + lane);
                 }
+                if (PREP == PREP_SWIGLU_F32) {       // the "up" half follows the "gate" half of the row
+                    g[2 * j] = __ldg(reinterpret_cast<const float4*>(in.x + cols + (size_t) blk * 256) + lane);
+                    g[2 * j + 1] = __ldg(reinterpret_cast<const float4*>(in.x + cols + (size_t) blk * 256) + 32 + lane);
+                }
             } else { v[2 * j] = make_float4(0, 0, 0, 0); v[2 * j + 1] = v[2 * j]; g[2 * j] = v[2 * j]; g[2 * j + 1] = v[2 * j]; }
         }
 #pragma unroll
@@ -98,6 +102,11 @@ __device__ __forceinline__ void q8k_prep_to_smem(const MatvecIn& in, int cols, i
                 const float ge[8] = {g[2 * j].x, g[2 * j].y, g[2 * j].z, g[2 * j].w, g[2 * j + 1].x, g[2 * j + 1].y, g[2 * j + 1].z, g[2 * j + 1].w};
 #pragma unroll
                 for (int i = 0; i < 8; ++i) e[i] = (e[i] * nscale) * ge[i];
+            }
+            if (PREP == PREP_SWIGLU_F32) {       // the arithmetic of prep_kernel<PK_SWIGLU> (stepops.cu), bit for bit
+                const float ue[8] = {g[2 * j].x, g[2 * j].y, g[2 * j].z, g[2 * j].w, g[2 * j + 1].x, g[2 * j + 1].y, g[2 * j + 1].z, g[2 * j + 1].w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) e[i] = (e[i] * (1.0f / (1.0f + expf(-e[i])))) * ue[i];
             }
             float amax = 0.0f;
 #pragma unroll

@@ -30,6 +30,10 @@ namespace sk {
 // small kernels of the step
 // ================================================================================================
 constexpr int PROLOGUE_PREP_MAX_COLS = 4096, PROLOGUE_PREP_MAX_COLS_RING = 8192;
+#ifndef SK_SWIGLU_PROLOGUE_MAX_COLS
+#define SK_SWIGLU_PROLOGUE_MAX_COLS 8192
+#endif
+constexpr int SWIGLU_PROLOGUE_MAX_COLS = SK_SWIGLU_PROLOGUE_MAX_COLS;   // widest down-projection input whose SwiGLU the ring kernel computes itself
 
 // After the merged q|k|v matvec: rotate q in place, rotate k and append it with v to the f16 cache at
 // each sequence's position. grid (rows, heads + 2*kv_heads), head_dim/2 threads. The rotation factors
@@ -263,20 +267,37 @@ static int32_t body(Model& m, int rows, bool prefill, int seq, int kv_bound, cud
     // epilogue stores its partial rows into every rank's inbox (rank 0 carries the residual), and the kernel that
     // follows only gathers, sums, normalises with gamma_next and quantizes. Otherwise: the projection into the
     // residual stream, then the group sum (fused with norm + quantizer where the peer-memory kernel applies).
-    auto row_parallel = [&](const Weight& w, const float* gamma_next, bool* prepared) -> int32_t {
+    // gate_up != nullptr (the down projection of one row): the activation is silu(gate) * up of that fp32 row; where the
+    // ring kernel can compute and quantize it in its own prologue the SwiGLU launch is skipped, else it runs first.
+    auto row_parallel = [&](const Weight& w, const float* gamma_next, bool* prepared, const float* gate_up = nullptr) -> int32_t {
         *prepared = false;
-        PeerOut po;
-        if (tp && !lin_split && gamma_next && comm_peer_out(m.comm, rows, c.d_model, &po)) {
-            MatvecIn in; in.q8 = act_q8k_layout(m.act, 1, w.cols);
-            const int32_t st = launch_matvec_fused(w, in, PREP_QUANTIZED, nullptr, rank0 ? m.x : nullptr, s, &po);
-            if (st == SKAINET_CUDA_OK) {
-                SK_TRY(comm_gather_norm_quant(m.comm, m.x, rows, c.d_model, gamma_next, c.rms_eps, act_q8k_layout(m.act, rows, c.d_model), s));
-                *prepared = true;
-                return SKAINET_CUDA_OK;
+        bool swiglu_inside = gate_up && rows == 1 && w.enc == SKAINET_ENC_Q4_K && w.cols <= SWIGLU_PROLOGUE_MAX_COLS && matvec_uses_ring(w, PREP_SWIGLU_F32);
+        for (;;) {
+            MatvecIn in;
+            int prep_mode = PREP_QUANTIZED;
+            if (swiglu_inside) { in.x = gate_up; prep_mode = PREP_SWIGLU_F32; }
+            else {
+                if (gate_up) SK_TRY(prep<PK_SWIGLU>(m, gate_up, nullptr, rows, w.cols, w.enc == SKAINET_ENC_Q8_0, s));
+                if (w.enc == SKAINET_ENC_Q8_0) in.split = act_split_layout(m.act, 1, w.cols); else in.q8 = act_q8k_layout(m.act, 1, w.cols);
             }
-            if (st != 1) return st;
+            PeerOut po;
+            int32_t st = 1;
+            if (tp && !lin_split && gamma_next && comm_peer_out(m.comm, rows, c.d_model, &po)) {
+                st = launch_matvec_fused(w, in, prep_mode, nullptr, rank0 ? m.x : nullptr, s, &po);
+                if (st == SKAINET_CUDA_OK) {
+                    SK_TRY(comm_gather_norm_quant(m.comm, m.x, rows, c.d_model, gamma_next, c.rms_eps, act_q8k_layout(m.act, rows, c.d_model), s));
+                    *prepared = true;
+                    return SKAINET_CUDA_OK;
+                }
+                if (st != 1) return st;
+            }
+            if (swiglu_inside) {
+                st = (tp && !rank0) ? launch_matvec_fused(w, in, prep_mode, m.x, nullptr, s) : launch_matvec_fused(w, in, prep_mode, m.x, m.x, s);
+                if (st == 1) { swiglu_inside = false; continue; }       // the ring kernel declined: SwiGLU as its own launch
+                if (st != SKAINET_CUDA_OK) return st;
+            } else if (tp && !rank0) SK_TRY(linear(m, w, rows, m.x, nullptr, s)); else SK_TRY(linear(m, w, rows, nullptr, m.x, s));
+            break;
         }
-        if (tp && !rank0) SK_TRY(linear(m, w, rows, m.x, nullptr, s)); else SK_TRY(linear(m, w, rows, nullptr, m.x, s));
         if (tp && gamma_next) return sum_then_norm(gamma_next, prepared);
         return tp_sum(m, m.x, (int64_t) rows * c.d_model, s);
     };
@@ -296,8 +317,7 @@ static int32_t body(Model& m, int rows, bool prefill, int seq, int kv_bound, cud
                 bool ffn_ready = false;
                 SK_TRY(row_parallel(*L.wo, L.g_ffn, &ffn_ready));
                 SK_TRY(projections(L.wgu, {L.wgate, L.wup}, ffn_ready, L.g_ffn, m.gu, 2 * m.ffn_l));
-                SK_TRY(prep<PK_SWIGLU>(m, m.gu, nullptr, rows, m.ffn_l, L.wdown->enc == SKAINET_ENC_Q8_0, s));
-                SK_TRY(row_parallel(*L.wdown, l + 1 < c.n_layers ? m.layers[l + 1].g_attn : final_gamma, &normed));
+                SK_TRY(row_parallel(*L.wdown, l + 1 < c.n_layers ? m.layers[l + 1].g_attn : final_gamma, &normed, m.gu));
                 continue;
             }
         }

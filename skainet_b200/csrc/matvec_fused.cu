@@ -290,12 +290,13 @@ int32_t launch_matvec_fused(const Weight& w, const MatvecIn& in, int prep, float
                             const PeerOut* peer) {
     int* flag = device_timeout_flag();
     if (w.rows <= 0) return 1;
-    if (peer && (w.enc != SKAINET_ENC_Q4_K || prep != PREP_QUANTIZED)) return 1;
+    if (peer && (w.enc != SKAINET_ENC_Q4_K || (prep != PREP_QUANTIZED && prep != PREP_SWIGLU_F32))) return 1;
     // Large weights go to the persistent ring kernel.
     if (matvec_uses_ring(w, prep)) {
         const int32_t st = launch_matvec_ring(w, in, prep, y, resid, s, peer);
         if (st != 1) return st;
     }
+    if (prep == PREP_SWIGLU_F32) return 1;              // only the ring kernel takes the gate | up form
     const int epi = resid ? EPI_ADD : EPI_STORE;
     if (w.enc == SKAINET_ENC_Q4_K) {
         const size_t fixed = (size_t) w.cols + w.cols / 16 + ((w.bpr * 4 + 15) & ~15) + 16 + MF_MAX_RW * 8 + 64 + 64;

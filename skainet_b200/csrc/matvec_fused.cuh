@@ -9,7 +9,8 @@ namespace sk {
 // How the activation reaches the kernel.
 enum { PREP_QUANTIZED = 0,   // already quantized in global memory (q8 for K-quants, split for Q8_0)
        PREP_F32 = 1,         // fp32 row, quantized inside the kernel
-       PREP_NORM_F32 = 2 };  // fp32 row, RMS-normalised with gamma and eps, then quantized
+       PREP_NORM_F32 = 2,    // fp32 row, RMS-normalised with gamma and eps, then quantized
+       PREP_SWIGLU_F32 = 3 };  // x = gate | up (2 * cols floats): silu(gate) * up, then quantized (ring kernel, K-quant weights)
 enum { EPI_STORE = 0, EPI_ADD = 1,     // y = W x   |   y = resid + W x
        EPI_PEER = 2 };                 // (resid +) W x stored into every tensor-parallel rank's inbox instead of y
 

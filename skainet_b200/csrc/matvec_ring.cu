@@ -361,10 +361,14 @@ static int32_t launch_q8_ring(const Weight& w, const MatvecIn& in, float* y, con
 int32_t launch_matvec_ring(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s, const PeerOut* peer) {
     int* flag = device_timeout_flag();
     if (w.rows <= 0) return 1;
-    if (peer && (w.enc != SKAINET_ENC_Q4_K || prep != PREP_QUANTIZED)) return 1;
+    if (peer && (w.enc != SKAINET_ENC_Q4_K || (prep != PREP_QUANTIZED && prep != PREP_SWIGLU_F32))) return 1;
+    if (prep == PREP_SWIGLU_F32 && w.enc != SKAINET_ENC_Q4_K) return 1;
     if (w.enc == SKAINET_ENC_Q4_K) {
-        if (peer) return launch_q4k_ring<PREP_QUANTIZED, EPI_PEER>(w, in, y, resid, flag, s, *peer);
+        if (peer) return prep == PREP_SWIGLU_F32 ? launch_q4k_ring<PREP_SWIGLU_F32, EPI_PEER>(w, in, y, resid, flag, s, *peer)
+                                                 : launch_q4k_ring<PREP_QUANTIZED, EPI_PEER>(w, in, y, resid, flag, s, *peer);
         switch (prep * 2 + (resid ? EPI_ADD : EPI_STORE)) {
+            case PREP_SWIGLU_F32 * 2 + EPI_STORE: return launch_q4k_ring<PREP_SWIGLU_F32, EPI_STORE>(w, in, y, resid, flag, s);
+            case PREP_SWIGLU_F32 * 2 + EPI_ADD:   return launch_q4k_ring<PREP_SWIGLU_F32, EPI_ADD>(w, in, y, resid, flag, s);
             case PREP_QUANTIZED * 2 + EPI_STORE: return launch_q4k_ring<PREP_QUANTIZED, EPI_STORE>(w, in, y, resid, flag, s);
             case PREP_QUANTIZED * 2 + EPI_ADD:   return launch_q4k_ring<PREP_QUANTIZED, EPI_ADD>(w, in, y, resid, flag, s);
             case PREP_F32 * 2 + EPI_STORE:       return launch_q4k_ring<PREP_F32, EPI_STORE>(w, in, y, resid, flag, s);

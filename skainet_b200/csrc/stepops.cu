@@ -4,6 +4,7 @@
 // CPU decompositions in skainet-compile/skainet-compile-dag/src/commonMain/kotlin/sk/ainet/lang/graph/exec/LLMFusedOpHandlers.kt:27-68,86-196).
 #include "stepops.cuh"
 #include "tma.cuh"
+#include "matvec_fused.cuh"
 
 namespace sk {
 
@@ -269,9 +270,16 @@ int32_t skainet_cuda_fused_swiglu_ffn_dev(skainet_weight_t w_gate_up, skainet_we
     SK_TRY(scratch_get(s, SCRATCH_ACT, need, &act));
     SK_TRY(launch_prep(gamma_dev ? PK_NORM : PK_QUANT, x_dev, gamma_dev, eps, m, wgu->cols, wgu->enc == SKAINET_ENC_Q8_0, act, s));
     SK_TRY(launch_linear_q(*wgu, act, m, gu, nullptr, nullptr, s));
+    if (resid_dev && resid_dev != out_dev) SK_CUDA(cudaMemcpyAsync(out_dev, resid_dev, sizeof(float) * (size_t) m * wd->rows, cudaMemcpyDeviceToDevice, s));
+    // One row into a ring-sized Q4_K down projection of at most 8192 inputs: the ring kernel computes silu(gate) * up and
+    // quantizes it in its own prologue, as the decoder's step does.
+    if (m == 1 && wd->enc == SKAINET_ENC_Q4_K && F <= 8192 && matvec_uses_ring(*wd, PREP_SWIGLU_F32)) {
+        MatvecIn in; in.x = gu;
+        const int32_t st = launch_matvec_fused(*wd, in, PREP_SWIGLU_F32, out_dev, resid_dev ? out_dev : nullptr, s);
+        if (st != 1) return st;
+    }
     SK_TRY(launch_prep(PK_SWIGLU, gu, nullptr, 0.0f, m, F, wd->enc == SKAINET_ENC_Q8_0, act, s));       // silu(gate) * up, quantized for down
     if (resid_dev == nullptr) return launch_linear_q(*wd, act, m, out_dev, nullptr, nullptr, s);
-    if (resid_dev != out_dev) SK_CUDA(cudaMemcpyAsync(out_dev, resid_dev, sizeof(float) * (size_t) m * wd->rows, cudaMemcpyDeviceToDevice, s));
     return launch_linear_q(*wd, act, m, nullptr, out_dev, spare, s);
 }
 
