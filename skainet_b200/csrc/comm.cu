@@ -114,6 +114,7 @@ __device__ __forceinline__ uint4 ld_volatile_u4(const uint32_t* p) {
     asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
     return r;
 }
+__device__ __forceinline__ bool p2p_pending(const uint4& r) { return r.x == P2P_SENTINEL || r.y == P2P_SENTINEL || r.z == P2P_SENTINEL || r.w == P2P_SENTINEL; }
 // Waits (bounded) until the four words at p have all arrived, returns them and puts the sentinel back.
 __device__ __forceinline__ float4 p2p_take(uint32_t* p, int* timeout_flag) {
     uint4 r = ld_volatile_u4(p);
@@ -143,14 +144,33 @@ allreduce_words_kernel(P2PView v, float* __restrict__ buf, int n, int* __restric
     const int seq = s_seq, par = seq & 1;
     if (live) {
         const float4 own = *reinterpret_cast<const float4*>(buf + i);
-        const uint4 w = p2p_words(own);
+        const uint4 mine = p2p_words(own);
         for (int p = 0; p < world; ++p)
-            if (p != rank) *reinterpret_cast<uint4*>(v.chan[p] + ((size_t) par * world + rank) * P2P_MAX_ELEMS + i) = w;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int p = 0; p < world; ++p) {
-            const float4 x = p == rank ? own : p2p_take(v.chan[rank] + ((size_t) par * world + p) * P2P_MAX_ELEMS + i, timeout_flag);
-            acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+            if (p != rank) *reinterpret_cast<uint4*>(v.chan[p] + ((size_t) par * world + rank) * P2P_MAX_ELEMS + i) = mine;
+        uint32_t* src0 = v.chan[rank] + (size_t) par * world * P2P_MAX_ELEMS + i;
+        uint4 w[P2P_MAX_WORLD];
+#pragma unroll
+        for (int p = 0; p < P2P_MAX_WORLD; ++p)
+            if (p < world && p != rank) w[p] = ld_volatile_u4(src0 + (size_t) p * P2P_MAX_ELEMS);
+        for (int spins = 0; ; ++spins) {
+            bool missing = false;
+#pragma unroll
+            for (int p = 0; p < P2P_MAX_WORLD; ++p)
+                if (p < world && p != rank && p2p_pending(w[p])) { w[p] = ld_volatile_u4(src0 + (size_t) p * P2P_MAX_ELEMS); missing = true; }
+            if (!missing) break;
+            if (spins >= P2P_SPIN_LIMIT) { if (timeout_flag) atomicExch(timeout_flag, 2); break; }
         }
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int p = 0; p < P2P_MAX_WORLD; ++p)          // rank order: every rank gets the same bits
+            if (p < world) {
+                float4 x = own;
+                if (p != rank) {
+                    *reinterpret_cast<uint4*>(src0 + (size_t) p * P2P_MAX_ELEMS) = make_uint4(P2P_SENTINEL, P2P_SENTINEL, P2P_SENTINEL, P2P_SENTINEL);
+                    x = make_float4(__uint_as_float(w[p].x), __uint_as_float(w[p].y), __uint_as_float(w[p].z), __uint_as_float(w[p].w));
+                }
+                acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+            }
         *reinterpret_cast<float4*>(buf + i) = acc;
     }
     if (threadIdx.x == 0) *seq_slot = seq;
@@ -189,12 +209,35 @@ gather_sum_norm_quant_kernel(P2PView v, float* __restrict__ x, int n, const floa
             *reinterpret_cast<uint4*>(dst) = w0; *reinterpret_cast<uint4*>(dst + 4) = w1;
         }
     }
-    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int p = 0; p < world; ++p) {                  // rank order: every rank gets the same bits
-        uint32_t* src = v.chan[rank] + ((size_t) par * world + p) * P2P_MAX_ELEMS + i;
-        const float4 u0 = p2p_take(src, timeout_flag), u1 = p2p_take(src + 4, timeout_flag);
-        a[0] += u0.x; a[1] += u0.y; a[2] += u0.z; a[3] += u0.w; a[4] += u1.x; a[5] += u1.y; a[6] += u1.z; a[7] += u1.w;
+    // gamma does not depend on the peers: fetch it before the wait
+    const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + col)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + col + 4));
+    // every slot's words are requested at once; only the ones that have not arrived are asked for again
+    uint32_t* src0 = v.chan[rank] + (size_t) par * world * P2P_MAX_ELEMS + i;
+    uint4 w[2 * P2P_MAX_WORLD];
+#pragma unroll
+    for (int p = 0; p < P2P_MAX_WORLD; ++p)
+        if (p < world) { w[2 * p] = ld_volatile_u4(src0 + (size_t) p * P2P_MAX_ELEMS); w[2 * p + 1] = ld_volatile_u4(src0 + (size_t) p * P2P_MAX_ELEMS + 4); }
+    for (int spins = 0; ; ++spins) {
+        bool missing = false;
+#pragma unroll
+        for (int p = 0; p < P2P_MAX_WORLD; ++p)
+            if (p < world) {
+                if (p2p_pending(w[2 * p])) { w[2 * p] = ld_volatile_u4(src0 + (size_t) p * P2P_MAX_ELEMS); missing = true; }
+                if (p2p_pending(w[2 * p + 1])) { w[2 * p + 1] = ld_volatile_u4(src0 + (size_t) p * P2P_MAX_ELEMS + 4); missing = true; }
+            }
+        if (!missing) break;
+        if (spins >= P2P_SPIN_LIMIT) { if (timeout_flag) atomicExch(timeout_flag, 2); break; }
     }
+    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const uint4 sent = make_uint4(P2P_SENTINEL, P2P_SENTINEL, P2P_SENTINEL, P2P_SENTINEL);
+#pragma unroll
+    for (int p = 0; p < P2P_MAX_WORLD; ++p)              // rank order: every rank gets the same bits
+        if (p < world) {
+            *reinterpret_cast<uint4*>(src0 + (size_t) p * P2P_MAX_ELEMS) = sent;          // the inbox cleans itself
+            *reinterpret_cast<uint4*>(src0 + (size_t) p * P2P_MAX_ELEMS + 4) = sent;
+            a[0] += __uint_as_float(w[2 * p].x); a[1] += __uint_as_float(w[2 * p].y); a[2] += __uint_as_float(w[2 * p].z); a[3] += __uint_as_float(w[2 * p].w);
+            a[4] += __uint_as_float(w[2 * p + 1].x); a[5] += __uint_as_float(w[2 * p + 1].y); a[6] += __uint_as_float(w[2 * p + 1].z); a[7] += __uint_as_float(w[2 * p + 1].w);
+        }
     *reinterpret_cast<float4*>(xr) = make_float4(a[0], a[1], a[2], a[3]);
     *reinterpret_cast<float4*>(xr + 4) = make_float4(a[4], a[5], a[6], a[7]);
     // sum of squares of the row: warp, CTA, cluster (fixed orders)
@@ -209,22 +252,23 @@ gather_sum_norm_quant_kernel(P2PView v, float* __restrict__ x, int n, const floa
 #pragma unroll
         for (int k = 0; k < 8; ++k) t += s_red[k];
         s_part = t;
-        // the last CTA of the launch to get here advances the round (every CTA has read it by then)
-        __threadfence();
-        if (atomicAdd(ticket, 1) == (int) (gridDim.x * gridDim.y) - 1) { *ticket = 0; *round_ctr = *round_ctr + 1; }
     }
     cluster.sync();
     float total = 0.0f;
     for (int r = 0; r < cs; ++r) total += *cluster.map_shared_rank(&s_part, r);
     cluster.sync();                                    // nobody leaves while its shared memory may still be read
     const float nscale = 1.0f / sqrtf(total * (1.0f / (float) n) + eps);
-    const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + col)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + col + 4));
     const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
 #pragma unroll
     for (int k = 0; k < 8; ++k) a[k] = (a[k] * nscale) * g[k];
     const int blk = col >> 8;
     skd::quant_q8k_regs(a, act.q + (size_t) row * n + (size_t) blk * 256, act.d + (size_t) row * (n >> 8) + blk,
                         act.bsums + (size_t) row * (n >> 5) + (size_t) blk * 8, lane);
+    // the last CTA of the launch to get here advances the round (every CTA has read it by then)
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(ticket, 1) == (int) (gridDim.x * gridDim.y) - 1) { *ticket = 0; *round_ctr = *round_ctr + 1; }
+    }
 }
 
 struct Comm {

@@ -381,6 +381,37 @@ argmax_pairs_kernel(const float* __restrict__ logits, int cols, int idx_offset, 
         vals[blockIdx.x] = best; idxs[blockIdx.x] = (bi == 0x7fffffff ? 0 : bi) + idx_offset;
     }
 }
+// Arg max of one chunk of a row's logits -> out[chunk][row] as a (value, index) record: with a vocabulary of 128256 one
+// CTA per row would scan for tens of microseconds at the end of every step; the chunks of all rows run side by side and
+// finish_step_kernel picks among them (lowest index on ties, as the reference's arg max does).
+constexpr int ARGMAX_CHUNKS = 32;
+__global__ void __launch_bounds__(256)
+argmax_chunks_kernel(const float* __restrict__ logits, int cols, int chunk_cols, float2* __restrict__ out, int batch) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    skd::pdl_launch_dependents();
+    skd::pdl_wait();
+    const int row = blockIdx.x, c0 = blockIdx.y * chunk_cols, c1 = min(cols, c0 + chunk_cols);
+    const float* r = logits + (size_t) row * cols;
+    float best = -INFINITY; int bi = 0x7fffffff;
+    for (int i = c0 + threadIdx.x; i < c1; i += 256) {
+        const float v = r[i];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(~0u, best, o); const int oi = __shfl_xor_sync(~0u, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+        out[(size_t) blockIdx.y * batch + row] = make_float2(best, __int_as_float(bi));
+    }
+}
 // pairs[world][batch] as (float, int) interleaved 8-byte records -> token per row, then the step's bookkeeping
 __global__ void finish_step_kernel(const float2* __restrict__ pairs, int world, int batch, int32_t* __restrict__ cur_token,
                                    int32_t* __restrict__ pos, int32_t* __restrict__ log, const int32_t* __restrict__ log_cursor) {
@@ -394,6 +425,7 @@ __global__ void finish_step_kernel(const float2* __restrict__ pairs, int world, 
         const int idx = __float_as_int(p.y);
         if (p.x > best || (p.x == best && idx < bi)) { best = p.x; bi = idx; }
     }
+    if (bi == 0x7fffffff) bi = 0;               // no finite logit in the row
     cur_token[b] = bi; pos[b] += 1;
     if (log) log[(size_t) log_cursor[0] * batch + b] = bi;
 }
@@ -421,6 +453,11 @@ static int32_t enqueue_step(Model& m, int batch, int kv_bound, cudaStream_t s) {
         SK_CUDA(launch_pdl(pack_pairs_kernel, dim3((batch + 255) / 256), dim3(256), 0, s, (const float*) vals, (const int32_t*) idxs, mine, batch));
         SK_TRY(comm_all_gather(m.comm, mine, all, (int64_t) batch * 8, s));
         SK_CUDA(launch_pdl(finish_step_kernel, dim3((batch + 255) / 256), dim3(256), 0, s, (const float2*) all, c.tp_world, batch, m.cur_token, m.pos, m.log, (const int32_t*) m.log_cursor));
+    } else if (c.vocab >= 8192 && (size_t) 2 * ARGMAX_CHUNKS * batch <= (size_t) m.max_rows * std::max(c.d_model, 64)) {
+        float2* pairs = (float2*) m.tmp;          // free again once the head has run
+        const int chunk_cols = (c.vocab + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
+        SK_CUDA(launch_pdl(argmax_chunks_kernel, dim3(batch, ARGMAX_CHUNKS), dim3(256), 0, s, (const float*) m.logits, c.vocab, chunk_cols, pairs, batch));
+        SK_CUDA(launch_pdl(finish_step_kernel, dim3((batch + 255) / 256), dim3(256), 0, s, (const float2*) pairs, ARGMAX_CHUNKS, batch, m.cur_token, m.pos, m.log, (const int32_t*) m.log_cursor));
     } else {
         SK_CUDA(launch_pdl(argmax_advance_kernel, dim3(batch), dim3(1024), 0, s, (const float*) m.logits, c.vocab, m.cur_token, m.pos, m.log, m.log_cursor, batch));
     }
