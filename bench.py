@@ -26,6 +26,8 @@ Prints ONE JSON line (rank 0). Workloads (all inputs synthetic and seeded):
       in a CUDA graph: the peer-memory sum, the store + gather + sum + RMSNorm + quantize kernel, and ncclAllReduce of the
       same row; metric = microseconds per exchange (lower is better). The N > 1 decode lines carry the same three numbers
       under `tp_exchange`.
+  kv_turboquant — the TurboQuant KV store (4-bit keys and values, 8 heads x 128, 32 layers): one decode step of attention over
+      --context positions per layer (blocks decoded to fp32, then fp32 attention); metric = microseconds per call (lower is better).
 
 `value` is timed on the device with everything resident in HBM (decode: one CUDA-graph replay per
 step, tokens fed back on the device). `e2e` is the same metric through the C ABI with HOST buffers
@@ -812,6 +814,75 @@ def tp_parity_check(torch, dist, m, cfg, model_name: str, ctx: int, batch: int, 
     return out
 
 
+def run_kv_turboquant(args) -> None:
+    """kv_turboquant: the TurboQuant KV store (4-bit keys and values, 8 heads x 128) behind one decode step of attention over
+    --context positions: decode of the window's blocks to fp32 + fp32 attention, per layer of a 32-layer store (the layers'
+    blocks together exceed L2). Also times the append (encode) of one token."""
+    import torch
+    from skainet_b200 import _lib as L, device
+    from skainet_b200.kvstore import DeviceKvCacheStore, TurboQuantConfig
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local); device.set_device(local)
+    layers, heads, d, ctx = 32, 8, 128, args.context
+    st = DeviceKvCacheStore(layers, heads, d, ctx + 8, keyConfig=TurboQuantConfig.polarOnly(4), valueConfig=TurboQuantConfig.polarOnly(4))
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    kv = torch.randn(2, heads * d, device="cuda", generator=gen)
+    stream = torch.cuda.Stream(); sp = stream.cuda_stream
+    with torch.cuda.stream(stream):
+        for _ in range(ctx):
+            for l in range(layers):
+                st.appendTokenDevice(l, kv[0].data_ptr(), kv[1].data_ptr(), sp)
+        stream.synchronize()
+        q = torch.randn(heads * d, device="cuda", generator=gen); out = torch.empty(heads * d, device="cuda")
+
+        def sweep():
+            for l in range(layers):
+                st.decodeStep(l, q.data_ptr(), out.data_ptr(), heads, 0, ctx, 0.0, sp)
+        sweep(); stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            sweep()
+        warm = max(3, args.warmup)
+        for _ in range(warm):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        clk = ClockSampler(local); clk.start()
+        stream.synchronize(); e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream); stream.synchronize()
+        clocks = clk.stop()
+        ms_step = e0.elapsed_time(e1) / args.steps
+        # append (encode) of one more token into every layer
+        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2.record(stream)
+        for l in range(layers):
+            st.appendTokenDevice(l, kv[0].data_ptr(), kv[1].data_ptr(), sp)
+        e3.record(stream); stream.synchronize()
+        append_us = e2.elapsed_time(e3) * 1e3 / layers
+    block = 64 + 16 + 4                               # 4-bit codes + four fp32 scales + the seed word the reference counts
+    call_bytes = 2 * heads * ctx * (64 + 16)          # compressed bytes one call must read
+    window_bytes = 2 * heads * ctx * d * 4            # the fp32 window written by the decode and read by the attention
+    peak, peak_kind = load_peaks()
+    us = ms_step * 1e3 / layers
+    achieved = (call_bytes + 2 * window_bytes) / (us * 1e-6) / 1e9
+    status = L.lib().skainet_cuda_device_status()
+    if status != 0:
+        raise SystemExit(f"device status {status}: {L.last_error()}")
+    line = {"metric": "kv_turboquant_attn_us", "value": us, "unit": "us", "n_gpus": 1, "steps": args.steps, "warmup": warm, "ms_per_step": ms_step,
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "4-bit codes + fp32 scales -> fp32", "data": "synthetic",
+            "config": {"workload": "kv_turboquant", "layers": layers, "heads": heads, "head_dim": d, "context": ctx, "key_bits": 4, "value_bits": 4,
+                       "block_bytes": block, "l2": f"{layers} layers x {call_bytes / 1e6:.1f} MB of blocks rotate"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "tq_decode_kernel", "note": "bytes = compressed blocks read + the fp32 window written once and read once; a first "
+                                                               "version: the blocks are decoded to fp32 rows and attended by the fp32 kernel",
+                         "compressed_bytes_per_call": call_bytes, "fp32_window_bytes": window_bytes},
+            "append_us_per_layer": append_us, "gpu_launches": 3 * layers * args.steps, "clocks": clocks,
+            "e2e": {"value": None, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0, "note": "device-resident entry points only"}}
+    print(json.dumps(line), flush=True)
+    st.free()
+
+
 def tp_exchange_times(m, torch, dist, rounds: int = 64, reps: int = 20) -> dict:
     """The group exchanges of a decode step timed on their own (every rank calls; the max over ranks is reported):
     device microseconds per exchange of one [d_model] fp32 row, `rounds` launches back to back in one CUDA graph."""
@@ -1018,7 +1089,7 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="decode_70b", choices=sorted(MATVEC_WORKLOADS) + sorted(DECODE_WORKLOADS) + sorted(ATTN_WORKLOADS) + sorted(GEMM_WORKLOADS) + sorted(REQUEST_WORKLOADS) + ["tp_collective"])
+    ap.add_argument("--workload", default="decode_70b", choices=sorted(MATVEC_WORKLOADS) + sorted(DECODE_WORKLOADS) + sorted(ATTN_WORKLOADS) + sorted(GEMM_WORKLOADS) + sorted(REQUEST_WORKLOADS) + ["tp_collective", "kv_turboquant"])
     ap.add_argument("--context", type=int, default=4096, help="keys per sequence (attn_decode workload)")
     ap.add_argument("--batch", type=int, default=1, help="sequences decoded together (decode workloads)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -1037,6 +1108,8 @@ def main() -> None:
         run_request(args)
     elif args.workload == "tp_collective":
         run_collective(args)
+    elif args.workload == "kv_turboquant":
+        run_kv_turboquant(args)
     else:
         run_decode(args)
 

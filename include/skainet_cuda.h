@@ -284,6 +284,26 @@ SKAINET_CUDA_API int32_t skainet_cuda_f32_to_f16_dev(const float* in, uint16_t* 
  * The sequence length advances when the last layer has been appended. head_dim 64 or 128. */
 SKAINET_CUDA_API int32_t skainet_cuda_kv_create(int32_t n_layers, int32_t n_heads, int32_t head_dim, int32_t max_seq,
     int32_t sliding_window, skainet_kv_t* out);
+/* The same store holding TurboQuant blocks instead of binary16 rows: the device counterpart of TurboQuantKvCacheStore
+ * (skainet-lang/skainet-lang-core/src/commonMain/kotlin/sk/ainet/lang/tensor/storage/TurboQuantKvCacheStore.kt:62-199), one block per
+ * (layer, position, head) with the rotation seed RandomRotation.seedFor(layer, head, position) for keys and that seed xor 0x5A5A5A5A
+ * for values. key_bits / value_bits in {2,3,4,8}; *_residual_bits 0 = rotation + scalar quantizer only (PolarOnly), 1..4 = with the
+ * residual stage (PolarPlusQjl). Dense only (a full cache refuses the append); head_dim in {32,64,128,256}. Encoded bytes, scales and
+ * the values a read returns are bit-identical to the reference's. kv_info reports ring = 2 and, as physical bytes, what the
+ * reference's memoryReport counts (the blocks of the positions held); beside every block the device also keeps the rotation's sign
+ * sequence (head_dim / 8 bytes), so that a read does not re-run the sequential generator. kv_attn_decode_dev decodes the window's blocks
+ * and attends them: through binary16 rows and the split-K kernel for head_dim 64 / 128 with 1, 2, 4 or 8 query heads per cache head, in
+ * fp32 otherwise; the window must end at or before currentSeqLen. */
+SKAINET_CUDA_API int32_t skainet_cuda_kv_create_turboquant(int32_t n_layers, int32_t n_heads, int32_t head_dim, int32_t max_seq,
+    int32_t key_bits, int32_t key_residual_bits, int32_t value_bits, int32_t value_residual_bits, skainet_kv_t* out);
+/* TurboQuantCodec.encode / decode for one vector of n in {32,64,128,256} floats with an explicit seed
+ * (skainet-lang/skainet-lang-core/src/commonMain/kotlin/sk/ainet/lang/tensor/ops/turboquant/TurboQuantCodec.kt:33-85); HOST pointers.
+ * codes_out: packedSize(n, bits) bytes (BitPacker.kt:46-54); scales_out: n / 32 floats; residual_out / residual_scale_out only when
+ * residual_bits > 0 (packedSize(n, residual_bits) bytes, one float). The same bytes the reference's golden test digests. */
+SKAINET_CUDA_API int32_t skainet_cuda_turboquant_encode(const float* input, int32_t n, int32_t bits, int32_t residual_bits, int32_t seed,
+    uint8_t* codes_out, float* scales_out, uint8_t* residual_out, float* residual_scale_out);
+SKAINET_CUDA_API int32_t skainet_cuda_turboquant_decode(const uint8_t* codes, const float* scales, const uint8_t* residual, float residual_scale,
+    int32_t n, int32_t bits, int32_t residual_bits, int32_t seed, float* output);
 SKAINET_CUDA_API int32_t skainet_cuda_kv_free(skainet_kv_t kv);
 /* appendToken(layer, key, value): key / value are [heads, head_dim] fp32; host pointers, or device pointers with a stream.
  * A full non-ring cache -> SKAINET_CUDA_ERR_INVALID ("KV cache is full", IllegalStateException in the reference). */

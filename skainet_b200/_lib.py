@@ -81,6 +81,9 @@ SIGNATURES = {
     "skainet_cuda_fused_qkv_proj_dev": [i64, i32, i32, i32, vp, vp, f32, i32, vp, vp, vp, vp],
     "skainet_cuda_fused_swiglu_ffn_dev": [i64, i64, vp, vp, f32, i32, vp, vp, vp],
     "skainet_cuda_kv_create": [i32, i32, i32, i32, i32, i64p],
+    "skainet_cuda_kv_create_turboquant": [i32, i32, i32, i32, i32, i32, i32, i32, i64p],
+    "skainet_cuda_turboquant_encode": [f32p, i32, i32, i32, i32, u8p, f32p, u8p, f32p],
+    "skainet_cuda_turboquant_decode": [u8p, f32p, u8p, C.c_float, i32, i32, i32, i32, f32p],
     "skainet_cuda_kv_free": [i64],
     "skainet_cuda_kv_append": [i64, i32, f32p, f32p],
     "skainet_cuda_kv_append_dev": [i64, i32, vp, vp, vp],

@@ -235,6 +235,7 @@ void scratch_release(cudaStream_t stream) {
 
 // Host twins share the default stream's staging buffers: one twin call at a time per process.
 static std::mutex g_twin_mu;
+std::mutex& twin_mutex() { return g_twin_mu; }
 #define SK_TWIN_LOCK() std::lock_guard<std::mutex> _twin_lk(::sk::g_twin_mu)
 
 // A host twin's device staging: upload `n` bytes into a scratch slot of the default stream.

@@ -1,6 +1,7 @@
 // Shared host/device helpers of libskainet_cuda: status + error plumbing, the resident weight
 // record, per-stream scratch, and small device utilities used by every kernel file.
 #pragma once
+#include <mutex>
 
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
@@ -78,6 +79,8 @@ Weight* weight_from_handle(skainet_weight_t h);   // nullptr (+ error set) when 
 int32_t scratch_get(cudaStream_t stream, int slot, size_t nbytes, void** out);
 size_t scratch_capacity(cudaStream_t stream, int slot);   // bytes the slot holds now (0 if never used)
 void scratch_release(cudaStream_t stream);                // frees every slot of a stream about to be destroyed
+// Entry points that take HOST pointers stage through the default stream's scratch slots: one such call at a time per process.
+std::mutex& twin_mutex();
 enum { SCRATCH_ACT = 0, SCRATCH_ATTN = 1, SCRATCH_TWIN_A = 2, SCRATCH_TWIN_B = 3, SCRATCH_TWIN_C = 4,
        SCRATCH_TWIN_D = 5, SCRATCH_TWIN_E = 6, SCRATCH_TWIN_F = 7, SCRATCH_FUSED = 8, SCRATCH_FUSED2 = 9, SCRATCH_GEMM = 10,
        SCRATCH_FFN = 11, SCRATCH_SLOTS = 12 };

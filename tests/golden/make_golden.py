@@ -24,7 +24,7 @@ sys.path.insert(0, ROOT)
 from oracle import ref as R  # noqa: E402
 
 KEYS = ["decode/Q4_K", "decode/Q8_0", "decode/Q5_K", "decode/Q6_K", "scalar-matmul/Q4_K", "scalar-matmul/Q8_0",
-        "dispatch-bridge/Q4_K", "dispatch-bridge/Q8_0"]
+        "dispatch-bridge/Q4_K", "dispatch-bridge/Q8_0"] + [f"turboquant/{t}/{k}" for t in ("polar4", "polar3", "polar4-qjl1") for k in ("codes", "scales", "decoded")]
 
 
 def digests(ref_root: str) -> dict:
