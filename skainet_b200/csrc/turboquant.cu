@@ -9,8 +9,9 @@
 // Every fp32 operation is written with the round-to-nearest intrinsics so that none is fused, and in the reference's
 // order: encoded bytes, scales and decoded values are bit-identical to the reference's (its golden digests,
 // Goldens.kt:62-71, are reproduced through this file by tests/test_kv_turboquant.py).
-// One CTA of head_dim threads per vector; head_dim a power of two from 32 to 256 (the transform then covers the whole
-// vector; the reference's handling of other sizes is not built).
+// Encode: one CTA of head_dim threads per vector (a token's vectors are few). Decode: one warp per vector, transform by lane
+// shuffles. head_dim a power of two from 32 to 256 (the transform then covers the whole vector; the reference's handling of
+// other sizes is not built).
 #include "common.cuh"
 #include "turboquant.cuh"
 
@@ -168,39 +169,104 @@ tq_encode_kernel(const float* __restrict__ rows, TqPlane pl, int layer, int pos,
     }
 }
 
-// grid (n positions, heads), block D. out [heads][n][D], fp32 (exactly the reference's decode) or rounded to binary16.
-template <typename OUT>
-__global__ void __launch_bounds__(TQ_MAX_D)
-tq_decode_kernel(TqPlane pl, int layer, int start_pos, int n, int heads, int D, int max_seq, int32_t seed_xor, int fixed_seed, OUT* __restrict__ out) {
-    __shared__ float x[TQ_MAX_D];
-    __shared__ uint32_t sg[TQ_MAX_D / 32], rsg[TQ_MAX_D / 32];
-    const int t = threadIdx.x, p = blockIdx.x, head = blockIdx.y, lane = t & 31;
-    const int pos = start_pos + p;
+// One WARP per vector, EPL = head_dim / 32 elements per lane (element e = 32 i + lane): the butterflies between elements
+// less than 32 apart are lane shuffles, the others stay inside a lane, so a decode has no barrier at all. The pairs and the
+// order of the stages are the reference's, each result one fp32 add or subtract: bit-identical to the shared-memory form.
+// Vectors are numbered position-major: vector = p * heads + head of the window [start_pos, start_pos + n).
+// out [heads][n][D], fp32 (exactly the reference's decode) or rounded to binary16.
+template <typename OUT, int EPL>
+__global__ void __launch_bounds__(256)
+tq_decode_kernel(TqPlane pl, int layer, int start_pos, int n, int heads, int32_t seed_xor, int fixed_seed, int max_seq, OUT* __restrict__ out) {
+    constexpr int D = EPL * 32;
+    const int lane = threadIdx.x & 31;
+    const int64_t widx = (int64_t) blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (widx >= (int64_t) n * heads) return;
+    const int p = (int) (widx / heads), head = (int) (widx % heads), pos = start_pos + p;
     const int32_t seed = fixed_seed ? seed_xor : (tq_seed_for(layer, head, pos) ^ seed_xor);
     const size_t vec = ((size_t) layer * max_seq + pos) * heads + head;
-    const int cps = tq_packed_size(D, pl.bits), ng = D / 32;
-    if (pl.signs) { if (t < ng) sg[t] = pl.signs[vec * ng + t]; }
-    else if (t == 0) tq_sign_words(seed, D, sg);
-    if (pl.rbits == 1) {
-        if (pl.rsigns) { if (t < ng) rsg[t] = pl.rsigns[vec * ng + t]; }
-        else if (t == (D > 32 ? 32 : 0)) tq_sign_words((int32_t) ((uint32_t) seed + 1u), D, rsg);
+    const int cps = tq_packed_size(D, pl.bits);
+    uint32_t sg[EPL], rsg[EPL];
+    if (pl.signs) {
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) sg[i] = pl.signs[vec * EPL + i];
+    } else {                                   // one-vector codec calls: lane 0 runs the generator
+        uint32_t wds[EPL];
+        if (lane == 0) tq_sign_words(seed, D, wds);
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) sg[i] = __shfl_sync(0xffffffffu, wds[i], 0);
     }
-    float v = __fmul_rn((float) tq_unpack(pl.codes + vec * cps, cps, pl.bits, t), pl.scales[vec * ng + (t >> 5)]);
-    __syncthreads();
+    if (pl.rbits == 1) {
+        if (pl.rsigns) {
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) rsg[i] = pl.rsigns[vec * EPL + i];
+        } else {
+            uint32_t wds[EPL];
+            if (lane == 0) tq_sign_words((int32_t) ((uint32_t) seed + 1u), D, wds);
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) rsg[i] = __shfl_sync(0xffffffffu, wds[i], 0);
+        }
+    }
+    float v[EPL];
+    const uint8_t* codes = pl.codes + vec * cps;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) v[i] = __fmul_rn((float) tq_unpack(codes, cps, pl.bits, 32 * i + lane), pl.scales[vec * EPL + i]);
     if (pl.rbits == 1) {
         const float rs = pl.rscale[vec];
-        const int bit = (pl.resid[vec * (size_t) tq_packed_size(D, 1) + (t >> 3)] >> (t & 7)) & 1;
-        const float sgn = ((rsg[t >> 5] >> lane) & 1) ? 1.0f : -1.0f;
-        v = __fadd_rn(v, __fmul_rn(bit ? rs : -rs, sgn));
+        const uint8_t* rb = pl.resid + vec * (size_t) (D / 8);
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            const int e = 32 * i + lane, bit = (rb[e >> 3] >> (e & 7)) & 1;
+            const float sgn = ((rsg[i] >> lane) & 1) ? 1.0f : -1.0f;
+            v[i] = __fadd_rn(v[i], __fmul_rn(bit ? rs : -rs, sgn));
+        }
     } else if (pl.rbits > 1) {
         const int rps = tq_packed_size(D, pl.rbits);
-        v = __fadd_rn(v, __fmul_rn((float) tq_unpack(pl.resid + vec * rps, rps, pl.rbits, t), pl.rscale[vec]));
+        const float rs = pl.rscale[vec];
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) v[i] = __fadd_rn(v[i], __fmul_rn((float) tq_unpack(pl.resid + vec * rps, rps, pl.rbits, 32 * i + lane), rs));
     }
-    x[t] = v;
-    tq_wht(x, D, t);
-    v = x[t];
-    if ((sg[t >> 5] >> lane) & 1) v = -v;
-    tq_store(out + ((size_t) head * n + p) * D + t, v);
+    // Walsh-Hadamard: stages h = 1 .. 16 across lanes, h = 32 .. D/2 inside the lane
+#pragma unroll
+    for (int h = 1; h < 32; h <<= 1) {
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            const float o = __shfl_xor_sync(0xffffffffu, v[i], h);
+            v[i] = (lane & h) ? __fsub_rn(o, v[i]) : __fadd_rn(v[i], o);
+        }
+    }
+#pragma unroll
+    for (int hi = 1; hi < EPL; hi <<= 1) {
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            if ((i & hi) == 0) {
+                const float a = v[i], bb = v[i + hi];
+                v[i] = __fadd_rn(a, bb); v[i + hi] = __fsub_rn(a, bb);
+            }
+        }
+    }
+    const float norm = __fdiv_rn(1.0f, __fsqrt_rn((float) D));
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+        float r = __fmul_rn(v[i], norm);
+        if ((sg[i] >> lane) & 1) r = -r;
+        tq_store(out + ((size_t) head * n + p) * D + 32 * i + lane, r);
+    }
+}
+
+template <typename OUT>
+int32_t tq_decode_dispatch(const TqPlane& pl, int layer, int start_pos, int n, int heads, int D, int max_seq, int32_t seed_xor, bool fixed_seed, OUT* out, cudaStream_t s) {
+    if (n <= 0) return SKAINET_CUDA_OK;
+    const unsigned grid = (unsigned) (((int64_t) n * heads + 7) / 8);
+    const int fs = fixed_seed ? 1 : 0;
+    switch (D) {
+        case 32: tq_decode_kernel<OUT, 1><<<grid, 256, 0, s>>>(pl, layer, start_pos, n, heads, seed_xor, fs, max_seq, out); break;
+        case 64: tq_decode_kernel<OUT, 2><<<grid, 256, 0, s>>>(pl, layer, start_pos, n, heads, seed_xor, fs, max_seq, out); break;
+        case 128: tq_decode_kernel<OUT, 4><<<grid, 256, 0, s>>>(pl, layer, start_pos, n, heads, seed_xor, fs, max_seq, out); break;
+        case 256: tq_decode_kernel<OUT, 8><<<grid, 256, 0, s>>>(pl, layer, start_pos, n, heads, seed_xor, fs, max_seq, out); break;
+        default: set_error("turboquant decode: head_dim %d not in {32,64,128,256}", D); return SKAINET_CUDA_ERR_INVALID;
+    }
+    SK_CUDA(cudaGetLastError());
+    return SKAINET_CUDA_OK;
 }
 
 }  // namespace
@@ -212,17 +278,11 @@ int32_t launch_tq_encode(const float* rows, const TqPlane& pl, int layer, int po
 }
 
 int32_t launch_tq_decode(const TqPlane& pl, int layer, int start_pos, int n, int heads, int D, int max_seq, int32_t seed_xor, float* out, cudaStream_t s, bool fixed_seed) {
-    if (n <= 0) return SKAINET_CUDA_OK;
-    tq_decode_kernel<float><<<dim3(n, heads), D, 0, s>>>(pl, layer, start_pos, n, heads, D, max_seq, seed_xor, fixed_seed ? 1 : 0, out);
-    SK_CUDA(cudaGetLastError());
-    return SKAINET_CUDA_OK;
+    return tq_decode_dispatch<float>(pl, layer, start_pos, n, heads, D, max_seq, seed_xor, fixed_seed, out, s);
 }
 
 int32_t launch_tq_decode_f16(const TqPlane& pl, int layer, int start_pos, int n, int heads, int D, int max_seq, int32_t seed_xor, __half* out, cudaStream_t s) {
-    if (n <= 0) return SKAINET_CUDA_OK;
-    tq_decode_kernel<__half><<<dim3(n, heads), D, 0, s>>>(pl, layer, start_pos, n, heads, D, max_seq, seed_xor, 0, out);
-    SK_CUDA(cudaGetLastError());
-    return SKAINET_CUDA_OK;
+    return tq_decode_dispatch<__half>(pl, layer, start_pos, n, heads, D, max_seq, seed_xor, false, out, s);
 }
 
 }  // namespace sk
