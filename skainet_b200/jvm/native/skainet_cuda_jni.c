@@ -176,6 +176,14 @@ JNIEXPORT jlong JNICALL JNI_FN(kvCreate)(JNIEnv* env, jobject thiz, jint layers,
     if (skainet_cuda_kv_create(layers, heads, headDim, maxSeqLen, slidingWindow ? 1 : 0, &h) != SKAINET_CUDA_OK) h = 0;
     return (jlong) h;
 }
+/* TurboQuantKvCacheStore.kt:62-199: residual bits 0 = PolarOnly */
+JNIEXPORT jlong JNICALL JNI_FN(kvCreateTurboquant)(JNIEnv* env, jobject thiz, jint layers, jint heads, jint headDim, jint maxSeqLen, jint keyBits,
+                                                   jint keyResidualBits, jint valueBits, jint valueResidualBits) {
+    (void) env; (void) thiz;
+    skainet_kv_t h = 0;
+    if (skainet_cuda_kv_create_turboquant(layers, heads, headDim, maxSeqLen, keyBits, keyResidualBits, valueBits, valueResidualBits, &h) != SKAINET_CUDA_OK) h = 0;
+    return (jlong) h;
+}
 JNIEXPORT jint JNICALL JNI_FN(kvFree)(JNIEnv* env, jobject thiz, jlong kv) { (void) env; (void) thiz; return skainet_cuda_kv_free((skainet_kv_t) kv); }
 JNIEXPORT jint JNICALL JNI_FN(kvEvict)(JNIEnv* env, jobject thiz, jlong kv, jint fromPos) { (void) env; (void) thiz; return skainet_cuda_kv_evict((skainet_kv_t) kv, fromPos); }
 JNIEXPORT jint JNICALL JNI_FN(kvClear)(JNIEnv* env, jobject thiz, jlong kv) { (void) env; (void) thiz; return skainet_cuda_kv_clear((skainet_kv_t) kv); }

@@ -50,6 +50,8 @@ public object CudaKernels {
 
     // KV-cache store
     public external fun kvCreate(layers: Int, heads: Int, headDim: Int, maxSeqLen: Int, slidingWindow: Boolean): Long
+    public external fun kvCreateTurboquant(layers: Int, heads: Int, headDim: Int, maxSeqLen: Int, keyBits: Int, keyResidualBits: Int,
+                                           valueBits: Int, valueResidualBits: Int): Long
     public external fun kvFree(kv: Long): Int
     public external fun kvAppend(kv: Long, layer: Int, key: FloatArray, value: FloatArray): Int
     public external fun kvRead(kv: Long, layer: Int, which: Int, startPos: Int, endPos: Int, out: FloatArray): Int
