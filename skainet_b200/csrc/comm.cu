@@ -190,7 +190,7 @@ gather_sum_norm_quant_kernel(P2PView v, float* __restrict__ x, int n, const floa
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     __shared__ float s_red[8];
-    __shared__ float s_part;                           // this CTA's sum of squares, read by the whole cluster
+    __shared__ float s_parts[8];                       // the sums of squares of the cluster's CTAs (at most 8), each written by its owner
     skd::pdl_launch_dependents();
     const int cs = gridDim.x, cx = blockIdx.x, row = blockIdx.y;
     const int world = v.world, rank = v.rank;
@@ -251,12 +251,13 @@ gather_sum_norm_quant_kernel(P2PView v, float* __restrict__ x, int n, const floa
         float t = 0.0f;
 #pragma unroll
         for (int k = 0; k < 8; ++k) t += s_red[k];
-        s_part = t;
+        // this CTA's partial goes into slot cx of EVERY CTA of the cluster: after the one barrier below each CTA sums its own
+        // copy, and nobody reads another CTA's shared memory afterwards (no second barrier before leaving)
+        for (int r = 0; r < cs; ++r) *cluster.map_shared_rank(&s_parts[cx], r) = t;
     }
     cluster.sync();
     float total = 0.0f;
-    for (int r = 0; r < cs; ++r) total += *cluster.map_shared_rank(&s_part, r);
-    cluster.sync();                                    // nobody leaves while its shared memory may still be read
+    for (int r = 0; r < cs; ++r) total += s_parts[r];
     const float nscale = 1.0f / sqrtf(total * (1.0f / (float) n) + eps);
     const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
 #pragma unroll

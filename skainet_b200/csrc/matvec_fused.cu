@@ -33,6 +33,7 @@ constexpr size_t MF_SMEM_MAX = 100 * 1024;
 // and down projections, everything under tensor parallelism) the two trade places shape by shape below 20 MB. When the
 // kernel itself quantizes an fp32 row, the ring kernel does so once per SM and the one-tile kernel once per CTA, and the
 // ring kernel wins down to a few MB (Q4_K 4096 x 4096: 3.3 against 5.2 us; 8192 x 1024: 4.1 against 4.6-5.7 us).
+// matvec_uses_ring() holds the rule.
 constexpr size_t RING_MIN_BYTES = (size_t) 20 << 20, RING_MIN_BYTES_F32_ROW = (size_t) 4 << 20;
 
 // ================================================================================================
@@ -282,8 +283,17 @@ static int32_t launch_q8_f(const Weight& w, const MatvecIn& in, float* y, const 
     }
 
 bool matvec_uses_ring(const Weight& w, int prep) {
-    const size_t lim = (prep != PREP_QUANTIZED && w.enc == SKAINET_ENC_Q4_K) ? RING_MIN_BYTES_F32_ROW : RING_MIN_BYTES;
-    return w.packed_bytes >= (int64_t) lim && (w.enc == SKAINET_ENC_Q4_K || w.enc == SKAINET_ENC_Q8_0);
+    if (w.enc != SKAINET_ENC_Q4_K && w.enc != SKAINET_ENC_Q8_0) return false;
+    if (w.packed_bytes >= (int64_t) RING_MIN_BYTES) return true;
+    if (w.enc != SKAINET_ENC_Q4_K || w.packed_bytes < (int64_t) RING_MIN_BYTES_F32_ROW) return false;
+    if (prep != PREP_QUANTIZED) return true;
+    // An already quantized row: the ring kernel where its static schedule fills the machine. Row groups of four go round
+    // robin over four groups per SM; when the last round is mostly empty (2560 rows: 640 groups over 592 slots) the
+    // one-tile kernel is faster (5.3 against 6.1 us), otherwise the ring kernel is (1280 x 8192: 4.5 against 4.9 us;
+    // 8192 x 2048: 5.6 against 6.0; 4096 x 4096: 4.8 against 5.4).
+    const int nrg = (w.rows + 3) / 4, slots = 4 * std::min(sm_count(), (nrg + 3) / 4);
+    const int rounds = (nrg + slots - 1) / slots;
+    return (int64_t) rounds * slots * 4 <= (int64_t) nrg * 5;          // at most a quarter of the slots idle
 }
 
 int32_t launch_matvec_fused(const Weight& w, const MatvecIn& in, int prep, float* y, const float* resid, cudaStream_t s,
