@@ -1,13 +1,8 @@
-// NCCL binding by dlopen (see comm.cuh), only the five entry points the decoder needs, plus a one-shot
-// all-reduce over peer memory for the small sums of a decode step.
-//
-// One-shot all-reduce (n <= P2P_MAX_ELEMS floats): every rank owns an "inbox" of world slots (two copies,
-// used alternately) and a flag word per (sender, CTA). A CTA stores its slice of the local vector into its
-// slot of every peer's inbox (plain stores over NVLink), publishes a sequence number with a system-scope
-// release store, waits (bounded) until every peer's number for this round has arrived, and sums the world
-// slots in rank order, so all ranks get bit-identical results. Nothing is reset between rounds: numbers only
-// grow, and a peer can be at most one round ahead, which the second inbox copy absorbs. Latency is one NVLink
-// store round instead of NCCL's multi-step protocol: what matters for a 32 KB sum issued 160 times per token.
+// NCCL binding by dlopen (see comm.cuh), only the entry points the decoder needs (setup, the arg-max gather, large sums),
+// plus the group exchanges of a decode step over peer memory: an in-place sum of a small vector, and the gather of the
+// rows a row-parallel matvec produced, fused with the RMSNorm and the activation quantizer that always follow it.
+// The protocol (no flags: every word of an inbox carries its own arrival state) is described where the kernels are.
+// Latency is one NVLink store instead of NCCL's multi-step protocol: what matters for a 32 KB sum issued 160 times per token.
 #include "comm.cuh"
 #include "tma.cuh"
 #include "actquant.cuh"

@@ -21,6 +21,8 @@
 #include "tma.cuh"
 #include "matvec_fused.cuh"
 
+#include <cstdlib>
+
 namespace sk {
 
 namespace {
@@ -363,6 +365,14 @@ int32_t launch_gemm_mma(const Weight& w, ActQ8K a, int m, float* y, const float*
     // One or two activation rows stay with the streaming matvec kernels (faster there; from three rows the tile
     // kernel wins: 13.6 vs 15.7 us on 11008x4096). Few rows: weight streaming decides, so 64-row tiles and a deep
     // pipeline; many rows: 128 x 32 output tiles.
+    // A small batch over a weight with few columns or few rows: the persistent ring with the same tile arithmetic
+    // (gemm_ring.cu). Measured at 8 rows: 4096 x 4096 5.5 against 8.6 us, 22016 x 4096 18.2 against 22.6, 4096 x 11008 18.2
+    // against 20.7; on 8192-column weights of 8192 rows and more this kernel's deep cp.async pipeline is the faster one
+    // (57344 x 8192: 77 against 135 us).
+    if (m >= 3 && m <= 8 && (w.cols <= 4096 || w.rows <= 4096)) {
+        const int32_t st = launch_rows_ring(w, a, m, y, resid, s);
+        if (st != 1) return st;
+    }
     if (m <= 2) return 1;
     // (row tiles of 32 or 16 for weights with few rows were measured slower: more activation re-fetch per weight byte)
     if (m <= 8) return launch_cfg<4, 1, 8>(w, a, m, y, resid, s);

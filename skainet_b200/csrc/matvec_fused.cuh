@@ -38,6 +38,8 @@ int32_t launch_matvec_ring(const Weight& w, const MatvecIn& in, int prep, float*
 // gemm_mma.cu: y[m][w.rows] (= resid +) for m >= 2 quantized activation rows on the tensor cores; 1 = not taken
 int32_t launch_gemm_mma(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s);
 int32_t launch_gemm_mma_q8(const Weight& w, ActSplit a, int m, float* y, const float* resid, cudaStream_t s);
+// gemm_ring.cu: 2..8 activation rows over a Q4_K weight through the persistent ring; 1 = not taken
+int32_t launch_rows_ring(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s);
 // gemm_tc.cu: the same for m >= 128 on tcgen05 with TMEM accumulators; 1 = not taken
 int32_t launch_gemm_tc(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s);
 

@@ -83,13 +83,13 @@ def test_q8_0_matvec_config1_shape(gpu, oracle):
 
 @pytest.mark.parametrize("n,k", [(11008, 4096), (4096, 11008)])
 def test_q4k_batched_rows_sweep(gpu, cuda_lib, oracle, n, k):
-    """Benchmark config 2 at M = 8, 64 (mma.sync tiles) and 512 (tcgen05), plus a ragged 130 on the first shape.
-    The reference computes M rows as M matvecs; the tile kernels use the same integer arithmetic, so the bar
-    is the matvec bar."""
+    """Benchmark config 2 at M = 8 (and 2, 5: the persistent ring with the tile arithmetic), 64 (mma.sync tiles) and 512
+    (tcgen05), plus a ragged 130 on the first shape. The reference computes M rows as M matvecs; the tile kernels use the
+    same integer arithmetic, so the bar is the matvec bar."""
     w = gpu.Weight.synth("Q4_K", n, k, seed=3 if n > k else 4, std=0.02)
     packed = w.export()
     rng = np.random.default_rng(5)
-    ms = [8, 64, 512] + ([130] if n > k else [])
+    ms = [2, 5, 8, 64, 512] + ([130] if n > k else [])
     x = rng.standard_normal((max(ms), k)).astype(np.float32)
     ref = _ref_matmul(oracle, "Q4_K", x, packed, k, n)
     for m in ms:
