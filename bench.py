@@ -20,7 +20,7 @@ Prints ONE JSON line (rank 0). Workloads (all inputs synthetic and seeded):
       --context keys (default 4096) for --batch sequences; metric = K/V bytes read per second.
   generate_7b — benchmark config 4 as one request: 512 random prompt tokens through the real prefill, then 128 greedy
       tokens; metric = generated tokens per second of request time, with the two phases reported apart.
-  q4k_gemm — benchmark config 2 at M = --batch rows (default 512) through the tensor-core tile kernels (tcgen05 from 128 rows);
+  q4k_gemm — benchmark config 2 at M = --batch rows (default 512) through the tensor-core tile kernels (tcgen05 from 288 rows);
       metric = 2*M*rows*cols operations per second, roofline against the measured cuBLAS bf16 burst.
   tp_collective — N >= 2 ranks: nothing but the group exchanges of a decode step (one [8192] fp32 row), timed on their own
       in a CUDA graph: the peer-memory sum, the store + gather + sum + RMSNorm + quantize kernel, and ncclAllReduce of the
@@ -273,7 +273,7 @@ def run_reference(args) -> None:
 
 def dtype_of(workload: str) -> str:
     if workload in GEMM_WORKLOADS:
-        return "f16 (4-bit code x 6-bit scale, exact) x f16 (int8 code) -> f32 on tcgen05 for m >= 128; u8 x s8 -> s32 on mma.sync below"
+        return "f16 (4-bit code x 6-bit scale, exact) x f16 (int8 code) -> f32 on tcgen05 for m >= 288; u8 x s8 -> s32 on mma.sync below"
     if workload in ATTN_WORKLOADS:
         return "f16 K/V, f32 q split in two f16 terms, f32 accumulate"
     if workload == "q8_0_matvec":
@@ -649,7 +649,7 @@ def run_gemm(args) -> None:
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype_of(args.workload),
             "data": "synthetic", "config": workload_config(args, 1, {"weights_per_shape": copies}),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
-                         "peak_kind": peak_kind, "kernel": "q4k_gemm_tc_kernel" if m >= 128 else "q4k_gemm_mma_kernel", "avg_launch_us": ms_step * 1e3 / len(ws),
+                         "peak_kind": peak_kind, "kernel": "q4k_gemm_tc_kernel" if m >= 288 else "q4k_gemm_mma_kernel", "avg_launch_us": ms_step * 1e3 / len(ws),
                          "note": "integer multiply-adds counted as 2 operations each; avg launch = timed region / calls (quantizer inside)"},
             "e2e": {"value": (ops / (e2e_ms * 1e-3) / 1e12) if e2e_ms else None, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": int(sum(4 * m * w.cols for w in ws)), "d2h_bytes_per_step": int(sum(4 * m * w.rows for w in ws))},

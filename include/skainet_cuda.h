@@ -175,7 +175,7 @@ SKAINET_CUDA_API int32_t skainet_cuda_weight_free(skainet_weight_t w);
 SKAINET_CUDA_API int32_t skainet_cuda_weight_dequant(skainet_weight_t w, float* dev_out, skainet_stream_t stream);
 
 /* y[m, rows] = x[m, cols] . W^T on the device. Q4_K / Q8_0: the dequant-fused matvec for m = 1 (and Q4_K up to
- * 2 rows), tensor-core tile kernels above that (mma.sync; tcgen05 with TMEM accumulators for Q4_K from 128 rows).
+ * 2 rows), tensor-core tile kernels above that (mma.sync; tcgen05 with TMEM accumulators for Q4_K from 288 rows).
  * Q6_K (native mode = int8 activations per 256 like skainet_q6k_matmul_rm, native/src/q6k_matmul.c:344-357)
  * and Q5_K (fp32 activations in both modes, native/src/q5k_matmul.c) run one warp per output row.
  * Counterpart of PackedViewMatmulKernel.runWith

@@ -358,7 +358,7 @@ int32_t launch_cfg_q8(const Weight& w, ActSplit a, int m, float* y, const float*
 // the weight is not Q4_K (the caller falls back to the per-row kernels).
 int32_t launch_gemm_mma(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s) {
     if (w.enc != SKAINET_ENC_Q4_K) return 1;
-    if (m >= 128) {
+    if (m >= TC_MIN_ROWS) {
         const int32_t st = launch_gemm_tc(w, a, m, y, resid, s);
         if (st != 1) return st;
     }

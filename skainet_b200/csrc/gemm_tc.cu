@@ -1,5 +1,5 @@
 // Batched rows on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM) for Q4_K weights
-// and m >= 128 activation rows: the prefill GEMM.
+// and many activation rows (the dispatcher sends 288 and more here): the prefill GEMM.
 //
 // The reference's arithmetic for one 256-element super-block (native/src/q4k_matmul.c:143-251) is
 //     y += d_x * ( d_w * S1 - dmin_w * S2 ),   S1 = sum_sb sc[sb] * <codes_sb, xq_sb>,   S2 = sum_sb mn[sb] * sum(xq_sb)
@@ -407,11 +407,11 @@ q4k_gemm_tc_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ h
 
 }  // namespace
 
-// y[m][w.rows] (= resid +) for m >= 128 quantized activation rows. Returns 1 when not taken (the caller
+// y[m][w.rows] (= resid +) for m >= TC_MIN_ROWS quantized activation rows. Returns 1 when not taken (the caller
 // falls back to the mma.sync tile kernel): other encodings, few rows, or scratch that would have to grow
 // while the stream is being captured.
 int32_t launch_gemm_tc(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s) {
-    if (w.enc != SKAINET_ENC_Q4_K || m < 128 || w.bpr < 1) return 1;
+    if (w.enc != SKAINET_ENC_Q4_K || m < TC_MIN_ROWS || w.bpr < 1) return 1;
     const int m_pad = (m + TC_N - 1) / TC_N * TC_N;
     const size_t xh_bytes = (size_t) m_pad * w.cols * 2, hs_bytes = (size_t) m_pad * (w.cols / 16) * 2, dx_bytes = (size_t) w.bpr * m_pad * 4;
     const size_t need = xh_bytes + hs_bytes + dx_bytes + 3 * 256;

@@ -30,6 +30,9 @@ namespace sk {
 // small kernels of the step
 // ================================================================================================
 constexpr int PROLOGUE_PREP_MAX_COLS = 4096, PROLOGUE_PREP_MAX_COLS_RING = 8192;
+// Prompt rows per pass of the body: the tcgen05 GEMM takes 132 us for 512 rows of a 25 MB weight against 2 x 95 us for two
+// passes of 256 through the mma.sync kernel (and 2 x 108 us through itself).
+constexpr int PREFILL_CHUNK_ROWS = 512;
 #ifndef SK_SWIGLU_PROLOGUE_MAX_COLS
 #define SK_SWIGLU_PROLOGUE_MAX_COLS 8192
 #endif
@@ -578,7 +581,7 @@ int32_t skainet_cuda_llama_create(const skainet_llama_config* cfg, skainet_model
     m->ffn_l = c.ffn_dim / c.tp_world; m->vocab_l = c.vocab / c.tp_world;
     m->layers.resize(c.n_layers);
     m->host_pos.assign(c.max_batch, 0);
-    m->max_rows = std::max(c.max_batch, 256);
+    m->max_rows = std::max(c.max_batch, PREFILL_CHUNK_ROWS);
     m->log_cap = 4096;
     m->magic = MODEL_MAGIC;
     { std::lock_guard<std::mutex> lk(g_model_mu); g_models.insert(m); }

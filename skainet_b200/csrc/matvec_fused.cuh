@@ -38,6 +38,10 @@ int32_t launch_matvec_ring(const Weight& w, const MatvecIn& in, int prep, float*
 // gemm_mma.cu: y[m][w.rows] (= resid +) for m >= 2 quantized activation rows on the tensor cores; 1 = not taken
 int32_t launch_gemm_mma(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s);
 int32_t launch_gemm_mma_q8(const Weight& w, ActSplit a, int m, float* y, const float* resid, cudaStream_t s);
+// Fewest activation rows sent to the tcgen05 kernel. Its call has a floor (activation tile preparation + one wave of
+// 128 x 128 tiles): measured per call on the 25 MB shapes, tcgen05 / mma.sync: 128 rows 86 / 64 us, 256 rows 108 / 95,
+// 384 rows 111 / 131, 512 rows 132 / 176.
+constexpr int TC_MIN_ROWS = 288;
 // gemm_ring.cu: 2..8 activation rows over a Q4_K weight through the persistent ring; 1 = not taken
 int32_t launch_rows_ring(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s);
 // gemm_tc.cu: the same for m >= 128 on tcgen05 with TMEM accumulators; 1 = not taken

@@ -3,8 +3,8 @@
 
 * the ring matvec kernels (weights of 20 MiB and more) on the Q4_K sweep shapes, the four linears of the
   70B-class layer and the Q8_0 32000 x 4096 table, plain and with the residual epilogue;
-* the Q4_K sweep at M in {8, 64, 512} on both shapes plus a ragged M = 130: `mma.sync` tiles below 128 rows,
-  the tcgen05 kernel from 128 rows;
+* the Q4_K sweep at M in {2, 5, 8, 64, 512} on both shapes plus ragged M = 130 and 300: the ring with the tile arithmetic up to
+  8 rows, `mma.sync` tiles below 288 rows, the tcgen05 kernel from 288 rows;
 * GQA decode attention (32 query / 8 KV heads, head_dim 128) at context 32768 x batch 1, 4096 x 16 and
   512 x 64, with RoPE (theta 1e4) applied to q and to every key before it is cached.
 
@@ -84,12 +84,12 @@ def test_q8_0_matvec_config1_shape(gpu, oracle):
 @pytest.mark.parametrize("n,k", [(11008, 4096), (4096, 11008)])
 def test_q4k_batched_rows_sweep(gpu, cuda_lib, oracle, n, k):
     """Benchmark config 2 at M = 8 (and 2, 5: the persistent ring with the tile arithmetic), 64 (mma.sync tiles) and 512
-    (tcgen05), plus a ragged 130 on the first shape. The reference computes M rows as M matvecs; the tile kernels use the
+    (tcgen05), plus ragged 130 (mma.sync) and 300 (tcgen05) on the first shape. The reference computes M rows as M matvecs; the tile kernels use the
     same integer arithmetic, so the bar is the matvec bar."""
     w = gpu.Weight.synth("Q4_K", n, k, seed=3 if n > k else 4, std=0.02)
     packed = w.export()
     rng = np.random.default_rng(5)
-    ms = [2, 5, 8, 64, 512] + ([130] if n > k else [])
+    ms = [2, 5, 8, 64, 512] + ([130, 300] if n > k else [])
     x = rng.standard_normal((max(ms), k)).astype(np.float32)
     ref = _ref_matmul(oracle, "Q4_K", x, packed, k, n)
     for m in ms:
