@@ -25,6 +25,8 @@
 // act_f16_tiles_kernel in exactly that order, so a B stage is one contiguous 32 KB bulk copy.
 // Every mbarrier wait is bounded; a wait that runs out raises the device flag, and the CTA still reaches
 // the common exit where TMEM is freed.
+// Measured and not kept: every CTA walking its super-blocks in a rotated order (so that CTAs sharing an activation tile do
+// not ask L2 for the same stage at the same moment): 138.6 against 134.0 us per call at 512 rows.
 #include "common.cuh"
 #include "actquant.cuh"
 #include "tma.cuh"
