@@ -16,6 +16,7 @@ Prints ONE JSON line (rank 0). Workloads (all inputs synthetic and seeded):
   q4k_matvec — benchmark config 2 at M=1: W[11008,4096] and W[4096,11008]; metric = algorithmic HBM
       GB/s over a sweep of distinct weights larger than 2x L2.
   q8_0_matvec — benchmark config 1: Q8_0 W[4096,4096], same protocol.
+  q6k_matvec, q5k_matvec — config 2's two shapes in the encodings Q4_K_M / Q5_K_M files mix in, same protocol.
   attn_decode — benchmark config 3: GQA decode attention, 32 query / 8 KV heads, head_dim 128, f16 cache of
       --context keys (default 4096) for --batch sequences; metric = K/V bytes read per second.
   generate_7b — benchmark config 4 as one request: 512 random prompt tokens through the real prefill, then 128 greedy
@@ -58,6 +59,9 @@ MATVEC_WORKLOADS = {
     # name: (encoding, [(rows=out, cols=in), ...], block bytes, block elems)
     "q4k_matvec": ("Q4_K", [(11008, 4096), (4096, 11008)], 144, 256),
     "q8_0_matvec": ("Q8_0", [(4096, 4096)], 34, 32),
+    # the formats Q4_K_M / Q5_K_M files mix in (ffn_down, attn_v, output head): config 2's shapes in those encodings
+    "q6k_matvec": ("Q6_K", [(11008, 4096), (4096, 11008)], 210, 256),
+    "q5k_matvec": ("Q5_K", [(11008, 4096), (4096, 11008)], 176, 256),
 }
 DECODE_WORKLOADS = {"decode_70b": ("70b", 4096), "decode_7b": ("7b", 512)}
 # decode attention alone: (query heads, kv heads, head_dim); context from --context
@@ -66,7 +70,7 @@ ATTN_WORKLOADS = {"attn_decode": (32, 8, 128)}
 GEMM_WORKLOADS = {"q4k_gemm": [(11008, 4096), (4096, 11008)]}
 # whole requests: (model, prompt tokens, generated tokens)
 REQUEST_WORKLOADS = {"generate_7b": ("7b", 512, 128)}
-BLOCK = {"Q4_K": (144, 256), "Q8_0": (34, 32)}
+BLOCK = {"Q4_K": (144, 256), "Q8_0": (34, 32), "Q5_K": (176, 256), "Q6_K": (210, 256)}
 
 
 def algorithmic_bytes(enc_bytes: int, enc_elems: int, rows: int, cols: int, m: int = 1) -> int:
@@ -145,8 +149,11 @@ def random_blocks(rng, enc: str, rows: int, cols: int) -> np.ndarray:
     bb, be = BLOCK[enc]
     packed = rng.integers(0, 256, size=rows * (cols // be) * bb, dtype=np.uint8)
     blk = packed.reshape(-1, bb)
+    if enc == "Q6_K":                       # ql[128] | qh[64] | scales[16] | d
+        blk[:, 208:210] = np.array([0.0002], np.float16).view(np.uint8)
+        return packed
     blk[:, 0:2] = np.array([0.002], np.float16).view(np.uint8)
-    if enc == "Q4_K":
+    if enc in ("Q4_K", "Q5_K"):
         blk[:, 2:4] = np.array([0.002], np.float16).view(np.uint8)
     return packed
 
@@ -165,7 +172,7 @@ def cpu_matvec_rate(workload: str, seconds: float) -> dict:
             R.matmul(enc, x, packed, c, r, "rm", use_ref=use_ref)
             done += algorithmic_bytes(bb, be, r, c); calls += 1
     dt = time.perf_counter() - t0
-    fn = "skainet_%s_matmul_rm" % ("q4k" if enc == "Q4_K" else "q8_0")
+    fn = "skainet_%s_matmul_rm" % {"Q4_K": "q4k", "Q8_0": "q8_0", "Q6_K": "q6k", "Q5_K": "q5k"}[enc]
     return {"value": done / dt / 1e9, "unit": "GB/s", "cores": 4 if use_ref else 1, "kind": "reference" if use_ref else "port",
             "sample": f"{calls} calls of {fn if use_ref else 'the oracle port'} over the workload's {len(items)} shapes in {dt:.1f} s "
                       f"({'its 4-thread row pool' if use_ref else 'scalar'}; host has {os.cpu_count()} cores)", "seconds": dt}
@@ -278,6 +285,10 @@ def dtype_of(workload: str) -> str:
         return "f16 K/V, f32 q split in two f16 terms, f32 accumulate"
     if workload == "q8_0_matvec":
         return "int8 x int8 (two-term activation) -> int32, f32 accumulate"
+    if workload == "q6k_matvec":
+        return "int8 x int6 -> int32, f32 accumulate"
+    if workload == "q5k_matvec":
+        return "f32 x 5-bit code, f32 accumulate"
     return "int8 x int4 -> int32, f32 accumulate (attention and norms f32, KV f16)" if workload in DECODE_WORKLOADS \
         else "int8 x int4 -> int32, f32 accumulate"
 
@@ -302,7 +313,7 @@ def workload_config(args, world: int, extra: dict | None = None) -> dict:
         enc, shapes, _, _ = MATVEC_WORKLOADS[args.workload]
         c = {"workload": args.workload, "encoding": enc, "shapes_out_in": shapes, "m": 1,
              "l2": "rotating distinct weights larger than 2x L2 per sweep", "activation": "fp32 N(0,1)",
-             "weights": "N(0,0.02) packed on device, seeded"}
+             "weights": "N(0,0.02) packed on device, seeded" if enc in ("Q4_K", "Q8_0") else "random valid blocks (random codes and scales, fixed f16 d), seeded, uploaded"}
     else:
         model, ctx = DECODE_WORKLOADS[args.workload]
         cfg = model_config(model)
@@ -345,6 +356,8 @@ def matmul_launches(w) -> int:
     """Kernels one skainet_cuda_matmul_dev call of one activation row launches: a Q4_K weight of 4 MiB or more with at
     most 12288 columns takes the ring kernel with the quantizer in its prologue (one launch); everything else is a quantizer
     launch followed by the matvec (csrc/api.cu)."""
+    if w.encoding == "Q5_K":                # fp32 activations: no quantizer
+        return 1
     return 1 if (w.encoding == "Q4_K" and w.packed_bytes >= (4 << 20) and w.cols <= 12288) else 2
 
 
@@ -418,7 +431,11 @@ def run_matvec(args) -> None:
     info = device.device_info()
     enc, shapes, bb, be = MATVEC_WORKLOADS[args.workload]
     copies = max(2, int(np.ceil(2.2 * info["l2_bytes"] / min(r * (c // be) * bb for r, c in shapes))))
-    weights = [device.Weight.synth(enc, r, c, seed=1000 * rank + 10 * si + ci, std=0.02) for ci in range(copies) for si, (r, c) in enumerate(shapes)]
+    if enc in ("Q4_K", "Q8_0"):
+        weights = [device.Weight.synth(enc, r, c, seed=1000 * rank + 10 * si + ci, std=0.02) for ci in range(copies) for si, (r, c) in enumerate(shapes)]
+    else:                                   # random valid blocks packed on the host (the reference's microbench fixture style)
+        hrng = np.random.default_rng(1000 * rank + 3)
+        weights = [device.Weight.upload(random_blocks(hrng, enc, r, c), enc, r, c) for ci in range(copies) for si, (r, c) in enumerate(shapes)]
     bytes_per_step = sum(algorithmic_bytes(bb, be, w.rows, w.cols) for w in weights)
     stream = torch.cuda.Stream()
 
@@ -476,9 +493,10 @@ def run_matvec(args) -> None:
             "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": dtype_of(args.workload), "data": "synthetic", "config": workload_config(args, world, {"weights_per_shape": copies}),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": bytes_per_step / len(weights) * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE,
-                         "traffic_source": "ncu dram bytes per launch of the 11008x4096 Q4_K capture, scaled by weight bytes",
-                         "peak_kind": peak_kind, "kernel": "q4k_matvec_ring_kernel" if enc == "Q4_K" else "q8_0_matvec_fused_kernel",
+                         "traffic": bytes_per_step / len(weights) * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE if enc in ("Q4_K", "Q8_0") else None,
+                         "traffic_source": "ncu dram bytes per launch of the 11008x4096 Q4_K capture, scaled by weight bytes" if enc in ("Q4_K", "Q8_0") else None,
+                         "peak_kind": peak_kind,
+                         "kernel": {"Q4_K": "q4k_matvec_ring_kernel", "Q8_0": "q8_0_matvec_fused_kernel", "Q6_K": "q6k_rows_kernel", "Q5_K": "q5k_rows_kernel"}[enc],
                          "avg_launch_us": per_launch_us,
                          "read_floor_us": floor_ms * 1e3 / len(weights), "read_floor_gbs": bytes_per_step / (floor_ms * 1e-3) / 1e9,
                          "note": "avg launch = timed region / matvec calls; the activation quantizer (its own launch for Q8_0 and small weights, the "

@@ -183,7 +183,7 @@ q4k_rows_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__
             if (lane == 0) gr_arrive(empty + stage);     // this warp is done reading the stage
             if (++stage == nstages) { stage = 0; phase ^= 1; }
         }
-        // the four warps' partial tiles -> one; two buffers, so one barrier per row group is enough
+        // the eight warps' partial tiles -> one; two buffers, so one barrier per row group is enough
         float* part = s_part + pbuf * GR_BLKS * 128;
         *reinterpret_cast<float4*>(part + warp * 128 + lane * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
         gr_group_sync(grp);

@@ -25,6 +25,13 @@ __global__ void __launch_bounds__(512) probe_read_kernel(const uint4* __restrict
 int32_t launch_probe_read(const Weight& w, uint32_t* sink, cudaStream_t s) {
     const size_t nblk = (size_t) w.rows * w.bpr;
     const size_t qs_b = w.enc == SKAINET_ENC_Q8_0 ? 32 : 128, hdr_b = w.enc == SKAINET_ENC_Q8_0 ? 2 : 16;
+    if (w.enc == SKAINET_ENC_Q5_K || w.enc == SKAINET_ENC_Q6_K) {
+        // four planes in one allocation (256-byte aligned, in this order): read the span from the first to the end of the last
+        const uint8_t* end = w.enc == SKAINET_ENC_Q6_K ? (const uint8_t*) w.aux + nblk * 2 : (const uint8_t*) w.extra + nblk * 32;
+        const size_t span = (size_t) (end - (const uint8_t*) w.qs);
+        SK_CUDA(launch_pdl(probe_read_kernel, dim3(sm_count() * 4), dim3(512), 0, s, (const uint4*) w.qs, (span + 15) / 16, (const uint4*) w.hdr, (size_t) 0, sink));
+        return SKAINET_CUDA_OK;
+    }
     SK_CUDA(launch_pdl(probe_read_kernel, dim3(sm_count() * 4), dim3(512), 0, s, (const uint4*) w.qs, nblk * qs_b / 16,
                        (const uint4*) w.hdr, nblk * hdr_b / 16, sink));
     return SKAINET_CUDA_OK;

@@ -193,16 +193,35 @@ def test_tcgen05_rows_tile_kernel_is_exact_and_repeatable(gpu, oracle, n, k, m, 
 
 
 @pytest.mark.parametrize("enc", ["Q6_K", "Q5_K"])
-@pytest.mark.parametrize("n,k,m", [(64, 256, 1), (129, 4096, 1), (33, 2048, 5)])
+@pytest.mark.parametrize("n,k,m", [(64, 256, 1), (129, 4096, 1), (33, 2048, 5), (4096, 11008, 1), (1001, 4096, 3), (515, 2304, 8),
+                                   (130, 1280, 11), (77, 256, 20), (11008, 4096, 2)])
 def test_k_quant_next_formats_matvec(gpu, oracle, enc, n, k, m):
     """Q6_K / Q5_K over resident planes against the reference's C kernels (native mode: Q6_K quantizes the
     activation to int8 per 256 and is integer-exact per block; Q5_K keeps fp32) and, in F32 mode, against the
-    dequantised product in float64."""
+    dequantised product in float64. The shapes cover rows that are not a multiple of the CTA's four, block counts per row
+    that are not a multiple of the four a warp step takes (43, 9, 5, 1), every activation-row group size and batches that
+    need more than one pass over the weight."""
     w_bytes = oracle.random_kquant_blocks(enc, n, k, seed=n + k + m)
     x = np.random.default_rng(n * 7 + m).standard_normal((m, k)).astype(np.float32)
     w = gpu.Weight.upload(w_bytes, enc, n, k)
     ref = oracle.matmul(enc, x, w_bytes, k, n, "rm", use_ref=oracle.ref() is not None)
     rel_err_ok(gpu.matmul_host(w, x), ref, 1e-5 if enc == "Q6_K" else 1e-4)
-    exact = x.astype(np.float64) @ oracle.dequant(enc, w_bytes).reshape(n, k).astype(np.float64).T
-    rel_err_ok(gpu.matmul_host(w, x, act_mode=1), exact, 1e-4)
+    if n * k <= 1 << 21:                       # the exact-float mode is a plain kernel; small shapes only
+        exact = x.astype(np.float64) @ oracle.dequant(enc, w_bytes).reshape(n, k).astype(np.float64).T
+        rel_err_ok(gpu.matmul_host(w, x, act_mode=1), exact, 1e-4)
+    w.free()
+
+
+@pytest.mark.parametrize("n,k,m", [(300, 2816, 1), (64, 4096, 8)])
+def test_q6k_rows_of_a_batch_equal_single_rows(gpu, oracle, n, k, m):
+    """Rows of a batch are independent matvecs (native/src/q6k_matmul.c:289-357): the eight-row pass must give each
+    row the very bits a single-row call gives it, and a second call must repeat them."""
+    w_bytes = oracle.random_kquant_blocks("Q6_K", n, k, seed=3 * n + m)
+    x = np.random.default_rng(n + m).standard_normal((max(m, 8), k)).astype(np.float32)
+    w = gpu.Weight.upload(w_bytes, "Q6_K", n, k)
+    full = gpu.matmul_host(w, x)
+    assert np.array_equal(full, gpu.matmul_host(w, x))
+    for i in (0, 3, 7):
+        assert np.array_equal(full[i], gpu.matmul_host(w, x[i:i + 1])[0])
+    assert np.array_equal(full[:5], gpu.matmul_host(w, x[:5]))
     w.free()
