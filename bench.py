@@ -17,6 +17,7 @@ Prints ONE JSON line (rank 0). Workloads (all inputs synthetic and seeded):
       GB/s over a sweep of distinct weights larger than 2x L2.
   q8_0_matvec — benchmark config 1: Q8_0 W[4096,4096], same protocol.
   q6k_matvec, q5k_matvec — config 2's two shapes in the encodings Q4_K_M / Q5_K_M files mix in, same protocol.
+  q6k_gemm — the q4k_gemm protocol (--batch activation rows, default 512) on the same shapes as Q6_K.
   attn_decode — benchmark config 3: GQA decode attention, 32 query / 8 KV heads, head_dim 128, f16 cache of
       --context keys (default 4096) for --batch sequences; metric = K/V bytes read per second.
   generate_7b — benchmark config 4 as one request: 512 random prompt tokens through the real prefill, then 128 greedy
@@ -67,7 +68,8 @@ DECODE_WORKLOADS = {"decode_70b": ("70b", 4096), "decode_7b": ("7b", 512)}
 # decode attention alone: (query heads, kv heads, head_dim); context from --context
 ATTN_WORKLOADS = {"attn_decode": (32, 8, 128)}
 # batched rows through the tensor-core tile kernel: the Q4_K sweep shapes with --batch activation rows (default 512)
-GEMM_WORKLOADS = {"q4k_gemm": [(11008, 4096), (4096, 11008)]}
+GEMM_WORKLOADS = {"q4k_gemm": [(11008, 4096), (4096, 11008)], "q6k_gemm": [(11008, 4096), (4096, 11008)]}
+GEMM_ENC = {"q4k_gemm": "Q4_K", "q6k_gemm": "Q6_K"}
 # whole requests: (model, prompt tokens, generated tokens)
 REQUEST_WORKLOADS = {"generate_7b": ("7b", 512, 128)}
 BLOCK = {"Q4_K": (144, 256), "Q8_0": (34, 32), "Q5_K": (176, 256), "Q6_K": (210, 256)}
@@ -259,7 +261,7 @@ def run_reference(args) -> None:
         elif args.workload in ATTN_WORKLOADS:
             r = cpu_attn_rate(args.workload, args.context, max(1, args.batch)); unit = "GB/s"; metric = "attn_decode_hbm_gbs"
         elif args.workload in GEMM_WORKLOADS:
-            r = cpu_gemm_rate(args.workload, args.batch if args.batch > 1 else 512, budget); unit = "TFLOP/s"; metric = "q4k_gemm_tflops"
+            r = cpu_gemm_rate(args.workload, args.batch if args.batch > 1 else 512, budget); unit = "TFLOP/s"; metric = f"{args.workload}_tflops"
         elif args.workload in REQUEST_WORKLOADS:
             r = cpu_request_rate(args.workload, budget); unit = "tokens/s"; metric = "request_generated_tokens_per_s"
         else:
@@ -279,6 +281,8 @@ def run_reference(args) -> None:
 
 
 def dtype_of(workload: str) -> str:
+    if workload == "q6k_gemm":
+        return "s8 (6-bit code - 32) x s8 -> s32 on mma.sync per 16-element scale group, int8 group scales, f32 block terms"
     if workload in GEMM_WORKLOADS:
         return "f16 (4-bit code x 6-bit scale, exact) x f16 (int8 code) -> f32 on tcgen05 for m >= 288; u8 x s8 -> s32 on mma.sync below"
     if workload in ATTN_WORKLOADS:
@@ -302,9 +306,10 @@ def workload_config(args, world: int, extra: dict | None = None) -> dict:
              "generated_tokens": n_gen, "prompt": "uniform random token ids, seeded", "weights": "N(0,0.02) packed on device, seeded",
              "l2": "weights per pass far larger than L2"}
     elif args.workload in GEMM_WORKLOADS:
-        c = {"workload": args.workload, "encoding": "Q4_K", "shapes_out_in": GEMM_WORKLOADS[args.workload],
+        c = {"workload": args.workload, "encoding": GEMM_ENC[args.workload], "shapes_out_in": GEMM_WORKLOADS[args.workload],
              "m": args.batch if args.batch > 1 else 512, "activation": "fp32 N(0,1), quantized to int8 per 256 on the device inside the timed region",
-             "weights": "N(0,0.02) packed on device, seeded", "l2": "rotating distinct weights larger than 2x L2 per sweep"}
+             "weights": "N(0,0.02) packed on device, seeded" if GEMM_ENC[args.workload] == "Q4_K" else "random valid blocks (random codes and scales, fixed f16 d), seeded, uploaded",
+             "l2": "rotating distinct weights larger than 2x L2 per sweep"}
     elif args.workload in ATTN_WORKLOADS:
         h, hkv, d = ATTN_WORKLOADS[args.workload]
         c = {"workload": args.workload, "heads": h, "kv_heads": hkv, "head_dim": d, "batch": max(1, args.batch), "context": args.context,
@@ -522,16 +527,17 @@ def cpu_gemm_rate(workload: str, m: int, seconds: float) -> dict:
     """The reference has no batched kernel: its row-major Q4_K matvec is called once per activation row."""
     from oracle import ref as R
     shapes = GEMM_WORKLOADS[workload]
+    enc = GEMM_ENC[workload]
     use_ref = R.ref() is not None
     rng = np.random.default_rng(5)
-    items = [(r, c, random_blocks(rng, "Q4_K", r, c), rng.standard_normal(c).astype(np.float32)) for r, c in shapes]
+    items = [(r, c, random_blocks(rng, enc, r, c), rng.standard_normal(c).astype(np.float32)) for r, c in shapes]
     t0 = time.perf_counter(); calls = 0; flops = 0
     while time.perf_counter() - t0 < seconds:
         for r, c, packed, x in items:
-            R.matmul("Q4_K", x, packed, c, r, "rm", use_ref=use_ref); calls += 1; flops += 2 * r * c
+            R.matmul(enc, x, packed, c, r, "rm", use_ref=use_ref); calls += 1; flops += 2 * r * c
     dt = time.perf_counter() - t0
     return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": 4 if use_ref else 1, "kind": "reference" if use_ref else "port",
-            "sample": f"{calls} single-row calls of the reference's row-major Q4_K kernel (it has no batched form); the rate per row "
+            "sample": f"{calls} single-row calls of the reference's row-major {enc} kernel (it has no batched form); the rate per row "
                       f"does not depend on m = {m}", "seconds": dt}
 
 
@@ -625,8 +631,13 @@ def run_gemm(args) -> None:
     info = device.device_info()
     shapes = GEMM_WORKLOADS[args.workload]
     m = args.batch if args.batch > 1 else 512
-    copies = max(2, int(np.ceil(2.2 * info["l2_bytes"] / min(r * (c // 256) * 144 for r, c in shapes))) // 2)
-    ws = [device.Weight.synth("Q4_K", r, c, seed=10 * si + ci, std=0.02) for ci in range(copies) for si, (r, c) in enumerate(shapes)]
+    enc = GEMM_ENC[args.workload]
+    copies = max(2, int(np.ceil(2.2 * info["l2_bytes"] / min(r * (c // 256) * BLOCK[enc][0] for r, c in shapes))) // 2)
+    if enc == "Q4_K":
+        ws = [device.Weight.synth("Q4_K", r, c, seed=10 * si + ci, std=0.02) for ci in range(copies) for si, (r, c) in enumerate(shapes)]
+    else:
+        hrng = np.random.default_rng(11)
+        ws = [device.Weight.upload(random_blocks(hrng, enc, r, c), enc, r, c) for ci in range(copies) for si, (r, c) in enumerate(shapes)]
     gen = torch.Generator(device="cuda").manual_seed(3)
     xs = {c: torch.randn(m, c, device="cuda", generator=gen) for _, c in shapes}
     ys = {r: torch.empty(m, r, device="cuda") for r, _ in shapes}
@@ -663,11 +674,15 @@ def run_gemm(args) -> None:
             t0 = time.perf_counter(); e2e_sweep(); e2e_ms = (time.perf_counter() - t0) * 1e3
     peak, peak_kind = load_tensor_peak()
     achieved = ops / (ms_step * 1e-3) / 1e12
-    line = {"metric": "q4k_gemm_tflops", "value": achieved, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": warm,
+    if enc == "Q4_K":
+        kernel = "q4k_gemm_tc_kernel" if m >= 288 else "q4k_gemm_mma_kernel"
+    else:
+        kernel = "q6k_gemm_mma_kernel" if m >= 9 else "q6k_rows_kernel"
+    line = {"metric": f"{args.workload}_tflops", "value": achieved, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": warm,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype_of(args.workload),
             "data": "synthetic", "config": workload_config(args, 1, {"weights_per_shape": copies}),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
-                         "peak_kind": peak_kind, "kernel": "q4k_gemm_tc_kernel" if m >= 288 else "q4k_gemm_mma_kernel", "avg_launch_us": ms_step * 1e3 / len(ws),
+                         "peak_kind": peak_kind, "kernel": kernel, "avg_launch_us": ms_step * 1e3 / len(ws),
                          "note": "integer multiply-adds counted as 2 operations each; avg launch = timed region / calls (quantizer inside)"},
             "e2e": {"value": (ops / (e2e_ms * 1e-3) / 1e12) if e2e_ms else None, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": int(sum(4 * m * w.cols for w in ws)), "d2h_bytes_per_step": int(sum(4 * m * w.rows for w in ws))},

@@ -3,7 +3,8 @@
 // The kernels that carry the traffic (q6k_rows_kernel, q5k_rows_kernel): one warp per output row, four super-blocks per
 // step, the next step's weight words requested before the current one is worked on (and the first step's before the wait
 // on the preceding kernel). Up to eight (Q6_K) or four (Q5_K) activation rows ride on one pass over the weight: the codes
-// are decoded once and reused; larger batches take one pass per group. Both formats interleave their bit fields in runs
+// are decoded once and reused; larger Q5_K batches take one pass per group, larger Q6_K ones the tensor-core tile kernel
+// of gemm_kq.cu. Both formats interleave their bit fields in runs
 // of 32 elements. Q6_K: eight lanes per super-block, 16 bytes per lane = 16 consecutive elements of one run in the low
 // nibbles and of the run 64 elements later in the high nibbles, one scale group each. Q5_K: see its kernel.
 //
@@ -67,6 +68,9 @@ q6k_matvec_f32_kernel(const uint8_t* __restrict__ ql, const uint8_t* __restrict_
     if (lane == 0) y[(size_t) mrow * rows + row] = acc;
 }
 
+// Activation rows from which the tensor-core tile kernel (gemm_kq.cu) takes a Q6_K product: 11008 x 4096 at 9 / 12 rows
+// 52 / 50 us there against 57 / 71 us in two passes of the row kernel (8 rows: 47 us in one pass).
+constexpr int Q6K_GEMM_MIN_ROWS = 9;
 constexpr int KQR_WARPS = 4;       // small CTAs: a 4096-row weight still spreads evenly over the SMs
 
 __device__ __forceinline__ uint32_t word_of(const uint4& v, int k) { return k == 0 ? v.x : k == 1 ? v.y : k == 2 ? v.z : v.w; }
@@ -249,6 +253,10 @@ cudaError_t launch_q5k_rows(const Weight& w, const float* x, int mm, float* y, c
 int32_t launch_matvec_kq(const Weight& w, const float* x, ActQ8K a, int m, float* y, int act_mode, cudaStream_t s) {
     if (m <= 0 || w.rows <= 0) return SKAINET_CUDA_OK;
     if (w.enc == SKAINET_ENC_Q6_K && act_mode == SKAINET_ACT_NATIVE) {
+        if (m >= Q6K_GEMM_MIN_ROWS) {
+            const int32_t st = launch_gemm_q6k(w, a, m, y, s);
+            if (st != 1) return st;
+        }
         for (int m0 = 0; m0 < m; m0 += 8) {
             const int mm = std::min(8, m - m0);
             if (mm == 1) SK_CUDA(launch_q6k_rows<1>(w, a, m0, mm, y, s));

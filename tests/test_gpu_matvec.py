@@ -194,13 +194,16 @@ def test_tcgen05_rows_tile_kernel_is_exact_and_repeatable(gpu, oracle, n, k, m, 
 
 @pytest.mark.parametrize("enc", ["Q6_K", "Q5_K"])
 @pytest.mark.parametrize("n,k,m", [(64, 256, 1), (129, 4096, 1), (33, 2048, 5), (4096, 11008, 1), (1001, 4096, 3), (515, 2304, 8),
-                                   (130, 1280, 11), (77, 256, 20), (11008, 4096, 2)])
+                                   (130, 1280, 11), (77, 256, 20), (11008, 4096, 2), (300, 2816, 16), (200, 1024, 70), (4096, 11008, 130),
+                                   (1000, 4096, 512), (11008, 1024, 130), (64, 512, 9)])
 def test_k_quant_next_formats_matvec(gpu, oracle, enc, n, k, m):
     """Q6_K / Q5_K over resident planes against the reference's C kernels (native mode: Q6_K quantizes the
     activation to int8 per 256 and is integer-exact per block; Q5_K keeps fp32) and, in F32 mode, against the
     dequantised product in float64. The shapes cover rows that are not a multiple of the CTA's four, block counts per row
-    that are not a multiple of the four a warp step takes (43, 9, 5, 1), every activation-row group size and batches that
-    need more than one pass over the weight."""
+    that are not a multiple of the four a warp step takes (43, 9, 5, 1), every activation-row group size, batches that
+    need more than one pass over the weight and, from nine rows, the Q6_K tensor-core tile kernel (ragged in both
+    directions: 300 / 200 / 1000 weight rows against tiles of 32, 11008 against tiles of 64, 9 / 70 / 130 activation rows
+    against tiles of 64)."""
     w_bytes = oracle.random_kquant_blocks(enc, n, k, seed=n + k + m)
     x = np.random.default_rng(n * 7 + m).standard_normal((m, k)).astype(np.float32)
     w = gpu.Weight.upload(w_bytes, enc, n, k)
@@ -212,16 +215,17 @@ def test_k_quant_next_formats_matvec(gpu, oracle, enc, n, k, m):
     w.free()
 
 
-@pytest.mark.parametrize("n,k,m", [(300, 2816, 1), (64, 4096, 8)])
+@pytest.mark.parametrize("n,k,m", [(300, 2816, 8), (64, 4096, 8), (300, 2816, 70), (129, 1024, 200)])
 def test_q6k_rows_of_a_batch_equal_single_rows(gpu, oracle, n, k, m):
-    """Rows of a batch are independent matvecs (native/src/q6k_matmul.c:289-357): the eight-row pass must give each
-    row the very bits a single-row call gives it, and a second call must repeat them."""
+    """Rows of a batch are independent matvecs (native/src/q6k_matmul.c:289-357): the eight-row pass and the tensor-core
+    tile kernel (nine rows and more) must give each row the very bits a single-row call gives it, and a second call
+    must repeat them."""
     w_bytes = oracle.random_kquant_blocks("Q6_K", n, k, seed=3 * n + m)
-    x = np.random.default_rng(n + m).standard_normal((max(m, 8), k)).astype(np.float32)
+    x = np.random.default_rng(n + m).standard_normal((m, k)).astype(np.float32)
     w = gpu.Weight.upload(w_bytes, "Q6_K", n, k)
     full = gpu.matmul_host(w, x)
     assert np.array_equal(full, gpu.matmul_host(w, x))
-    for i in (0, 3, 7):
+    for i in (0, 3, 7, m - 1):
         assert np.array_equal(full[i], gpu.matmul_host(w, x[i:i + 1])[0])
     assert np.array_equal(full[:5], gpu.matmul_host(w, x[:5]))
     w.free()
