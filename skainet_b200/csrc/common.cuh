@@ -115,9 +115,9 @@ size_t act_scratch_bytes(int enc, int act_mode, int m, int cols);
 int32_t launch_act_quant(int enc, int act_mode, const float* x, int m, int cols, void* scratch, cudaStream_t s);
 struct ActQ8K;
 // matvec_kq.cu: Q6_K (int8-per-256 or fp32 activations) and Q5_K (fp32 activations) over resident planes
-int32_t launch_matvec_kq(const Weight& w, const float* x, ActQ8K a, int m, float* y, int act_mode, cudaStream_t s);
+int32_t launch_matvec_kq(const Weight& w, const float* x, ActQ8K a, int m, float* y, int act_mode, cudaStream_t s, const float* resid = nullptr);
 // gemm_kq.cu: Q6_K weights x m quantized activation rows on the tensor cores (mma.sync); 1 = not taken
-int32_t launch_gemm_q6k(const Weight& w, ActQ8K a, int m, float* y, cudaStream_t s);
+int32_t launch_gemm_q6k(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s);
 int32_t launch_matvec(const Weight& w, const float* x, const void* act_scratch, int m, float* y, int act_mode,
                       cudaStream_t s);
 // matvec_stream.cu: rows m0..m0+mm of the quantized activation; returns 1 when the shape is not taken

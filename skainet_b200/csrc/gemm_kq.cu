@@ -55,7 +55,7 @@ __device__ __forceinline__ void kg_mma_s8(int (&c)[4], uint32_t a0, uint32_t a1,
 template <int NW, int NS>
 __global__ void __launch_bounds__(NW * 32)
 q6k_gemm_mma_kernel(const uint8_t* __restrict__ ql, const uint8_t* __restrict__ qh, const int8_t* __restrict__ sc, const uint8_t* __restrict__ dd,
-                    int rows, int bpr, ActQ8K act, int m, float* __restrict__ y) {
+                    int rows, int bpr, ActQ8K act, int m, float* y, const float* resid) {
     constexpr int KG_RT = NW * 16, NTHR = NW * 32;
     constexpr int KG_OFF_QH = kg_off_qh(NW), KG_OFF_SC = kg_off_sc(NW), KG_OFF_X = kg_off_x(NW), KG_OFF_XD = kg_off_xd(NW), KG_STAGE = kg_stage(NW);
     extern __shared__ __align__(128) uint8_t smem[];
@@ -168,33 +168,36 @@ q6k_gemm_mma_kernel(const uint8_t* __restrict__ ql, const uint8_t* __restrict__ 
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int row = row0 + warp * 16 + g + 8 * (j >> 1), col = col0 + nt * 8 + 2 * t + (j & 1);
-            if (row < rows && col < m) y[(size_t) col * rows + row] = acc[nt][j];
+            if (row < rows && col < m) {
+                const size_t o = (size_t) col * rows + row;
+                y[o] = resid ? __fadd_rn(resid[o], acc[nt][j]) : acc[nt][j];       // resid may be y itself: read and written by this thread only
+            }
         }
     }
 }
 
 template <int NW, int NS>
-int32_t launch_gemm_q6k_nw(const Weight& w, ActQ8K a, int m, float* y, cudaStream_t s) {
+int32_t launch_gemm_q6k_nw(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s) {
     const int smem = NS * kg_stage(NW);
     SK_TRY(ensure_dynamic_smem((const void*) q6k_gemm_mma_kernel<NW, NS>, smem));
     const dim3 grid((m + KG_MT - 1) / KG_MT, (w.rows + NW * 16 - 1) / (NW * 16));
     if (grid.y > 65535) return 1;
     SK_CUDA(launch_pdl(q6k_gemm_mma_kernel<NW, NS>, grid, dim3(NW * 32), (size_t) smem, s, (const uint8_t*) w.qs, (const uint8_t*) w.extra, (const int8_t*) w.hdr,
-                       (const uint8_t*) w.aux, w.rows, w.bpr, a, m, y));
+                       (const uint8_t*) w.aux, w.rows, w.bpr, a, m, y, resid));
     return SKAINET_CUDA_OK;
 }
 
 }  // namespace
 
-// y[m][w.rows] for a Q6_K weight and m quantized activation rows on the tensor cores. A grid that gives each SM at most
+// y[m][w.rows] (= resid +) for a Q6_K weight and m quantized activation rows on the tensor cores. A grid that gives each SM at most
 // one CTA has nothing but its own ring to hide the load latency behind: four stages there, three otherwise (two CTAs per
 // SM). Measured per call on 37 MB / 55 MB weights, stages 2 / 3 / 4: 11008 x 4096 at 64 rows 64 / 43 / 52 us, at 512 rows
 // 200 / 198 / 249; 4096 x 11008 at 64 rows 91 / 108 / 68, at 128 rows 167 / 110 / 69; 8192 x 8192 at 64 rows 123 / 82 / 53.
 // Tiles of 32 weight rows (two warps) were slower throughout (the activation tile is reloaded twice as often).
-int32_t launch_gemm_q6k(const Weight& w, ActQ8K a, int m, float* y, cudaStream_t s) {
+int32_t launch_gemm_q6k(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s) {
     if (w.enc != SKAINET_ENC_Q6_K || m < 1 || w.rows < 1 || w.bpr < 1) return 1;
     const int64_t ctas = (int64_t) ((m + KG_MT - 1) / KG_MT) * ((w.rows + 63) / 64);
-    return ctas <= sm_count() ? launch_gemm_q6k_nw<4, 4>(w, a, m, y, s) : launch_gemm_q6k_nw<4, 3>(w, a, m, y, s);
+    return ctas <= sm_count() ? launch_gemm_q6k_nw<4, 4>(w, a, m, y, resid, s) : launch_gemm_q6k_nw<4, 3>(w, a, m, y, resid, s);
 }
 
 }  // namespace sk

@@ -87,7 +87,7 @@ struct Q6Step { uint4 a, h; uint2 s8; float d; };
 template <int MT>
 __global__ void __launch_bounds__(KQR_WARPS * 32)
 q6k_rows_kernel(const uint8_t* __restrict__ ql, const uint8_t* __restrict__ qh, const int8_t* __restrict__ sc, const uint8_t* __restrict__ dd,
-                int rows, int bpr, ActQ8K act, int m0, int mm, float* __restrict__ y) {
+                int rows, int bpr, ActQ8K act, int m0, int mm, float* y, const float* resid) {
     skd::pdl_launch_dependents();
     const int lane = threadIdx.x & 31, row = min((int) (blockIdx.x * KQR_WARPS + (threadIdx.x >> 5)), rows - 1);   // a warp past the end repeats the last row
     const int cols = bpr * 256, j = lane & 7, bq = lane >> 3;
@@ -147,7 +147,10 @@ q6k_rows_kernel(const uint8_t* __restrict__ ql, const uint8_t* __restrict__ qh, 
     if ((int) (blockIdx.x * KQR_WARPS + (threadIdx.x >> 5)) >= rows) return;
 #pragma unroll
     for (int i = 0; i < MT; ++i)
-        if (i < mm && lane == i) y[(size_t) (m0 + i) * rows + row] = acc[i];
+        if (i < mm && lane == i) {
+            const size_t o = (size_t) (m0 + i) * rows + row;
+            y[o] = resid ? __fadd_rn(resid[o], acc[i]) : acc[i];       // resid may be y itself: read and written by this thread only
+        }
 }
 
 // Q5_K over MT fp32 activation rows. The fp32 activation is sixteen times the weight bytes, so its loads decide
@@ -236,9 +239,9 @@ q5k_rows_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ hdr,
 }
 
 template <int MT>
-cudaError_t launch_q6k_rows(const Weight& w, ActQ8K a, int m0, int mm, float* y, cudaStream_t s) {
+cudaError_t launch_q6k_rows(const Weight& w, ActQ8K a, int m0, int mm, float* y, const float* resid, cudaStream_t s) {
     return launch_pdl(q6k_rows_kernel<MT>, dim3((w.rows + KQR_WARPS - 1) / KQR_WARPS), dim3(KQR_WARPS * 32), 0, s, (const uint8_t*) w.qs,
-                      (const uint8_t*) w.extra, (const int8_t*) w.hdr, (const uint8_t*) w.aux, w.rows, w.bpr, a, m0, mm, y);
+                      (const uint8_t*) w.extra, (const int8_t*) w.hdr, (const uint8_t*) w.aux, w.rows, w.bpr, a, m0, mm, y, resid);
 }
 template <int MT>
 cudaError_t launch_q5k_rows(const Weight& w, const float* x, int mm, float* y, cudaStream_t s) {
@@ -249,20 +252,25 @@ cudaError_t launch_q5k_rows(const Weight& w, const float* x, int mm, float* y, c
 }  // namespace
 
 // y[m][w.rows] for Q6_K (native int8 activations already quantized into `a`, or fp32 x) and Q5_K (always fp32 x).
-// Activation rows go through in groups of up to eight (Q6_K) or four (Q5_K) per pass over the weight.
-int32_t launch_matvec_kq(const Weight& w, const float* x, ActQ8K a, int m, float* y, int act_mode, cudaStream_t s) {
+// Activation rows go through in groups of up to eight (Q6_K) or four (Q5_K) per pass over the weight. resid (native Q6_K
+// only; may be y itself): y = resid + W x.
+int32_t launch_matvec_kq(const Weight& w, const float* x, ActQ8K a, int m, float* y, int act_mode, cudaStream_t s, const float* resid) {
     if (m <= 0 || w.rows <= 0) return SKAINET_CUDA_OK;
+    if (resid && !(w.enc == SKAINET_ENC_Q6_K && act_mode == SKAINET_ACT_NATIVE)) {
+        set_error("matmul: the residual epilogue exists for native Q6_K only");
+        return SKAINET_CUDA_ERR_INVALID;
+    }
     if (w.enc == SKAINET_ENC_Q6_K && act_mode == SKAINET_ACT_NATIVE) {
         if (m >= Q6K_GEMM_MIN_ROWS) {
-            const int32_t st = launch_gemm_q6k(w, a, m, y, s);
+            const int32_t st = launch_gemm_q6k(w, a, m, y, resid, s);
             if (st != 1) return st;
         }
         for (int m0 = 0; m0 < m; m0 += 8) {
             const int mm = std::min(8, m - m0);
-            if (mm == 1) SK_CUDA(launch_q6k_rows<1>(w, a, m0, mm, y, s));
-            else if (mm == 2) SK_CUDA(launch_q6k_rows<2>(w, a, m0, mm, y, s));
-            else if (mm <= 4) SK_CUDA(launch_q6k_rows<4>(w, a, m0, mm, y, s));
-            else SK_CUDA(launch_q6k_rows<8>(w, a, m0, mm, y, s));
+            if (mm == 1) SK_CUDA(launch_q6k_rows<1>(w, a, m0, mm, y, resid, s));
+            else if (mm == 2) SK_CUDA(launch_q6k_rows<2>(w, a, m0, mm, y, resid, s));
+            else if (mm <= 4) SK_CUDA(launch_q6k_rows<4>(w, a, m0, mm, y, resid, s));
+            else SK_CUDA(launch_q6k_rows<8>(w, a, m0, mm, y, resid, s));
         }
         return SKAINET_CUDA_OK;
     }

@@ -122,6 +122,8 @@ int32_t launch_linear_q(const Weight& w, void* act, int rows, float* y, float* r
             : launch_gemm_mma(w, act_q8k_layout(act, rows, w.cols), rows, resid_inplace ? resid_inplace : y, resid_inplace, s);
         if (st != 1) return st;
     }
+    if (w.enc == SKAINET_ENC_Q6_K)            // a Q6_K tensor inside a K-quant model: its kernels add the residual themselves
+        return launch_matvec_kq(w, nullptr, act_q8k_layout(act, rows, w.cols), rows, resid_inplace ? resid_inplace : y, SKAINET_ACT_NATIVE, s, resid_inplace);
     float* out = resid_inplace ? tmp : y;
     SK_TRY(launch_matvec(w, nullptr, act, rows, out, SKAINET_ACT_NATIVE, s));
     if (resid_inplace) {
