@@ -13,6 +13,8 @@ Prints ONE JSON line (rank 0). Workloads (all inputs synthetic and seeded):
       GEMM, so a 4096-row prompt is out of reach for its side). --batch B decodes B sequences.
   decode_7b — benchmark config 4: 32 layers, d 4096, FFN 11008, 32 heads, vocab 32000; Q4_K linears,
       Q8_0 embedding/output; batch 1 behind a 512-token context.
+  decode_7b_mixed — decode_7b with attn_v and ffn_down of every second layer as Q6_K (the mix K-quant files carry);
+      one GPU.
   q4k_matvec — benchmark config 2 at M=1: W[11008,4096] and W[4096,11008]; metric = algorithmic HBM
       GB/s over a sweep of distinct weights larger than 2x L2.
   q8_0_matvec — benchmark config 1: Q8_0 W[4096,4096], same protocol.
@@ -64,7 +66,9 @@ MATVEC_WORKLOADS = {
     "q6k_matvec": ("Q6_K", [(11008, 4096), (4096, 11008)], 210, 256),
     "q5k_matvec": ("Q5_K", [(11008, 4096), (4096, 11008)], 176, 256),
 }
-DECODE_WORKLOADS = {"decode_70b": ("70b", 4096), "decode_7b": ("7b", 512)}
+DECODE_WORKLOADS = {"decode_70b": ("70b", 4096), "decode_7b": ("7b", 512), "decode_7b_mixed": ("7b", 512)}
+# a K-quant file's usual mix: attn_v and ffn_down of every second layer carried as Q6_K beside the Q4_K tensors
+MIXED_WORKLOADS = {"decode_7b_mixed"}
 # decode attention alone: (query heads, kv heads, head_dim); context from --context
 ATTN_WORKLOADS = {"attn_decode": (32, 8, 128)}
 # batched rows through the tensor-core tile kernel: the Q4_K sweep shapes with --batch activation rows (default 512)
@@ -180,7 +184,7 @@ def cpu_matvec_rate(workload: str, seconds: float) -> dict:
                       f"({'its 4-thread row pool' if use_ref else 'scalar'}; host has {os.cpu_count()} cores)", "seconds": dt}
 
 
-def cpu_decode_rate(model: str, ctx: int, budget_s: float) -> dict:
+def cpu_decode_rate(model: str, ctx: int, budget_s: float, mixed: bool = False) -> dict:
     """tokens/s of a decoder composed from the reference's C kernels: one layer (random valid packed
     weights of the model's shapes, context of `ctx` cached keys) and the output head are timed, the layer
     time is multiplied by the layer count. Activation quantization, RMSNorm, SDPA, SiLU, mul, add as the
@@ -193,6 +197,7 @@ def cpu_decode_rate(model: str, ctx: int, budget_s: float) -> dict:
     le, te = cfg.linear_enc, cfg.table_enc
     W = {"q": (H * D, d), "k": (HK * D, d), "v": (HK * D, d), "o": (d, H * D), "gate": (F, d), "up": (F, d), "down": (d, F)}
     packed = {k: random_blocks(rng, le, r, c) for k, (r, c) in W.items()}
+    packed6 = {k: random_blocks(rng, "Q6_K", *W[k]) for k in ("v", "down")} if mixed else {}
     vocab_sample = min(cfg.vocab, 16000)          # the head is timed on a slice of its rows and scaled
     head = random_blocks(rng, te, vocab_sample, d)
     K = rng.standard_normal((1, HK, ctx + 1, D)).astype(np.float16).astype(np.float32)
@@ -200,23 +205,26 @@ def cpu_decode_rate(model: str, ctx: int, budget_s: float) -> dict:
     x = rng.standard_normal(d).astype(np.float32)
     ones = np.ones(d, np.float32)
 
-    def mm(name, v):
+    def mm(name, v, q6=False):
         r, c = W[name]
+        if q6 and name in packed6:
+            return R.matmul("Q6_K", v, packed6[name], c, r, "rm", use_ref=use_ref)
         return R.matmul(le, v, packed[name], c, r, "rm", use_ref=use_ref)
 
-    def layer(x):
+    def layer(x, q6=False):
         xn = R.rms_norm(x, ones, cfg.rms_eps, use_ref=use_ref)
-        q = R.rope(mm("q", xn).reshape(H, D), H, D, ctx); k = R.rope(mm("k", xn).reshape(HK, D), HK, D, ctx); v = mm("v", xn)
+        q = R.rope(mm("q", xn).reshape(H, D), H, D, ctx); k = R.rope(mm("k", xn).reshape(HK, D), HK, D, ctx); v = mm("v", xn, q6)
         K[0, :, ctx] = R.round_f16(k); V[0, :, ctx] = R.round_f16(v.reshape(HK, D))
         a = R.sdpa(q.reshape(1, H, 1, D), K, V, 1.0 / np.sqrt(D), causal=True, use_ref=use_ref).reshape(-1)
         x = x + mm("o", a)
         xn = R.rms_norm(x, ones, cfg.rms_eps, use_ref=use_ref)
-        return x + mm("down", R.swiglu(mm("gate", xn), mm("up", xn)))
+        return x + mm("down", R.swiglu(mm("gate", xn), mm("up", xn)), q6)
 
     layer(x)                                        # warm-up
     t0 = time.perf_counter(); n_layer = 0
-    while n_layer < 1 or time.perf_counter() - t0 < budget_s * 0.8:
-        x = layer(x); x /= max(1.0, float(np.abs(x).max())); n_layer += 1
+    # mixed: layers with Q6_K attn_v / ffn_down and plain ones alternate, an even number of them is timed
+    while n_layer < 1 or (mixed and n_layer % 2 == 1) or time.perf_counter() - t0 < budget_s * 0.8:
+        x = layer(x, mixed and n_layer % 2 == 0); x /= max(1.0, float(np.abs(x).max())); n_layer += 1
     t_layer = (time.perf_counter() - t0) / n_layer
     t0 = time.perf_counter(); n_head = 0
     while n_head < 1 or time.perf_counter() - t0 < budget_s * 0.2:
@@ -266,7 +274,7 @@ def run_reference(args) -> None:
             r = cpu_request_rate(args.workload, budget); unit = "tokens/s"; metric = "request_generated_tokens_per_s"
         else:
             model, ctx = DECODE_WORKLOADS[args.workload]
-            r = cpu_decode_rate(model, ctx, budget); unit = "tokens/s"; metric = "decode_tokens_per_s"
+            r = cpu_decode_rate(model, ctx, budget, mixed=args.workload in MIXED_WORKLOADS); unit = "tokens/s"; metric = "decode_tokens_per_s"
         if i >= args.warmup:
             vals.append(r["value"]); times.append(r["seconds"] * 1e3)
     v = float(np.mean(vals))
@@ -289,6 +297,8 @@ def dtype_of(workload: str) -> str:
         return "f16 K/V, f32 q split in two f16 terms, f32 accumulate"
     if workload == "q8_0_matvec":
         return "int8 x int8 (two-term activation) -> int32, f32 accumulate"
+    if workload in MIXED_WORKLOADS:
+        return "int8 x int4 / int6 -> int32, f32 accumulate (attention and norms f32, KV f16)"
     if workload == "q6k_matvec":
         return "int8 x int6 -> int32, f32 accumulate"
     if workload == "q5k_matvec":
@@ -326,6 +336,9 @@ def workload_config(args, world: int, extra: dict | None = None) -> dict:
              "kv_heads": cfg.n_kv_heads, "vocab": cfg.vocab, "linear": cfg.linear_enc, "tables": cfg.table_enc, "batch": args.batch,
              "context": ctx, "context_fill": "seeded noise K/V (no prompt pass)", "parallelism": f"tp{world}",
              "l2": "weights per step far larger than L2", "weights": "N(0,0.02) packed on device, seeded"}
+        if args.workload in MIXED_WORKLOADS:
+            c["linear"] = "Q4_K; attn_v and ffn_down of every second layer Q6_K"
+            c["weights"] += "; the Q6_K tensors: random valid blocks (random codes and scales, f16 d = 6e-5), seeded, uploaded"
     if extra:
         c.update(extra)
     return c
@@ -980,8 +993,11 @@ def run_decode(args) -> None:
     import torch
     import torch.distributed as dist
     from skainet_b200 import _lib as L, device
-    from skainet_b200.llama import Llama, W_HEAD, W_O, W_DOWN, W_QKV, W_GATE_UP
+    from skainet_b200.llama import Llama, W_HEAD, W_O, W_DOWN, W_QKV, W_GATE_UP, W_Q, W_K, W_V
     rank, world, local = dist_env()
+    mixed = args.workload in MIXED_WORKLOADS
+    if mixed and world > 1:
+        raise SystemExit(f"{args.workload} is a one-GPU workload")
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     torch.cuda.set_device(local); device.set_device(local)
@@ -990,6 +1006,14 @@ def run_decode(args) -> None:
     cfg = model_config(model_name, max_seq=ctx + 2048, max_batch=batch, tp_rank=rank, tp_world=world)
     m = Llama(cfg)
     m.synth(seed=100, std=0.02)
+    mixed_layers = list(range(0, cfg.n_layers, 2)) if mixed else []
+    if mixed:
+        hrng = np.random.default_rng(17)
+        for l in mixed_layers:
+            for which, rows, cols in ((W_V, cfg.n_kv_heads * cfg.head_dim, cfg.d_model), (W_DOWN, cfg.d_model, cfg.ffn_dim)):
+                packed = random_blocks(hrng, "Q6_K", rows, cols)
+                packed.reshape(-1, 210)[:, 208:210] = np.array([6e-5], np.float16).view(np.uint8)
+                m.set_weight(l, which, device.Weight.upload(packed, "Q6_K", rows, cols))
     m.finalize()
     if world > 1:
         ids = [Llama.tp_unique_id() if rank == 0 else None]
@@ -1056,7 +1080,8 @@ def run_decode(args) -> None:
     # the matvec kernel alone over this rank's own weights (every layer's four linears + the head)
     ws = []
     for l in range(cfg.n_layers):
-        ws += [m.weight(l, W_QKV), m.weight(l, W_O), m.weight(l, W_GATE_UP), m.weight(l, W_DOWN)]
+        qkv = [m.weight(l, W_Q), m.weight(l, W_K), m.weight(l, W_V)] if l in mixed_layers else [m.weight(l, W_QKV)]     # a Q6_K attn_v is not merged
+        ws += qkv + [m.weight(l, W_O), m.weight(l, W_GATE_UP), m.weight(l, W_DOWN)]
     ws.append(m.weight(0, W_HEAD))
     mv_bytes = sum(algorithmic_bytes(*BLOCK[w.encoding], w.rows, w.cols) for w in ws)
     stream = torch.cuda.Stream()
@@ -1089,7 +1114,7 @@ def run_decode(args) -> None:
                          "traffic": launch_bytes * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE,
                          "traffic_source": "dram read+write bytes of one q4k_matvec_ring_kernel launch from the ncu captures summarised in "
                                            "profiles/ (1.001 x the weight bytes at 25 MB and at 264 MB), scaled to this run's mean weight size",
-                         "peak_kind": peak_kind, "kernel": "q4k_matvec_ring_kernel",
+                         "peak_kind": peak_kind, "kernel": "q4k_matvec_ring_kernel" + (" (Q6_K tensors: q6k_rows_kernel)" if mixed else ""),
                          "note": "per GPU. achieved / frac: bytes one decode step must read (weights once + visible K/V) / measured step time. "
                                  "kernel_*: the matvec path alone (quantizer + matvec) swept over this rank's own weights in a CUDA graph",
                          "step_bytes_per_gpu": bytes_step, "kernel_achieved": achieved, "kernel_frac": achieved / peak,
@@ -1109,7 +1134,7 @@ def run_decode(args) -> None:
         if matvec_summary is not None:
             line["matvec"] = matvec_summary
         if world == 1 and not args.skip_cpu:
-            cpu = cpu_decode_rate(model_name, ctx, 20.0)
+            cpu = cpu_decode_rate(model_name, ctx, 20.0, mixed=mixed)
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line), flush=True)
     m.free()
