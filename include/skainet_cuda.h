@@ -58,10 +58,11 @@ extern "C" {
 #define SKAINET_ORDER_INPUT_MAJOR 1   /* BLOCKED_INPUT_MAJOR ("feed order"): (b * out + o)             */
 
 /* How the activation enters the integer dot.
- * NATIVE follows the reference kernel of the weight's format: Q4_K/Q5_K/Q6_K quantize each
- * 256-element activation block to int8 with one scale (native/src/q4k_matmul.c:74-92); Q8_0 keeps
- * fp32 activations (native/src/q8_0_matmul.c:61-67), which this library carries as an exact
- * two-term int8 split (hi*128+lo, 15 bits) per 32-element block.
+ * NATIVE follows the reference kernel of the weight's format: Q4_K / Q6_K quantize each
+ * 256-element activation block to int8 with one scale (native/src/q4k_matmul.c:74-92,
+ * native/src/q6k_matmul.c:53-67); Q8_0 keeps fp32 activations (native/src/q8_0_matmul.c:61-67), which this
+ * library carries as an exact two-term int8 split (hi*128+lo, 15 bits) per 32-element block; Q5_K keeps
+ * fp32 activations as they are (native/src/q5k_matmul.c:93-215).
  * F32 is the exact-float arithmetic of the scalar Kotlin kernels
  * (skainet-backends/skainet-backend-cpu/src/commonMain/kotlin/sk/ainet/exec/kernel/ScalarQ4_KMatmulKernel.kt:15-82). */
 #define SKAINET_ACT_NATIVE 0
@@ -176,8 +177,10 @@ SKAINET_CUDA_API int32_t skainet_cuda_weight_dequant(skainet_weight_t w, float* 
 
 /* y[m, rows] = x[m, cols] . W^T on the device. Q4_K / Q8_0: the dequant-fused matvec for m = 1 (and Q4_K up to
  * 2 rows), tensor-core tile kernels above that (mma.sync; tcgen05 with TMEM accumulators for Q4_K from 288 rows).
- * Q6_K (native mode = int8 activations per 256 like skainet_q6k_matmul_rm, native/src/q6k_matmul.c:344-357)
- * and Q5_K (fp32 activations in both modes, native/src/q5k_matmul.c) run one warp per output row.
+ * Q6_K (native mode = int8 activations per 256 like skainet_q6k_matmul_rm, native/src/q6k_matmul.c:344-357): one warp
+ * per output row and up to eight activation rows per pass over the weight, an mma.sync tile kernel from nine rows,
+ * every row bit-identical to the single-row result. Q5_K (fp32 activations in both modes, native/src/q5k_matmul.c):
+ * one warp per output row, up to four activation rows per pass.
  * Counterpart of PackedViewMatmulKernel.runWith
  * (skainet-backends/skainet-backend-api/src/commonMain/kotlin/sk/ainet/backend/api/kernel/PackedViewMatmulKernel.kt:69-107),
  * which issues m matvec calls. act_mode: SKAINET_ACT_*. */
