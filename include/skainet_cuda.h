@@ -206,12 +206,13 @@ SKAINET_CUDA_API int32_t skainet_cuda_matvec_fused_dev(skainet_weight_t w, const
  * matmul + split") or gate and up of a fused_swiglu_ffn node. The parts stay valid and owned by the caller. */
 SKAINET_CUDA_API int32_t skainet_cuda_weight_concat_rows(skainet_weight_t a, skainet_weight_t b, skainet_weight_t c, skainet_weight_t* out);
 /* fused_qkv_proj (LLMFusionPass.kt:117, LLMFusedOpHandlers.kt:143-196): q[m, q_rows], k[m, k_rows], v[m, v_rows] = x[m, cols] . W^T
- * for the merged weight's three row ranges, one pass over the activation. */
+ * for the merged weight's three row ranges, one pass over the activation. Encodings: Q4_K, Q8_0, Q6_K. */
 SKAINET_CUDA_API int32_t skainet_cuda_fused_qkv_proj_dev(skainet_weight_t w_qkv, int32_t q_rows, int32_t k_rows, int32_t v_rows,
     const float* x_dev, const float* gamma_dev, float eps, int32_t m, float* q_dev, float* k_dev, float* v_dev, skainet_stream_t stream);
 /* fused_swiglu_ffn (LLMFusionPass.kt:86, LLMFusedOpHandlers.kt:86-127): out[m, d] = (resid +) W_down . (silu(W_gate x) * (W_up x)),
  * gate and up as one merged weight (gate rows first); the intermediate never leaves the device and is quantized for the
- * down projection inside the SwiGLU kernel. resid_dev may be NULL or equal out_dev. */
+ * down projection inside the SwiGLU kernel. resid_dev may be NULL or equal out_dev. Encodings: Q4_K, Q8_0, Q6_K; the
+ * down projection may be Q6_K behind Q4_K gate and up (the mix K-quant files carry), Q8_0 goes with Q8_0 only. */
 SKAINET_CUDA_API int32_t skainet_cuda_fused_swiglu_ffn_dev(skainet_weight_t w_gate_up, skainet_weight_t w_down, const float* x_dev,
     const float* gamma_dev, float eps, int32_t m, const float* resid_dev, float* out_dev, skainet_stream_t stream);
 

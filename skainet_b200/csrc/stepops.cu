@@ -213,7 +213,7 @@ int32_t skainet_cuda_fused_qkv_proj_dev(skainet_weight_t wqkv, int32_t q_rows, i
                                         skainet_stream_t stream) {
     Weight* w = weight_from_handle(wqkv);
     if (!w) return SKAINET_CUDA_ERR_HANDLE;
-    SK_REQUIRE(w->enc == SKAINET_ENC_Q4_K || w->enc == SKAINET_ENC_Q8_0, "fused_qkv_proj: encoding %d not supported", w->enc);
+    SK_REQUIRE(w->enc == SKAINET_ENC_Q4_K || w->enc == SKAINET_ENC_Q8_0 || w->enc == SKAINET_ENC_Q6_K, "fused_qkv_proj: encoding %d not supported", w->enc);
     SK_REQUIRE(q_rows > 0 && k_rows > 0 && v_rows > 0 && q_rows + k_rows + v_rows == w->rows,
                "fused_qkv_proj: %d + %d + %d output rows, the merged weight has %d", q_rows, k_rows, v_rows, w->rows);
     SK_REQUIRE(m >= 0, "fused_qkv_proj: negative row count %d", m);
@@ -251,7 +251,10 @@ int32_t skainet_cuda_fused_swiglu_ffn_dev(skainet_weight_t w_gate_up, skainet_we
     Weight* wd = wgu ? weight_from_handle(w_down) : nullptr;
     if (!wgu || !wd) return SKAINET_CUDA_ERR_HANDLE;
     for (const Weight* w : {wgu, wd})
-        SK_REQUIRE(w->enc == SKAINET_ENC_Q4_K || w->enc == SKAINET_ENC_Q8_0, "fused_swiglu_ffn: encoding %d not supported", w->enc);
+        SK_REQUIRE(w->enc == SKAINET_ENC_Q4_K || w->enc == SKAINET_ENC_Q8_0 || w->enc == SKAINET_ENC_Q6_K, "fused_swiglu_ffn: encoding %d not supported", w->enc);
+    // gate|up and down may differ in encoding (a Q6_K ffn_down behind Q4_K gate and up, as K-quant files carry them), as long
+    // as both take the same activation form
+    SK_REQUIRE((wgu->enc == SKAINET_ENC_Q8_0) == (wd->enc == SKAINET_ENC_Q8_0), "fused_swiglu_ffn: Q8_0 and K-quant weights cannot be mixed");
     SK_REQUIRE(wgu->rows % 2 == 0 && wgu->rows / 2 == wd->cols, "fused_swiglu_ffn: gate|up has %d rows, down takes %d inputs", wgu->rows, wd->cols);
     SK_REQUIRE(m >= 0, "fused_swiglu_ffn: negative row count %d", m);
     if (m == 0) return SKAINET_CUDA_OK;

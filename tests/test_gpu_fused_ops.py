@@ -84,3 +84,65 @@ def test_fused_swiglu_ffn_equals_the_reference_decomposition(gpu, oracle, enc, d
         np.testing.assert_array_equal(dr.download(np.float32, m * d).reshape(m, d), got)
     for w in (wg, wu, wd, wgu):
         w.free()
+
+
+def _q6k(oracle, rows, cols, seed, d_scale=6e-5):
+    blk = oracle.random_kquant_blocks("Q6_K", rows, cols, seed=seed).reshape(-1, 210)
+    rng = np.random.default_rng(seed + 1)
+    blk[:, 208:210] = np.abs(d_scale * (1 + 0.3 * rng.standard_normal(blk.shape[0]))).astype(np.float16).view(np.uint8).reshape(-1, 2)
+    return blk.reshape(-1)
+
+
+@pytest.mark.parametrize("d,f,m,resid", [(1024, 2816, 1, True), (512, 1024, 12, True), (1024, 2048, 5, False), (512, 1280, 70, True)])
+def test_fused_swiglu_ffn_with_a_q6k_down_projection(gpu, oracle, d, f, m, resid):
+    """ffn_down as Q6_K behind Q4_K gate and up (the mix K-quant files carry): the down projection runs on the Q6_K row
+    kernel (up to eight rows) or its tensor-core tile kernel, both with the residual in their epilogue; reference =
+    the same decomposition with native/src/q6k_matmul.c for the last product."""
+    use_ref = oracle.ref() is not None
+    (pg, pu), (wg, wu) = _weights(gpu, oracle, "Q4_K", [(f, d), (f, d)], seed=f + m)
+    pd = _q6k(oracle, d, f, seed=3 * f + m)
+    wd = gpu.Weight.upload(pd, "Q6_K", d, f)
+    wgu = gpu.concat_rows(wg, wu)
+    rng = np.random.default_rng(f)
+    x = (2 * rng.standard_normal((m, d))).astype(np.float32)
+    gamma = (1 + 0.1 * rng.standard_normal(d)).astype(np.float32)
+    r = rng.standard_normal((m, d)).astype(np.float32)
+    dx, dg, dr = gpu.DeviceBuffer.from_host(x), gpu.DeviceBuffer.from_host(gamma), gpu.DeviceBuffer.from_host(r)
+    dout = gpu.DeviceBuffer(m * d * 4)
+    gpu.fused_swiglu_ffn(wgu, wd, dx.ptr, m, dout.ptr, resid_ptr=dr.ptr if resid else 0, gamma_ptr=dg.ptr, eps=1e-5)
+    got = dout.download(np.float32, m * d).reshape(m, d)
+    xin = oracle.rms_norm(x, gamma, 1e-5, use_ref=use_ref)
+    gate = oracle.matmul("Q4_K", xin, pg, d, f, "rm", use_ref=use_ref).reshape(m, f)
+    up = oracle.matmul("Q4_K", xin, pu, d, f, "rm", use_ref=use_ref).reshape(m, f)
+    ref = oracle.matmul("Q6_K", oracle.swiglu(gate, up), pd, f, d, "rm", use_ref=use_ref).reshape(m, d)
+    err = np.sqrt(np.mean((got - (r if resid else 0) - ref) ** 2) / np.mean(ref ** 2))
+    assert err < 2e-3, err
+    if resid:                              # in place: out == resid
+        gpu.fused_swiglu_ffn(wgu, wd, dx.ptr, m, dr.ptr, resid_ptr=dr.ptr, gamma_ptr=dg.ptr, eps=1e-5)
+        np.testing.assert_array_equal(dr.download(np.float32, m * d).reshape(m, d), got)
+    with pytest.raises(ValueError):        # the two-term Q8_0 activation and the K-quant one cannot share a call
+        w8 = gpu.Weight.upload(oracle.quantize_q8_0(np.zeros((d, f), np.float32)), "Q8_0", d, f)
+        try:
+            gpu.fused_swiglu_ffn(wgu, w8, dx.ptr, m, dout.ptr)
+        finally:
+            w8.free()
+    for w in (wg, wu, wd, wgu):
+        w.free()
+
+
+@pytest.mark.parametrize("m", [1, 10])
+def test_fused_qkv_proj_over_q6k_weights(gpu, oracle, m):
+    use_ref = oracle.ref() is not None
+    d, qr, kr = 1024, 512, 128
+    packed = [_q6k(oracle, r, d, seed=9 * r + m) for r in (qr, kr, kr)]
+    ws = [gpu.Weight.upload(p, "Q6_K", r, d) for p, r in zip(packed, (qr, kr, kr))]
+    merged = gpu.concat_rows(*ws)
+    np.testing.assert_array_equal(merged.export(), np.concatenate(packed))
+    x = (2 * np.random.default_rng(m).standard_normal((m, d))).astype(np.float32)
+    dx = gpu.DeviceBuffer.from_host(x)
+    bufs = [gpu.DeviceBuffer(m * r * 4) for r in (qr, kr, kr)]
+    gpu.fused_qkv_proj(merged, qr, kr, kr, dx.ptr, m, *(b.ptr for b in bufs))
+    for p, r, b in zip(packed, (qr, kr, kr), bufs):
+        rel_err_ok(b.download(np.float32, m * r).reshape(m, r), oracle.matmul("Q6_K", x, p, d, r, "rm", use_ref=use_ref).reshape(m, r), 1e-5)
+    for w in ws + [merged]:
+        w.free()
