@@ -114,6 +114,26 @@ SKAINET_CUDA_API int32_t skainet_cuda_q8_0_matmul_rm(const float* input, int32_t
     const uint8_t* weight, int32_t weight_byte_offset, int32_t input_dim, int32_t output_dim,
     float* output, int32_t output_offset);
 
+/* Q6_K matvec (int8 activations per 256, integer group dots), feed order and row-major. Replace skainet_q6k_matmul and
+ * skainet_q6k_matmul_rm, skainet_kernels.h:135-166 (SPI Q6KMatmulKernel.kt, KernelProvider.kt:86). Contract as the Q4_K
+ * twins: input_dim % 256 != 0 -> ERR_INVALID; input_dim <= 0 or output_dim <= 0 -> OK with the output untouched
+ * (native/src/q6k_matmul.c:284). */
+SKAINET_CUDA_API int32_t skainet_cuda_q6k_matmul(const float* input, int32_t input_offset,
+    const uint8_t* weight, int32_t weight_byte_offset, int32_t input_dim, int32_t output_dim,
+    float* output, int32_t output_offset);
+SKAINET_CUDA_API int32_t skainet_cuda_q6k_matmul_rm(const float* input, int32_t input_offset,
+    const uint8_t* weight, int32_t weight_byte_offset, int32_t input_dim, int32_t output_dim,
+    float* output, int32_t output_offset);
+/* Q5_K matvec (fp32 activations), feed order and row-major. Replace skainet_q5k_matmul and skainet_q5k_matmul_rm,
+ * skainet_kernels.h:105-114,251-260 (SPI Q5KMatmulKernel.kt, KernelProvider.kt:92); same contract
+ * (native/src/q5k_matmul.c:264). */
+SKAINET_CUDA_API int32_t skainet_cuda_q5k_matmul(const float* input, int32_t input_offset,
+    const uint8_t* weight, int32_t weight_byte_offset, int32_t input_dim, int32_t output_dim,
+    float* output, int32_t output_offset);
+SKAINET_CUDA_API int32_t skainet_cuda_q5k_matmul_rm(const float* input, int32_t input_offset,
+    const uint8_t* weight, int32_t weight_byte_offset, int32_t input_dim, int32_t output_dim,
+    float* output, int32_t output_offset);
+
 /* out[r,c] = in[r,c] / sqrt(mean(in[r,:]^2) + eps) * gamma[c]; gamma may be NULL.
  * Replaces skainet_f32_rms_norm, skainet_kernels.h:574-576 (SPI Fp32FusedKernels.kt:46-52). */
 SKAINET_CUDA_API int32_t skainet_cuda_f32_rms_norm(const float* in, const float* gamma, float* out,

@@ -44,6 +44,10 @@ SIGNATURES = {
     "skainet_cuda_q4k_matmul_rm": _MATVEC,
     "skainet_cuda_q8_0_matmul": _MATVEC,
     "skainet_cuda_q8_0_matmul_rm": _MATVEC,
+    "skainet_cuda_q6k_matmul": _MATVEC,
+    "skainet_cuda_q6k_matmul_rm": _MATVEC,
+    "skainet_cuda_q5k_matmul": _MATVEC,
+    "skainet_cuda_q5k_matmul_rm": _MATVEC,
     "skainet_cuda_f32_rms_norm": [f32p, f32p, f32p, i32, i32, f32],
     "skainet_cuda_f32_sdpa": [f32p, f32p, f32p, f32p] + [i32] * 6 + [f32] + [i32] * 3 + [i32p, f32p] + [i32] * 4,
     "skainet_cuda_f32_unary": [i32, f32p, f32p, i32],

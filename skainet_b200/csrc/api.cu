@@ -658,11 +658,12 @@ int32_t skainet_cuda_smoke_double(const float* input, float* output, int32_t len
 // callers that care about speed upload once and use skainet_cuda_matmul_dev.
 static int32_t host_matvec(int enc, int order, const float* input, int32_t input_offset, const uint8_t* weight,
                            int32_t weight_byte_offset, int32_t input_dim, int32_t output_dim, float* output, int32_t output_offset) {
-    const char* who = enc == SKAINET_ENC_Q4_K ? "q4k_matmul" : "q8_0_matmul";
+    const char* who = enc == SKAINET_ENC_Q4_K ? "q4k_matmul" : enc == SKAINET_ENC_Q8_0 ? "q8_0_matmul" : enc == SKAINET_ENC_Q6_K ? "q6k_matmul" : "q5k_matmul";
     SK_REQUIRE(input_dim < 0 || input_dim % block_elems(enc) == 0, "%s: inputDim must be a multiple of %d; got %d", who, block_elems(enc), input_dim);
     if (output_dim <= 0) return SKAINET_CUDA_OK;
     if (input_dim <= 0) {
-        // Q8_0 zeroes the output (q8_0_matmul.c:175-179); native Q4_K leaves it untouched (q4k_matmul.c:326).
+        // Q8_0 zeroes the output (q8_0_matmul.c:175-179); the native K-quant kernels leave it untouched (q4k_matmul.c:326,
+        // q6k_matmul.c:284, q5k_matmul.c:264).
         if (enc == SKAINET_ENC_Q8_0) { SK_REQUIRE(output, "%s: null output", who); memset(output + output_offset, 0, sizeof(float) * (size_t) output_dim); }
         return SKAINET_CUDA_OK;
     }
@@ -696,6 +697,18 @@ int32_t skainet_cuda_q8_0_matmul(const float* in, int32_t io, const uint8_t* w, 
 }
 int32_t skainet_cuda_q8_0_matmul_rm(const float* in, int32_t io, const uint8_t* w, int32_t wo, int32_t k, int32_t n, float* out, int32_t oo) {
     return host_matvec(SKAINET_ENC_Q8_0, SKAINET_ORDER_ROW_MAJOR, in, io, w, wo, k, n, out, oo);
+}
+int32_t skainet_cuda_q6k_matmul(const float* in, int32_t io, const uint8_t* w, int32_t wo, int32_t k, int32_t n, float* out, int32_t oo) {
+    return host_matvec(SKAINET_ENC_Q6_K, SKAINET_ORDER_INPUT_MAJOR, in, io, w, wo, k, n, out, oo);
+}
+int32_t skainet_cuda_q6k_matmul_rm(const float* in, int32_t io, const uint8_t* w, int32_t wo, int32_t k, int32_t n, float* out, int32_t oo) {
+    return host_matvec(SKAINET_ENC_Q6_K, SKAINET_ORDER_ROW_MAJOR, in, io, w, wo, k, n, out, oo);
+}
+int32_t skainet_cuda_q5k_matmul(const float* in, int32_t io, const uint8_t* w, int32_t wo, int32_t k, int32_t n, float* out, int32_t oo) {
+    return host_matvec(SKAINET_ENC_Q5_K, SKAINET_ORDER_INPUT_MAJOR, in, io, w, wo, k, n, out, oo);
+}
+int32_t skainet_cuda_q5k_matmul_rm(const float* in, int32_t io, const uint8_t* w, int32_t wo, int32_t k, int32_t n, float* out, int32_t oo) {
+    return host_matvec(SKAINET_ENC_Q5_K, SKAINET_ORDER_ROW_MAJOR, in, io, w, wo, k, n, out, oo);
 }
 
 int32_t skainet_cuda_f32_rms_norm(const float* in, const float* gamma, float* out, int32_t rows, int32_t cols, float eps) {

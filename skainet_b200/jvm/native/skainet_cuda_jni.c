@@ -71,6 +71,10 @@ SKAINET_JNI_MATMUL(q4kMatmul, skainet_cuda_q4k_matmul)
 SKAINET_JNI_MATMUL(q4kMatmulRm, skainet_cuda_q4k_matmul_rm)
 SKAINET_JNI_MATMUL(q80Matmul, skainet_cuda_q8_0_matmul)
 SKAINET_JNI_MATMUL(q80MatmulRm, skainet_cuda_q8_0_matmul_rm)
+SKAINET_JNI_MATMUL(q6kMatmul, skainet_cuda_q6k_matmul)
+SKAINET_JNI_MATMUL(q6kMatmulRm, skainet_cuda_q6k_matmul_rm)
+SKAINET_JNI_MATMUL(q5kMatmul, skainet_cuda_q5k_matmul)
+SKAINET_JNI_MATMUL(q5kMatmulRm, skainet_cuda_q5k_matmul_rm)
 
 /* ---- resident weights: upload once, multiply many times ---- */
 /* weight as a heap ByteArray; order 0 = row-major (GGUF file order), 1 = input-major ("feed order"). Returns the handle, or 0. */

@@ -5,6 +5,8 @@ import sk.ainet.backend.api.kernel.Fp32MatmulKernel
 import sk.ainet.backend.api.kernel.Fp32NormKernel
 import sk.ainet.backend.api.kernel.KernelProvider
 import sk.ainet.backend.api.kernel.Q4KMatmulKernel
+import sk.ainet.backend.api.kernel.Q5KMatmulKernel
+import sk.ainet.backend.api.kernel.Q6KMatmulKernel
 import sk.ainet.backend.api.kernel.Q8_0MatmulKernel
 
 /**
@@ -46,6 +48,10 @@ public object CudaKernelProvider : KernelProvider {
 
     override fun matmulQ8_0(): Q8_0MatmulKernel? = if (available) CudaQ80Matmul else null
 
+    override fun matmulQ6K(): Q6KMatmulKernel? = if (available) CudaQ6KMatmul else null
+
+    override fun matmulQ5K(): Q5KMatmulKernel? = if (available) CudaQ5KMatmul else null
+
     override fun normFp32(): Fp32NormKernel? = if (available) CudaNorm else null
 
     override fun attentionFp32(): Fp32AttentionKernel? = if (available) CudaAttention else null
@@ -66,6 +72,24 @@ public object CudaKernelProvider : KernelProvider {
             inputDim: Int, outputDim: Int,
             output: FloatArray, outputOffset: Int,
         ): Unit = CudaKernels.check(CudaKernels.q80Matmul(input, inputOffset, weight, weightByteOffset, inputDim, outputDim, output, outputOffset))
+    }
+
+    private object CudaQ6KMatmul : Q6KMatmulKernel {
+        override fun matmul(
+            input: FloatArray, inputOffset: Int,
+            weight: ByteArray, weightByteOffset: Int,
+            inputDim: Int, outputDim: Int,
+            output: FloatArray, outputOffset: Int,
+        ): Unit = CudaKernels.check(CudaKernels.q6kMatmul(input, inputOffset, weight, weightByteOffset, inputDim, outputDim, output, outputOffset))
+    }
+
+    private object CudaQ5KMatmul : Q5KMatmulKernel {
+        override fun matmul(
+            input: FloatArray, inputOffset: Int,
+            weight: ByteArray, weightByteOffset: Int,
+            inputDim: Int, outputDim: Int,
+            output: FloatArray, outputOffset: Int,
+        ): Unit = CudaKernels.check(CudaKernels.q5kMatmul(input, inputOffset, weight, weightByteOffset, inputDim, outputDim, output, outputOffset))
     }
 
     private object CudaNorm : Fp32NormKernel {

@@ -33,6 +33,10 @@ public object CudaKernels {
     public external fun q4kMatmulRm(input: FloatArray, inputOffset: Int, weight: ByteArray, weightByteOffset: Int, inputDim: Int, outputDim: Int, output: FloatArray, outputOffset: Int): Int
     public external fun q80Matmul(input: FloatArray, inputOffset: Int, weight: ByteArray, weightByteOffset: Int, inputDim: Int, outputDim: Int, output: FloatArray, outputOffset: Int): Int
     public external fun q80MatmulRm(input: FloatArray, inputOffset: Int, weight: ByteArray, weightByteOffset: Int, inputDim: Int, outputDim: Int, output: FloatArray, outputOffset: Int): Int
+    public external fun q6kMatmul(input: FloatArray, inputOffset: Int, weight: ByteArray, weightByteOffset: Int, inputDim: Int, outputDim: Int, output: FloatArray, outputOffset: Int): Int
+    public external fun q6kMatmulRm(input: FloatArray, inputOffset: Int, weight: ByteArray, weightByteOffset: Int, inputDim: Int, outputDim: Int, output: FloatArray, outputOffset: Int): Int
+    public external fun q5kMatmul(input: FloatArray, inputOffset: Int, weight: ByteArray, weightByteOffset: Int, inputDim: Int, outputDim: Int, output: FloatArray, outputOffset: Int): Int
+    public external fun q5kMatmulRm(input: FloatArray, inputOffset: Int, weight: ByteArray, weightByteOffset: Int, inputDim: Int, outputDim: Int, output: FloatArray, outputOffset: Int): Int
 
     // resident weights: upload once (handle, or 0 on failure), multiply many times
     public external fun uploadWeight(weight: ByteArray, byteOffset: Int, nbytes: Long, encoding: Int, rows: Int, cols: Int, order: Int): Long

@@ -75,6 +75,17 @@ class CudaQ8_0MatmulKernel(_PackedMatmulKernel):
     _enc, _entry = "Q8_0", "skainet_cuda_q8_0_matmul"
 
 
+class CudaQ6KMatmulKernel(_PackedMatmulKernel):
+    """Q6_K matvec on the GPU (SPI Q6KMatmulKernel.kt; replaces the native kernel behind skainet_q6k_matmul / _rm,
+    skainet-backends/skainet-backend-native-cpu/native/src/q6k_matmul.c:272-357)."""
+    _enc, _entry = "Q6_K", "skainet_cuda_q6k_matmul"
+
+
+class CudaQ5KMatmulKernel(_PackedMatmulKernel):
+    """Q5_K matvec on the GPU (SPI Q5KMatmulKernel.kt; skainet_q5k_matmul / _rm, native/src/q5k_matmul.c)."""
+    _enc, _entry = "Q5_K", "skainet_cuda_q5k_matmul"
+
+
 class CudaFp32NormKernel:
     """``rmsNorm(input, inputOffset, gamma, out, outOffset, rows, cols, eps)`` — Fp32FusedKernels.kt:46-52."""
 
@@ -149,6 +160,18 @@ class CudaKernelProvider:
     def matmulQ8_0(self) -> Optional[CudaQ8_0MatmulKernel]:
         return CudaQ8_0MatmulKernel() if self.isAvailable() else None
 
+    def matmulQ6K(self) -> Optional[CudaQ6KMatmulKernel]:
+        return CudaQ6KMatmulKernel() if self.isAvailable() else None
+
+    def matmulQ5K(self) -> Optional[CudaQ5KMatmulKernel]:
+        return CudaQ5KMatmulKernel() if self.isAvailable() else None
+
+    def matmulQ6KRowMajor(self) -> Optional[CudaQ6KMatmulKernel]:
+        return CudaQ6KMatmulKernel(row_major=True) if self.isAvailable() else None
+
+    def matmulQ5KRowMajor(self) -> Optional[CudaQ5KMatmulKernel]:
+        return CudaQ5KMatmulKernel(row_major=True) if self.isAvailable() else None
+
     def matmulQ4KRowMajor(self) -> Optional[CudaQ4KMatmulKernel]:
         return CudaQ4KMatmulKernel(row_major=True) if self.isAvailable() else None
 
@@ -177,4 +200,4 @@ class CudaKernelProvider:
             return False
         if len(keys) != 2 or keys[0] != "Float32" or opName != "matmul":
             return False
-        return {"Q4_K": self.matmulQ4K, "Q8_0": self.matmulQ8_0}.get(keys[1], lambda: None)() is not None
+        return {"Q4_K": self.matmulQ4K, "Q8_0": self.matmulQ8_0, "Q6_K": self.matmulQ6K, "Q5_K": self.matmulQ5K}.get(keys[1], lambda: None)() is not None

@@ -20,7 +20,8 @@ def declared_symbols():
 
 def test_header_declares_the_drop_in_twins():
     names = declared_symbols()
-    for twin in ("smoke_double", "q4k_matmul", "q4k_matmul_rm", "q8_0_matmul", "q8_0_matmul_rm", "f32_rms_norm", "f32_sdpa"):
+    for twin in ("smoke_double", "q4k_matmul", "q4k_matmul_rm", "q8_0_matmul", "q8_0_matmul_rm", "q6k_matmul", "q6k_matmul_rm", "q5k_matmul", "q5k_matmul_rm",
+                 "f32_rms_norm", "f32_sdpa"):
         assert "skainet_cuda_" + twin in names
 
 
@@ -36,7 +37,8 @@ def test_python_binding_covers_every_declared_symbol():
 
 def test_every_declaration_cites_what_it_replaces():
     text = open(os.path.join(ROOT, "include", "skainet_cuda.h")).read()
-    for twin in ("smoke_double", "q4k_matmul", "q4k_matmul_rm", "q8_0_matmul", "q8_0_matmul_rm", "f32_rms_norm", "f32_sdpa"):
+    for twin in ("smoke_double", "q4k_matmul", "q4k_matmul_rm", "q8_0_matmul", "q8_0_matmul_rm", "q6k_matmul", "q6k_matmul_rm", "q5k_matmul", "q5k_matmul_rm",
+                 "f32_rms_norm", "f32_sdpa"):
         i = text.index("skainet_cuda_" + twin + "(")
         assert "skainet_kernels.h:" in text[max(0, i - 900):i], twin
 

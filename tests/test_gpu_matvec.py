@@ -73,6 +73,34 @@ def test_host_twins_match_reference_c_outputs(gpu, oracle, tag):
         rel_err_ok(out[3:], VEC[tag + ("_y_rm" if row_major else "_y_feed")])
 
 
+@pytest.mark.parametrize("enc,n,k", [("Q6_K", 37, 1024), ("Q6_K", 130, 2816), ("Q5_K", 37, 1024), ("Q5_K", 130, 2816)])
+def test_k_quant_host_twins_match_the_reference_c(gpu, oracle, enc, n, k):
+    """skainet_cuda_q6k_matmul / _rm and skainet_cuda_q5k_matmul / _rm through the provider's Q6_K / Q5_K slots
+    (KernelProvider.kt:86,92) in both weight orders, offsets mid-array, against the reference's own C kernels."""
+    from skainet_b200.provider import CudaKernelProvider
+    p = CudaKernelProvider()
+    assert p.isAvailable() and p.supports("matmul", ["Float32", enc])
+    w = oracle.random_kquant_blocks(enc, n, k, seed=n + k)
+    x = np.random.default_rng(n).standard_normal(k).astype(np.float32)
+    ref = oracle.matmul(enc, x, w, k, n, "rm", use_ref=oracle.ref() is not None).reshape(-1)
+    for row_major in (True, False):
+        kern = {("Q6_K", True): p.matmulQ6KRowMajor, ("Q6_K", False): p.matmulQ6K, ("Q5_K", True): p.matmulQ5KRowMajor, ("Q5_K", False): p.matmulQ5K}[(enc, row_major)]()
+        wb = w if row_major else oracle.to_feed_order(w, enc, n, k)
+        xin = np.concatenate([np.full(5, 9.0, np.float32), x])
+        wbuf = np.concatenate([np.full(16, 0xEE, np.uint8), wb])
+        out = np.full(n + 3, -7.0, np.float32)
+        x_before, w_before = xin.copy(), wbuf.copy()
+        kern.matmul(xin, 5, wbuf, 16, k, n, out, 3)
+        assert (out[:3] == -7.0).all()
+        np.testing.assert_array_equal(xin, x_before); np.testing.assert_array_equal(wbuf, w_before)
+        rel_err_ok(out[3:], ref, 1e-5 if enc == "Q6_K" else 1e-4)
+    with pytest.raises(ValueError):
+        p.matmulQ6K().matmul(x, 0, w, 0, 100, n, np.zeros(n, np.float32), 0)
+    untouched = np.full(4, 3.0, np.float32)
+    p.matmulQ5K().matmul(x, 0, w, 0, 0, 4, untouched, 0)            # inputDim 0: output left as it was (q5k_matmul.c:264)
+    assert (untouched == 3.0).all()
+
+
 @pytest.mark.parametrize("enc,n,k", [("Q4_K", 64, 256), ("Q4_K", 129, 4096), ("Q4_K", 33, 11008), ("Q4_K", 1, 512),
                                      ("Q8_0", 64, 32), ("Q8_0", 130, 4096), ("Q8_0", 9, 11008), ("Q8_0", 1, 64)])
 @pytest.mark.parametrize("m", [1, 3, 8, 13, 40, 130])
