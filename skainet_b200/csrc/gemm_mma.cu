@@ -375,7 +375,10 @@ int32_t launch_gemm_mma(const Weight& w, ActQ8K a, int m, float* y, const float*
     }
     if (m <= 2) return 1;
     // (row tiles of 32 or 16 for weights with few rows were measured slower: more activation re-fetch per weight byte)
-    if (m <= 8) return launch_cfg<4, 1, 8>(w, a, m, y, resid, s);
+    // Up to eight rows: a grid of at least one 64-row tile per SM keeps enough bytes in flight with three stages and six
+    // CTAs per SM (57344 x 8192: 65.7 against 77.4 us with eight stages and two CTAs per SM; 10240 x 8192: 21.0 against
+    // 22.2); fewer tiles than SMs need the deep pipeline (8192 x 28672: 70 against 117 us, 8192 x 8192: 19.4 against 20.5).
+    if (m <= 8) return (w.rows + 63) / 64 >= sm_count() ? launch_cfg<4, 1, 3>(w, a, m, y, resid, s) : launch_cfg<4, 1, 8>(w, a, m, y, resid, s);
     if (m <= 16) return launch_cfg<4, 2, 6>(w, a, m, y, resid, s);
     // 64-row tiles until 128-row tiles give about two CTAs per SM (measured on both decoder shapes at batch 32: +3 % / +20 %)
     if ((int64_t) ((w.rows + 127) / 128) * ((m + 31) / 32) < 2 * sm_count()) return launch_cfg<4, 4, 4>(w, a, m, y, resid, s);
