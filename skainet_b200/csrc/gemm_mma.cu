@@ -367,9 +367,12 @@ int32_t launch_gemm_mma(const Weight& w, ActQ8K a, int m, float* y, const float*
     // pipeline; many rows: 128 x 32 output tiles.
     // A small batch over a weight with few columns or few rows: the persistent ring with the same tile arithmetic
     // (gemm_ring.cu). Measured at 8 rows: 4096 x 4096 5.5 against 8.6 us, 22016 x 4096 18.2 against 22.6, 4096 x 11008 18.2
-    // against 20.7; on 8192-column weights of 8192 rows and more this kernel's deep cp.async pipeline is the faster one
-    // (57344 x 8192: 77 against 135 us).
-    if (m >= 3 && m <= 8 && (w.cols <= 4096 || w.rows <= 4096)) {
+    // against 20.7, 8192 x 8192 19.8 against 19.4 (at 4 rows 15.4 against 21.4; inside the 70B decode step at batch 8 / 4:
+    // 16.43 against 16.55 / 18.57 against 19.10 ms); on 8192-column weights of more than 8192 rows this kernel's cp.async
+    // pipeline is the faster one (57344 x 8192: 66 against 100 us, 10240 x 8192: 21 against 27). 8192 x 28672 is faster through
+    // the ring when timed alone (54.6 against 70.3 us) but slower inside the decode step (17.9 against 16.6 ms at batch 8:
+    // the ring's CTAs fill the SMs' shared memory, so the kernel that follows cannot start beside their tail), and stays here.
+    if (m >= 3 && m <= 8 && (w.cols <= 4096 || w.rows <= 4096 || (w.rows <= 8192 && w.cols <= 8192))) {
         const int32_t st = launch_rows_ring(w, a, m, y, resid, s);
         if (st != 1) return st;
     }

@@ -10,10 +10,11 @@
 // Stage = 16 weight rows (one MMA tile) x 8 super-blocks: row r's 1024 bytes of nibbles at r * 1040 (the 16-byte pad makes
 // ldmatrix over eight rows hit 32 distinct banks), then the rows' 128 bytes of headers at stride 144. Consumer warp w takes
 // super-block w of the stage for all 16 rows; the eight warps' partial tiles are added once per row group, in warp order.
-// Two groups per CTA (one when the activation leaves too little room). The quantized activation rows (codes, sub-block
-// sums, block scales) are staged once per CTA in the layout the B fragments read without bank conflicts; shapes whose
-// eight rows do not fit beside three stages are declined (the caller then uses the general tile kernel). Four super-blocks
-// per stage and four groups measured the same (184 against 193 us over twelve 25 MB weights).
+// Two groups per CTA. The quantized activation rows (codes, sub-block sums, block scales) are staged once per CTA in the
+// layout the B fragments read without bank conflicts; where eight rows do not fit beside three stages per group (rows of
+// more than 8192 elements) every consumer warp fetches its super-block's slice of the activation from global memory (L2)
+// into registers one stage ahead instead, and the rings take all of the shared memory. Four super-blocks per stage and
+// four groups measured the same (184 against 193 us over twelve 25 MB weights).
 #include "common.cuh"
 #include "actquant.cuh"
 #include "tma.cuh"
@@ -52,7 +53,7 @@ __device__ __forceinline__ void gr_group_sync(int grp) {
 }
 
 // x_stride: bytes between activation rows in shared memory (bpr * 272, + 16 when that is a multiple of 128 bytes' worth of banks)
-template <int NG, int EPI>
+template <int NG, int EPI, bool XG>
 __global__ void __launch_bounds__(NG * GR_GW * 32)
 q4k_rows_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ hdr, int rows, int bpr, ActQ8K act, int m,
                      float* __restrict__ y, const float* __restrict__ resid, int nstages, int x_stride, int* __restrict__ timeout_flag) {
@@ -61,10 +62,13 @@ q4k_rows_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__
     const int lane = threadIdx.x & 31;
     const int grp = (int) (threadIdx.x >> 5) / GR_GW, warp = (int) (threadIdx.x >> 5) - grp * GR_GW;       // warp GR_BLKS = the group's producer
     uint8_t* s_ring = smem + (size_t) grp * nstages * GR_STAGE;
+    // XG: the activation rows are too long to stage; every consumer warp fetches its super-block's slice from global
+    // memory (L2) into registers one stage ahead instead
     uint8_t* s_x = smem + (size_t) NG * nstages * GR_STAGE;
-    float* s_d = (float*) (s_x + (size_t) GR_MT * x_stride);
-    float* s_part = s_d + ((GR_MT * bpr + 3) & ~3) + grp * 2 * GR_BLKS * 128;
-    uint64_t* full = (uint64_t*) (s_d + ((GR_MT * bpr + 3) & ~3) + NG * 2 * GR_BLKS * 128) + grp * 2 * GR_MAX_STAGES;
+    float* s_d = (float*) (s_x + (XG ? 0 : (size_t) GR_MT * x_stride));
+    const int nd = XG ? 0 : ((GR_MT * bpr + 3) & ~3);
+    float* s_part = s_d + nd + grp * 2 * GR_BLKS * 128;
+    uint64_t* full = (uint64_t*) (s_d + nd + NG * 2 * GR_BLKS * 128) + grp * 2 * GR_MAX_STAGES;
     uint64_t* empty = full + GR_MAX_STAGES;
 
     const int vcta = (int) blockIdx.x * NG + grp, vgrid = (int) gridDim.x * NG;
@@ -103,7 +107,7 @@ q4k_rows_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__
 
     // ---------------- consumers ----------------
     skd::pdl_wait();                                   // the quantized activation rows are the predecessor's output
-    {
+    if (!XG) {
         const int ct = (grp * GR_BLKS + warp) * 32 + lane, nct = NG * GR_BLKS * 32;          // this thread among the consumer threads of the CTA
         for (int c = ct; c < GR_MT * (cols >> 4); c += nct) {                 // 16 codes
             const int row = c / (cols >> 4), ch = c % (cols >> 4), blk = ch >> 4, k16 = ch & 15;
@@ -117,17 +121,42 @@ q4k_rows_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__
             s_d[row * bpr + blk] = row < m ? __ldg(act.d + (size_t) row * bpr + blk) : 0.0f;
         }
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(NG * GR_BLKS * 32) : "memory");
+    if (!XG) asm volatile("bar.sync 1, %0;" ::"n"(NG * GR_BLKS * 32) : "memory");
 
     const int g = lane >> 2, t = lane & 3;
     const int lm_row = (lane & 7) + 8 * ((lane >> 3) & 1), lm_byte = 16 * (lane >> 4);
     int stage = 0, phase = 0, pbuf = 0;
+    // XG: B fragments of activation row g (words 4 t .. of every 16 codes), sub-block sums and block scales of rows 2 t, 2 t + 1
+    uint32_t xw[16], xw_n[16];
+    uint4 xbs[2], xbs_n[2];
+    float xd[2], xd_n[2];
+    auto fetch_x = [&](int b, uint32_t (&w)[16], uint4 (&bs2)[2], float (&d2)[2]) {
+        const int bb = min(b, bpr - 1);
+        const bool live = g < m;
+        const int8_t* src = act.q + (size_t) min(g, m - 1) * cols + (size_t) bb * 256 + 4 * t;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) w[i] = live ? __ldg(reinterpret_cast<const uint32_t*>(src + 16 * i)) : 0u;
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+            const int col = 2 * t + cc;
+            const bool cl = col < m;
+            bs2[cc] = cl ? skd::ld_ro(act.bsums + ((size_t) col * bpr + bb) * 8) : make_uint4(0, 0, 0, 0);
+            d2[cc] = cl ? __ldg(act.d + (size_t) col * bpr + bb) : 0.0f;
+        }
+    };
+    if (XG && my_rgs > 0) fetch_x(warp, xw_n, xbs_n, xd_n);
     for (int rgi = 0; rgi < my_rgs; ++rgi) {
         const int row0 = (vcta + rgi * vgrid) * GR_ROWS;
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         for (int cg = 0; cg < ncg; ++cg) {
             const int b = cg * GR_BLKS + warp;
             const bool live = b < bpr;
+            if (XG) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) xw[i] = xw_n[i];
+                xbs[0] = xbs_n[0]; xbs[1] = xbs_n[1]; xd[0] = xd_n[0]; xd[1] = xd_n[1];
+                fetch_x((cg + 1 < ncg ? cg + 1 : 0) * GR_BLKS + warp, xw_n, xbs_n, xd_n);     // the slice the next stage needs (the same for every row group)
+            }
             if (!skd::mbar_wait_bounded(full + stage, phase, timeout_flag)) return;
             if (live) {
                 const uint8_t* st = s_ring + (size_t) stage * GR_STAGE;
@@ -156,19 +185,21 @@ q4k_rows_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__
                         s_hi[r] = (int) ((word >> (16 * (gq & 1) + 8)) & 0xff);
                     }
                     const uint8_t* xr = xb + 64 * gq;
+                    const uint32_t b0 = XG ? xw[4 * gq] : *(const uint32_t*) xr, b1 = XG ? xw[4 * gq + 1] : *(const uint32_t*) (xr + 16);
+                    const uint32_t b2 = XG ? xw[4 * gq + 2] : *(const uint32_t*) (xr + 32), b3 = XG ? xw[4 * gq + 3] : *(const uint32_t*) (xr + 48);
                     int c[4] = {0, 0, 0, 0};
-                    gr_mma_u8s8(c, lo, *(const uint32_t*) xr, *(const uint32_t*) (xr + 16));
+                    gr_mma_u8s8(c, lo, b0, b1);
                     isum[0] += s_lo[0] * c[0]; isum[1] += s_lo[0] * c[1]; isum[2] += s_lo[1] * c[2]; isum[3] += s_lo[1] * c[3];
                     int e[4] = {0, 0, 0, 0};
-                    gr_mma_u8s8(e, hi, *(const uint32_t*) (xr + 32), *(const uint32_t*) (xr + 48));
+                    gr_mma_u8s8(e, hi, b2, b3);
                     isum[0] += s_hi[0] * e[0]; isum[1] += s_hi[0] * e[1]; isum[2] += s_hi[1] * e[2]; isum[3] += s_hi[1] * e[3];
                 }
                 // mins and the fp32 update; accumulator j: weight row g + 8 (j / 2), activation row 2 t + (j & 1)
 #pragma unroll
                 for (int cc = 0; cc < 2; ++cc) {
                     const int col = 2 * t + cc;
-                    const uint4 bs = skd::lds128(s_x + (size_t) col * x_stride + b * 272 + 256);
-                    const float dx = s_d[col * bpr + b];
+                    const uint4 bs = XG ? xbs[cc] : skd::lds128(s_x + (size_t) col * x_stride + b * 272 + 256);
+                    const float dx = XG ? xd[cc] : s_d[col * bpr + b];
 #pragma unroll
                     for (int r = 0; r < 2; ++r) {
                         int ms = __dp2a_lo((int) bs.x, (int) mn_lo[r], 0);
@@ -208,7 +239,7 @@ q4k_rows_ring_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__
     }
 }
 
-template <int NG>
+template <int NG, bool XG>
 int32_t launch_rows_ring_ng(const Weight& w, ActQ8K a, int m, float* y, const float* resid, size_t fixed, int x_stride, cudaStream_t s) {
     if (GR_BUDGET <= fixed) return 1;
     const int ns = (int) std::min<size_t>(GR_MAX_STAGES, (GR_BUDGET - fixed - (size_t) NG * (2 * GR_BLKS * 128 * 4 + 2 * GR_MAX_STAGES * 8)) / ((size_t) NG * GR_STAGE));
@@ -217,11 +248,11 @@ int32_t launch_rows_ring_ng(const Weight& w, ActQ8K a, int m, float* y, const fl
     const int nrg = (w.rows + GR_ROWS - 1) / GR_ROWS, grid = std::min(sm_count(), (nrg + NG - 1) / NG);
     int* flag = device_timeout_flag();
     if (resid) {
-        auto kernel = q4k_rows_ring_kernel<NG, EPI_ADD>;
+        auto kernel = q4k_rows_ring_kernel<NG, EPI_ADD, XG>;
         SK_TRY(ensure_dynamic_smem((const void*) kernel, 200 * 1024));
         SK_CUDA(launch_pdl(kernel, dim3(grid), dim3(NG * GR_GW * 32), smem, s, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr, a, m, y, resid, ns, x_stride, flag));
     } else {
-        auto kernel = q4k_rows_ring_kernel<NG, EPI_STORE>;
+        auto kernel = q4k_rows_ring_kernel<NG, EPI_STORE, XG>;
         SK_TRY(ensure_dynamic_smem((const void*) kernel, 200 * 1024));
         SK_CUDA(launch_pdl(kernel, dim3(grid), dim3(NG * GR_GW * 32), smem, s, (const uint8_t*) w.qs, (const uint8_t*) w.hdr, w.rows, w.bpr, a, m, y, resid, ns, x_stride, flag));
     }
@@ -238,9 +269,12 @@ int32_t launch_rows_ring(const Weight& w, ActQ8K a, int m, float* y, const float
     const int x_stride = w.bpr * 272 + ((w.bpr & 1) ? 0 : 16);
     const size_t fixed = (size_t) GR_MT * x_stride + (((size_t) GR_MT * w.bpr + 3) & ~(size_t) 3) * 4;
     constexpr int NG0 = 16 / GR_BLKS;                  // sixteen consumer warps per SM
-    const int32_t st = launch_rows_ring_ng<NG0>(w, a, m, y, resid, fixed, x_stride, s);
-    if (st != 1 || NG0 == 1) return st;
-    return launch_rows_ring_ng<(NG0 > 1 ? NG0 / 2 : 1)>(w, a, m, y, resid, fixed, x_stride, s);
+    // staged activation rows where eight of them fit beside three stages per group (11008 x 4096 at 8 rows: 11.3 us staged,
+    // 16.4 us fetched); longer rows are fetched from global memory by the consumers (4096 x 11008: 13.8 us against 18.2 us
+    // for one group with staged rows; 7B decode at batch 8 / 4: 3117 / 1846 against 2931 / 1734 tokens/s)
+    const int32_t st = launch_rows_ring_ng<NG0, false>(w, a, m, y, resid, fixed, x_stride, s);
+    if (st != 1) return st;
+    return launch_rows_ring_ng<NG0, true>(w, a, m, y, resid, 0, x_stride, s);
 }
 
 }  // namespace sk

@@ -57,7 +57,9 @@ def test_fused_qkv_proj_equals_three_reference_matmuls(gpu, oracle, enc, d, qr, 
                                                   # one row into a down projection of 4 MB or more with at most 8192 inputs: SwiGLU inside the ring kernel's prologue
                                                   ("Q4_K", 2048, 4096, 1, True, True), ("Q4_K", 2048, 8192, 1, False, False),
                                                   # a small batch over weights of 4 MB or more: the persistent ring with the tile arithmetic, with and without residual
-                                                  ("Q4_K", 2048, 4096, 6, True, True), ("Q4_K", 2048, 4096, 3, False, False)])
+                                                  ("Q4_K", 2048, 4096, 6, True, True), ("Q4_K", 2048, 4096, 3, False, False),
+                                                  # the same over a down projection whose rows are too long to stage: the ring's consumers fetch the activation, residual epilogue
+                                                  ("Q4_K", 1024, 12288, 6, True, True)])
 def test_fused_swiglu_ffn_equals_the_reference_decomposition(gpu, oracle, enc, d, f, m, norm, resid):
     use_ref = oracle.ref() is not None
     (pg, pu, pd), (wg, wu, wd) = _weights(gpu, oracle, enc, [(f, d), (f, d), (d, f)], seed=f + m)

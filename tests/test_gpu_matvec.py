@@ -102,6 +102,7 @@ def test_k_quant_host_twins_match_the_reference_c(gpu, oracle, enc, n, k):
 
 
 @pytest.mark.parametrize("enc,n,k", [("Q4_K", 64, 256), ("Q4_K", 129, 4096), ("Q4_K", 33, 11008), ("Q4_K", 1, 512),
+                                     ("Q4_K", 520, 16384),       # 4.8 MB with rows too long to stage: 3..8 rows take the ring whose consumers fetch the activation
                                      ("Q8_0", 64, 32), ("Q8_0", 130, 4096), ("Q8_0", 9, 11008), ("Q8_0", 1, 64)])
 @pytest.mark.parametrize("m", [1, 3, 8, 13, 40, 130])
 def test_resident_matvec_matches_oracle(gpu, oracle, enc, n, k, m):
