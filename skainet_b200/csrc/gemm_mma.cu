@@ -384,7 +384,9 @@ int32_t launch_gemm_mma(const Weight& w, ActQ8K a, int m, float* y, const float*
         const int32_t st = launch_rows_ring(w, a, m, y, resid, s);
         if (st != 1) return st;
     }
-    if (m <= 2) return 1;
+    // Two rows: two passes of the streaming matvec, except over weights of 64 MB and more, where one pass of the tile kernel
+    // is faster (57344 x 8192: 64 against 69 us, 8192 x 28672: 66 against 81; 10240 x 8192: 22 against 18 the other way).
+    if (m <= 1 || (m == 2 && w.packed_bytes < ((int64_t) 64 << 20))) return 1;
     // (row tiles of 32 or 16 for weights with few rows were measured slower: more activation re-fetch per weight byte)
     // Up to eight rows: a grid of at least one 64-row tile per SM keeps enough bytes in flight with three stages and six
     // CTAs per SM (57344 x 8192: 65.7 against 77.4 us with eight stages and two CTAs per SM; 10240 x 8192: 21.0 against
