@@ -511,8 +511,11 @@ def run_matvec(args) -> None:
             "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": dtype_of(args.workload), "data": "synthetic", "config": workload_config(args, world, {"weights_per_shape": copies}),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": bytes_per_step / len(weights) * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE if enc in ("Q4_K", "Q8_0") else None,
-                         "traffic_source": "ncu dram bytes per launch of the 11008x4096 Q4_K capture, scaled by weight bytes" if enc in ("Q4_K", "Q8_0") else None,
+                         "traffic": bytes_per_step / len(weights) * {"Q4_K": NCU_TRAFFIC_PER_ALGORITHMIC_BYTE, "Q8_0": NCU_TRAFFIC_PER_ALGORITHMIC_BYTE, "Q6_K": 1.0003}[enc] if enc != "Q5_K" else None,
+                         "traffic_source": {"Q4_K": "ncu dram bytes per launch of the 11008x4096 Q4_K capture, scaled by weight bytes",
+                                            "Q8_0": "ncu dram bytes per launch of the 11008x4096 Q4_K capture, scaled by weight bytes",
+                                            "Q6_K": "ncu dram bytes per q6k_rows_kernel launch on this workload's own shapes (36,998,400 and 37,005,568 read, 0 written, "
+                                                    "against 36,986,880 of weights)", "Q5_K": None}[enc],
                          "peak_kind": peak_kind,
                          "kernel": {"Q4_K": "q4k_matvec_ring_kernel", "Q8_0": "q8_0_matvec_fused_kernel", "Q6_K": "q6k_rows_kernel", "Q5_K": "q5k_rows_kernel"}[enc],
                          "avg_launch_us": per_launch_us,
