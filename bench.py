@@ -19,7 +19,7 @@ Prints ONE JSON line (rank 0). Workloads (all inputs synthetic and seeded):
       GB/s over a sweep of distinct weights larger than 2x L2.
   q8_0_matvec — benchmark config 1: Q8_0 W[4096,4096], same protocol.
   q6k_matvec, q5k_matvec — config 2's two shapes in the encodings Q4_K_M / Q5_K_M files mix in, same protocol.
-  q6k_gemm — the q4k_gemm protocol (--batch activation rows, default 512) on the same shapes as Q6_K.
+  q6k_gemm, q5k_gemm — the q4k_gemm protocol (--batch activation rows, default 512) on the same shapes as Q6_K / Q5_K.
   attn_decode — benchmark config 3: GQA decode attention, 32 query / 8 KV heads, head_dim 128, f16 cache of
       --context keys (default 4096) for --batch sequences; metric = K/V bytes read per second.
   generate_7b — benchmark config 4 as one request: 512 random prompt tokens through the real prefill, then 128 greedy
@@ -72,8 +72,8 @@ MIXED_WORKLOADS = {"decode_7b_mixed"}
 # decode attention alone: (query heads, kv heads, head_dim); context from --context
 ATTN_WORKLOADS = {"attn_decode": (32, 8, 128)}
 # batched rows through the tensor-core tile kernel: the Q4_K sweep shapes with --batch activation rows (default 512)
-GEMM_WORKLOADS = {"q4k_gemm": [(11008, 4096), (4096, 11008)], "q6k_gemm": [(11008, 4096), (4096, 11008)]}
-GEMM_ENC = {"q4k_gemm": "Q4_K", "q6k_gemm": "Q6_K"}
+GEMM_WORKLOADS = {"q4k_gemm": [(11008, 4096), (4096, 11008)], "q6k_gemm": [(11008, 4096), (4096, 11008)], "q5k_gemm": [(11008, 4096), (4096, 11008)]}
+GEMM_ENC = {"q4k_gemm": "Q4_K", "q6k_gemm": "Q6_K", "q5k_gemm": "Q5_K"}
 # whole requests: (model, prompt tokens, generated tokens)
 REQUEST_WORKLOADS = {"generate_7b": ("7b", 512, 128)}
 BLOCK = {"Q4_K": (144, 256), "Q8_0": (34, 32), "Q5_K": (176, 256), "Q6_K": (210, 256)}
@@ -291,6 +291,8 @@ def run_reference(args) -> None:
 def dtype_of(workload: str) -> str:
     if workload == "q6k_gemm":
         return "s8 (6-bit code - 32) x s8 -> s32 on mma.sync per 16-element scale group, int8 group scales, f32 block terms"
+    if workload == "q5k_gemm":
+        return "f16 (5-bit code x 6-bit scale, exact) x f32 activation as two f16 terms -> f32 on mma.sync"
     if workload in GEMM_WORKLOADS:
         return "f16 (4-bit code x 6-bit scale, exact) x f16 (int8 code) -> f32 on tcgen05 for m >= 288; u8 x s8 -> s32 on mma.sync below"
     if workload in ATTN_WORKLOADS:
@@ -317,7 +319,9 @@ def workload_config(args, world: int, extra: dict | None = None) -> dict:
              "l2": "weights per pass far larger than L2"}
     elif args.workload in GEMM_WORKLOADS:
         c = {"workload": args.workload, "encoding": GEMM_ENC[args.workload], "shapes_out_in": GEMM_WORKLOADS[args.workload],
-             "m": args.batch if args.batch > 1 else 512, "activation": "fp32 N(0,1), quantized to int8 per 256 on the device inside the timed region",
+             "m": args.batch if args.batch > 1 else 512,
+             "activation": "fp32 N(0,1), split into two f16 terms on the device inside the timed region" if GEMM_ENC[args.workload] == "Q5_K"
+                           else "fp32 N(0,1), quantized to int8 per 256 on the device inside the timed region",
              "weights": "N(0,0.02) packed on device, seeded" if GEMM_ENC[args.workload] == "Q4_K" else "random valid blocks (random codes and scales, fixed f16 d), seeded, uploaded",
              "l2": "rotating distinct weights larger than 2x L2 per sweep"}
     elif args.workload in ATTN_WORKLOADS:
@@ -692,8 +696,10 @@ def run_gemm(args) -> None:
     achieved = ops / (ms_step * 1e-3) / 1e12
     if enc == "Q4_K":
         kernel = "q4k_gemm_tc_kernel" if m >= 288 else "q4k_gemm_mma_kernel"
-    else:
+    elif enc == "Q6_K":
         kernel = "q6k_gemm_mma_kernel" if m >= 9 else "q6k_rows_kernel"
+    else:
+        kernel = "q5k_gemm_mma_kernel" if m >= 5 else "q5k_rows_kernel"
     line = {"metric": f"{args.workload}_tflops", "value": achieved, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": warm,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype_of(args.workload),
             "data": "synthetic", "config": workload_config(args, 1, {"weights_per_shape": copies}),

@@ -200,7 +200,8 @@ SKAINET_CUDA_API int32_t skainet_cuda_weight_dequant(skainet_weight_t w, float* 
  * Q6_K (native mode = int8 activations per 256 like skainet_q6k_matmul_rm, native/src/q6k_matmul.c:344-357): one warp
  * per output row and up to eight activation rows per pass over the weight, an mma.sync tile kernel from nine rows,
  * every row bit-identical to the single-row result. Q5_K (fp32 activations in both modes, native/src/q5k_matmul.c):
- * one warp per output row, up to four activation rows per pass.
+ * one warp per output row, up to four activation rows per pass; from five rows (native mode) an mma.sync tile kernel
+ * with the activation carried as two f16 terms.
  * Counterpart of PackedViewMatmulKernel.runWith
  * (skainet-backends/skainet-backend-api/src/commonMain/kotlin/sk/ainet/backend/api/kernel/PackedViewMatmulKernel.kt:69-107),
  * which issues m matvec calls. act_mode: SKAINET_ACT_*. */

@@ -118,6 +118,13 @@ struct ActQ8K;
 int32_t launch_matvec_kq(const Weight& w, const float* x, ActQ8K a, int m, float* y, int act_mode, cudaStream_t s, const float* resid = nullptr);
 // gemm_kq.cu: Q6_K weights x m quantized activation rows on the tensor cores (mma.sync); 1 = not taken
 int32_t launch_gemm_q6k(const Weight& w, ActQ8K a, int m, float* y, const float* resid, cudaStream_t s);
+// gemm_kq.cu: Q5_K weights x m fp32 activation rows carried as two f16 terms (hi + lo) plus per-32 sums, on the tensor cores.
+// Activation rows from which a Q5_K product takes this path (fewer rows: the row kernel of matvec_kq.cu, four per pass).
+// 11008 x 4096: 47 us here for up to 32 rows against 42 us for four rows and 83 us for eight through the row kernel.
+constexpr int Q5K_GEMM_MIN_ROWS = 5;
+size_t act_f16split_bytes(int m, int cols);
+int32_t launch_act_f16split(const float* x, int m, int cols, void* scratch, cudaStream_t s);
+int32_t launch_gemm_q5k(const Weight& w, const void* act_scratch, int m, float* y, cudaStream_t s);
 int32_t launch_matvec(const Weight& w, const float* x, const void* act_scratch, int m, float* y, int act_mode,
                       cudaStream_t s);
 // matvec_stream.cu: rows m0..m0+mm of the quantized activation; returns 1 when the shape is not taken

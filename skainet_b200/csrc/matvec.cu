@@ -24,6 +24,7 @@ static inline size_t align256(size_t x) { return (x + 255) & ~(size_t) 255; }
 
 size_t act_scratch_bytes(int enc, int act_mode, int m, int cols) {
     if (act_mode == SKAINET_ACT_F32) return 0;
+    if (enc == SKAINET_ENC_Q5_K) return m >= Q5K_GEMM_MIN_ROWS ? act_f16split_bytes(m, cols) : 0;      // fp32 activations: only the tile kernel wants them prepared
     if (enc == SKAINET_ENC_Q8_0) return align256((size_t) m * cols) * 2 + align256((size_t) m * (cols / 32) * 4);
     return align256((size_t) m * cols) + align256((size_t) m * (cols / 256) * 4) + align256((size_t) m * (cols / 32) * 2);
 }
@@ -66,6 +67,7 @@ __global__ void act_quant_split_kernel(const float* x, int64_t nblocks32, ActSpl
 
 int32_t launch_act_quant(int enc, int act_mode, const float* x, int m, int cols, void* scratch, cudaStream_t s) {
     if (act_mode == SKAINET_ACT_F32 || m == 0 || cols == 0) return SKAINET_CUDA_OK;
+    if (enc == SKAINET_ENC_Q5_K) return m >= Q5K_GEMM_MIN_ROWS ? launch_act_f16split(x, m, cols, scratch, s) : SKAINET_CUDA_OK;
     if (enc == SKAINET_ENC_Q8_0) {
         const int64_t nb = (int64_t) m * (cols / 32);
         SK_CUDA(launch_pdl(act_quant_split_kernel, dim3((unsigned) ((nb * 4 + 255) / 256)), dim3(256), 0, s, x, nb, act_split_layout(scratch, m, cols)));
@@ -281,6 +283,10 @@ int32_t launch_matvec(const Weight& w, const float* x, const void* act_scratch, 
         if (x == nullptr && (w.enc == SKAINET_ENC_Q5_K || act_mode == SKAINET_ACT_F32)) {      // Q6_K in the native mode reads the quantized rows only
             set_error("matmul: Q5_K (and Q6_K in the F32 mode) take the fp32 activation pointer");
             return SKAINET_CUDA_ERR_INVALID;
+        }
+        if (w.enc == SKAINET_ENC_Q5_K && act_mode == SKAINET_ACT_NATIVE && m >= Q5K_GEMM_MIN_ROWS && act_scratch) {
+            const int32_t st = launch_gemm_q5k(w, act_scratch, m, y, s);
+            if (st != 1) return st;
         }
         return launch_matvec_kq(w, x, act_q8k_layout(const_cast<void*>(act_scratch), m, w.cols), m, y, act_mode, s);
     }

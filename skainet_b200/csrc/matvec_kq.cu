@@ -3,8 +3,8 @@
 // The kernels that carry the traffic (q6k_rows_kernel, q5k_rows_kernel): one warp per output row, four super-blocks per
 // step, the next step's weight words requested before the current one is worked on (and the first step's before the wait
 // on the preceding kernel). Up to eight (Q6_K) or four (Q5_K) activation rows ride on one pass over the weight: the codes
-// are decoded once and reused; larger Q5_K batches take one pass per group, larger Q6_K ones the tensor-core tile kernel
-// of gemm_kq.cu. Both formats interleave their bit fields in runs
+// are decoded once and reused; larger batches take the tensor-core tile kernels of gemm_kq.cu (Q6_K from nine rows, Q5_K
+// from five). Both formats interleave their bit fields in runs
 // of 32 elements. Q6_K: eight lanes per super-block, 16 bytes per lane = 16 consecutive elements of one run in the low
 // nibbles and of the run 64 elements later in the high nibbles, one scale group each. Q5_K: see its kernel.
 //
@@ -252,7 +252,8 @@ cudaError_t launch_q5k_rows(const Weight& w, const float* x, int mm, float* y, c
 }  // namespace
 
 // y[m][w.rows] for Q6_K (native int8 activations already quantized into `a`, or fp32 x) and Q5_K (always fp32 x).
-// Activation rows go through in groups of up to eight (Q6_K) or four (Q5_K) per pass over the weight. resid (native Q6_K
+// Activation rows go through in groups of up to eight (Q6_K) or four (Q5_K) per pass over the weight (the callers send
+// larger batches to the tile kernels of gemm_kq.cu first). resid (native Q6_K
 // only; may be y itself): y = resid + W x.
 int32_t launch_matvec_kq(const Weight& w, const float* x, ActQ8K a, int m, float* y, int act_mode, cudaStream_t s, const float* resid) {
     if (m <= 0 || w.rows <= 0) return SKAINET_CUDA_OK;

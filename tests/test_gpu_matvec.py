@@ -230,7 +230,7 @@ def test_k_quant_next_formats_matvec(gpu, oracle, enc, n, k, m):
     activation to int8 per 256 and is integer-exact per block; Q5_K keeps fp32) and, in F32 mode, against the
     dequantised product in float64. The shapes cover rows that are not a multiple of the CTA's four, block counts per row
     that are not a multiple of the four a warp step takes (43, 9, 5, 1), every activation-row group size, batches that
-    need more than one pass over the weight and, from nine rows, the Q6_K tensor-core tile kernel (ragged in both
+    need more than one pass over the weight and the tensor-core tile kernels (Q6_K from nine rows, Q5_K from five) (ragged in both
     directions: 300 / 200 / 1000 weight rows against tiles of 32, 11008 against tiles of 64, 9 / 70 / 130 activation rows
     against tiles of 64)."""
     w_bytes = oracle.random_kquant_blocks(enc, n, k, seed=n + k + m)
