@@ -51,6 +51,10 @@ def test_invalid_dims_raise_before_any_device_work(cuda_lib):
         CudaQ4KMatmulKernel().matmul(x, 0, w, 0, 300, 4, out, 0)
     with pytest.raises(ValueError, match="multiple of 32"):
         CudaQ8_0MatmulKernel().matmul(x, 0, w, 0, 33, 4, out, 0)
+    from skainet_b200.provider import CudaQ6KMatmulKernel, CudaQ5KMatmulKernel
+    for kern in (CudaQ6KMatmulKernel(), CudaQ5KMatmulKernel(), CudaQ6KMatmulKernel(row_major=True), CudaQ5KMatmulKernel(row_major=True)):
+        with pytest.raises(ValueError, match="multiple of 256"):
+            kern.matmul(x, 0, w, 0, 300, 4, out, 0)
 
 
 def test_zero_dims_keep_each_formats_edge_behaviour(cuda_lib):
@@ -62,6 +66,12 @@ def test_zero_dims_keep_each_formats_edge_behaviour(cuda_lib):
     assert (out == 7.0).all()
     CudaQ8_0MatmulKernel().matmul(x, 0, w, 0, 0, 3, out, 0)
     assert (out == 0.0).all()
+    # the other K-quant kernels return early like Q4_K (q6k_matmul.c:284, q5k_matmul.c:264)
+    from skainet_b200.provider import CudaQ6KMatmulKernel, CudaQ5KMatmulKernel
+    out[:] = 7.0
+    CudaQ6KMatmulKernel().matmul(x, 0, w, 0, 0, 3, out, 0)
+    CudaQ5KMatmulKernel(row_major=True).matmul(x, 0, w, 0, 0, 3, out, 0)
+    assert (out == 7.0).all()
 
 
 def test_no_gpu_means_unavailable_not_fallback(cuda_lib):
@@ -72,6 +82,7 @@ def test_no_gpu_means_unavailable_not_fallback(cuda_lib):
         assert p.isAvailable()
         return
     assert not p.isAvailable() and p.matmulQ4K() is None and not p.supports("matmul", ["Float32", "Q4_K"])
+    assert p.matmulQ6K() is None and p.matmulQ5K() is None and not p.supports("matmul", ["Float32", "Q6_K"])
     x = np.ones(4, np.float32); out = np.zeros(4, np.float32)
     st = cuda_lib.skainet_cuda_smoke_double(x.ctypes.data_as(_lib.f32p), out.ctypes.data_as(_lib.f32p), 4)
     assert st == _lib.ERR_NODEVICE and not out.any()
