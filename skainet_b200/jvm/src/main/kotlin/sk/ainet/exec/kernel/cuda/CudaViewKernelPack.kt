@@ -118,7 +118,8 @@ public class CudaPackedMatmulKernel internal constructor(
 }
 
 /**
- * Registers the GPU view kernels into [KernelDispatch]: Q4_K and Q8_0, both block orders. Idempotent, and a
+ * Registers the GPU view kernels into [KernelDispatch]: Q4_K, Q8_0, Q6_K and Q5_K (the encodings `FfmRowMajorKernelPack`
+ * serves that the library has kernels for), both block orders. Idempotent, and a
  * no-op when the provider is unavailable (`ViewKernelPack.install` contract).
  */
 public object CudaViewKernelPack : ViewKernelPack {
@@ -129,7 +130,10 @@ public object CudaViewKernelPack : ViewKernelPack {
     @Synchronized
     override fun install() {
         if (installed || !CudaKernelProvider.isAvailable()) return
-        for ((encoding, id) in listOf(TensorEncoding.Q4_K to CudaKernels.ENC_Q4_K, TensorEncoding.Q8_0 to CudaKernels.ENC_Q8_0)) {
+        for ((encoding, id) in listOf(
+            TensorEncoding.Q4_K to CudaKernels.ENC_Q4_K, TensorEncoding.Q8_0 to CudaKernels.ENC_Q8_0,
+            TensorEncoding.Q6_K to CudaKernels.ENC_Q6_K, TensorEncoding.Q5_K to CudaKernels.ENC_Q5_K,
+        )) {
             for (order in listOf(LayoutClass.BLOCKED_ROW_MAJOR, LayoutClass.BLOCKED_INPUT_MAJOR)) {
                 KernelDispatch.register(CudaPackedMatmulKernel(encoding, id, order))
             }
